@@ -1,0 +1,270 @@
+/*
+ * CUDA device wrapper behind the reference's OpenCL-wrapper entry points
+ * (reference src/dR_clwrap.c): device selection + primary context, one stream as the
+ * in-order command queue (:90), device buffers (:886-913), blocking upload / download
+ * (:1079-1190), per-kernel finish with optional event profiling (:955-1058), error
+ * reporting (:874-883, 1254-1328) and teardown (:1193-1252).  No run-time compilation:
+ * every kernel in the library is built for sm_100a ahead of time.
+ */
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include "dR_core.h"
+#include "dR_b200.h"
+
+static cudaStream_t streamOf(dR_Graph *net) { return (cudaStream_t)net->clConfig->clCommandQueue; }
+
+static gboolean check(dR_Graph *net, cudaError_t e, const char *what)
+{
+    net->clConfig->clError = (cl_int)e;
+    if (e == cudaSuccess) return TRUE;
+    g_print("CUDA error in %s: %s (%d)\n", what, cudaGetErrorString(e), (int)e);
+    return FALSE;
+}
+
+extern "C" const char *dR_b200_version(void)
+{
+    return "deepracin-b200: CUDA sm_100a kernels (FP32 FFMA + tcgen05 TF32), C host API";
+}
+
+extern "C" gboolean dR_clInit(dR_Graph *net)
+{
+    dR_ClConfig *c = net->clConfig;
+    int count = 0;
+    if (!check(net, cudaGetDeviceCount(&count), "cudaGetDeviceCount") || count == 0) {
+        g_print("dR_initCL: no CUDA device available\n");
+        return FALSE;
+    }
+    int ordinal = (int)c->clDeviceNumber;
+    if (ordinal < 0 || ordinal >= count) { g_print("dR_initCL: device ordinal %d out of range (%d devices)\n", ordinal, count); return FALSE; }
+    if (!check(net, cudaSetDevice(ordinal), "cudaSetDevice")) return FALSE;
+    if (!check(net, cudaFree(0), "context creation")) return FALSE;
+    cudaDeviceProp prop;
+    if (!check(net, cudaGetDeviceProperties(&prop, ordinal), "cudaGetDeviceProperties")) return FALSE;
+    c->clNumDevices = (cl_uint)count;
+    c->clDeviceId = ordinal;
+    g_free(c->clDeviceName);
+    c->clDeviceName = g_strdup(prop.name);
+    c->smCount = prop.multiProcessorCount;
+    c->smemPerBlockOptin = prop.sharedMemPerBlockOptin;
+    if (prop.major < 10) g_print("dR_initCL: warning, device %s is sm_%d%d; kernels are built for sm_100a\n", prop.name, prop.major, prop.minor);
+    if (!c->clCommandQueue) {
+        cudaStream_t s;
+        if (!check(net, cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "cudaStreamCreate")) return FALSE;
+        c->clCommandQueue = (cl_command_queue)s;
+        c->ownsStream = TRUE;
+    }
+    if (!c->evStart) {
+        cudaEvent_t a, b;
+        if (!check(net, cudaEventCreate(&a), "cudaEventCreate") || !check(net, cudaEventCreate(&b), "cudaEventCreate")) return FALSE;
+        c->evStart = a; c->evStop = b;
+    }
+    if (c->clInfo && !net->config->silent)
+        g_print("deepRACIN CUDA device %d: %s, %d SMs, %.1f GB\n", ordinal, prop.name, prop.multiProcessorCount, prop.totalGlobalMem / 1073741824.0);
+    c->cleanupDone = FALSE;
+    return TRUE;
+}
+
+static gboolean bindDevice(dR_Graph *net)
+{
+    return check(net, cudaSetDevice((int)net->clConfig->clDeviceNumber), "cudaSetDevice");
+}
+
+extern "C" gboolean dR_createFloatBufferL(dR_Graph *net, cl_mem *mem, size_t numFloats)
+{
+    void *p = NULL;
+    if (numFloats == 0) numFloats = 1;
+    if (net->config->dryRun) {      /* placeholder address, never dereferenced */
+        size_t bytes = (numFloats * sizeof(float) + 255) / 256 * 256;
+        *mem = (void *)(uintptr_t)(0x10000 + net->config->dryRunCursor);
+        net->config->dryRunCursor += bytes;
+        net->clConfig->memConsumptionGPU += (glong)(numFloats * sizeof(float));
+        return TRUE;
+    }
+    if (!bindDevice(net)) return FALSE;
+    if (!check(net, cudaMalloc(&p, numFloats * sizeof(float)), "cudaMalloc")) { *mem = NULL; return FALSE; }
+    net->clConfig->memConsumptionGPU += (glong)(numFloats * sizeof(float));
+    *mem = p;
+    return TRUE;
+}
+
+extern "C" gboolean dR_createFloatBuffer(dR_Graph *net, cl_mem *mem, gint size, int buffertype)
+{
+    (void)buffertype;
+    if (size < 0) return FALSE;
+    return dR_createFloatBufferL(net, mem, (size_t)size);
+}
+
+extern "C" gboolean dR_uploadArray(dR_Graph *net, gchar *name, void *src, size_t offset, size_t numBytes, cl_mem dst)
+{
+    (void)name;
+    if (net->config->dryRun) return TRUE;
+    if (!dst || !src) { g_print("dR_uploadArray: NULL buffer\n"); return FALSE; }
+    if (!bindDevice(net)) return FALSE;
+    cudaStream_t s = streamOf(net);
+    if (!check(net, cudaMemcpyAsync((char *)dst + offset, src, numBytes, cudaMemcpyHostToDevice, s), "cudaMemcpyAsync H2D")) return FALSE;
+    return check(net, cudaStreamSynchronize(s), "upload synchronize");
+}
+
+extern "C" void dR_downloadArray(dR_Graph *net, gchar *name, cl_mem *src, size_t byteOffset, size_t numBytes, void *dst)
+{
+    (void)name;
+    if (!src || !*src || !dst) { g_print("dR_downloadArray: NULL buffer\n"); return; }
+    if (!bindDevice(net)) return;
+    cudaStream_t s = streamOf(net);
+    if (!check(net, cudaMemcpyAsync(dst, (char *)*src + byteOffset, numBytes, cudaMemcpyDeviceToHost, s), "cudaMemcpyAsync D2H")) return;
+    check(net, cudaStreamSynchronize(s), "download synchronize");
+}
+
+extern "C" gboolean dR_uploadArrayAsync(dR_Graph *net, void *src, size_t numBytes, cl_mem dst)
+{
+    if (!dst || !src) return FALSE;
+    return check(net, cudaMemcpyAsync(dst, src, numBytes, cudaMemcpyHostToDevice, streamOf(net)), "cudaMemcpyAsync H2D");
+}
+
+extern "C" gboolean dR_downloadArrayAsync(dR_Graph *net, cl_mem src, size_t numBytes, void *dst)
+{
+    if (!dst || !src) return FALSE;
+    return check(net, cudaMemcpyAsync(dst, src, numBytes, cudaMemcpyDeviceToHost, streamOf(net)), "cudaMemcpyAsync D2H");
+}
+
+extern "C" gboolean dR_zeroBuffer(dR_Graph *net, cl_mem mem, size_t numFloats)
+{
+    if (net->config->dryRun) return TRUE;
+    return check(net, cudaMemsetAsync(mem, 0, numFloats * sizeof(float), streamOf(net)), "cudaMemsetAsync");
+}
+
+extern "C" void *dR_hostAllocPinned(size_t bytes)
+{
+    void *p = NULL;
+    if (cudaMallocHost(&p, bytes) != cudaSuccess) return NULL;
+    return p;
+}
+
+extern "C" void dR_hostFreePinned(void *p) { if (p) cudaFreeHost(p); }
+
+extern "C" gboolean dR_finish(dR_Graph *net)
+{
+    if (!net->clConfig->clCommandQueue || net->config->dryRun) return TRUE;
+    return check(net, cudaStreamSynchronize(streamOf(net)), "cudaStreamSynchronize");
+}
+
+extern "C" void dR_beginCLKernel(dR_Graph *net)
+{
+    if (net->config->profilingGPU) cudaEventRecord((cudaEvent_t)net->clConfig->evStart, streamOf(net));
+}
+
+extern "C" gboolean dR_finishCLKernel(dR_Graph *net, char *kernelName)
+{
+    dR_ClConfig *c = net->clConfig;
+    if (c->clError != 0) return !dR_openCLError(net, (char *)"kernel launch failed", kernelName);
+    cudaError_t e = cudaPeekAtLastError();
+    if (e != cudaSuccess) { c->clError = (cl_int)e; return !dR_openCLError(net, (char *)"kernel launch failed", kernelName); }
+    if (net->config->profilingGPU) {
+        float ms = 0.f;
+        cudaEventRecord((cudaEvent_t)c->evStop, streamOf(net));
+        e = cudaEventSynchronize((cudaEvent_t)c->evStop);
+        if (e != cudaSuccess) { c->clError = (cl_int)e; return !dR_openCLError(net, (char *)"kernel execution failed", kernelName); }
+        cudaEventElapsedTime(&ms, (cudaEvent_t)c->evStart, (cudaEvent_t)c->evStop);
+        if (!net->config->silent) g_print("GPU Profiling: %s took %2.4f ms\n", kernelName, ms);
+        c->totalKernelGPUTime += ms;
+        c->queueKernelGPUTime = ms;
+    }
+    return TRUE;
+}
+
+extern "C" gboolean dR_openCLError(dR_Graph *net, char *message, char *callerName)
+{
+    cl_int e = net->clConfig->clError;
+    if (e == 0) return FALSE;
+    if (e > 0) g_print("CUDA error %d (%s): %s [%s]\n", e, cudaGetErrorString((cudaError_t)e), message, callerName);
+    else g_print("Kernel argument error %d: %s [%s]\n", e, message, callerName);
+    cudaGetLastError();     /* clear the sticky launch error; the context stays alive */
+    return TRUE;
+}
+
+extern "C" gboolean dR_openCLErrorWithoutCleanup(dR_Graph *net, char *message, char *callerName) { return dR_openCLError(net, message, callerName); }
+
+extern "C" gboolean dR_clMemoryBufferCleanup(dR_Graph *net, cl_mem mem)
+{
+    if (!mem || net->config->dryRun) return TRUE;
+    return check(net, cudaFree(mem), "cudaFree");
+}
+
+extern "C" gboolean dR_cleanupKernel(cl_kernel kernel) { (void)kernel; return TRUE; }
+extern "C" gboolean dR_cleanupProgram(cl_program program) { (void)program; return TRUE; }
+
+extern "C" gboolean dR_cleanupCL(dR_Graph *net)
+{
+    dR_ClConfig *c = net->clConfig;
+    if (c->cleanupDone) return TRUE;
+    if (c->evStart) { cudaEventDestroy((cudaEvent_t)c->evStart); cudaEventDestroy((cudaEvent_t)c->evStop); c->evStart = c->evStop = NULL; }
+    if (c->ownsStream && c->clCommandQueue) cudaStreamDestroy(streamOf(net));
+    c->clCommandQueue = NULL;
+    g_free(c->clDeviceName);
+    c->clDeviceName = NULL;
+    c->cleanupDone = TRUE;
+    return TRUE;
+}
+
+extern "C" gboolean dR_exportFloatArrayToCSV(dR_Graph *net, gchar *filepath, gchar *filename, cl_mem deviceMem, cl_float *hostMem, size_t numFloats)
+{
+    gchar *p = dR_build_filename(filepath, filename);
+    cl_mem m = deviceMem;
+    dR_downloadArray(net, (gchar *)"", &m, 0, numFloats * sizeof(float), hostMem);
+    FILE *f = fopen(p, "w");
+    g_free(p);
+    if (!f) return FALSE;
+    for (size_t i = 0; i < numFloats; i++) fprintf(f, "%g%s", hostMem[i], (i % 16 == 15 || i + 1 == numFloats) ? "\n" : ",");
+    fclose(f);
+    return TRUE;
+}
+
+extern "C" void dR_timerStart(dR_Graph *net) { cudaEventRecord((cudaEvent_t)net->clConfig->evStart, streamOf(net)); }
+
+extern "C" gdouble dR_timerStopMs(dR_Graph *net)
+{
+    float ms = 0.f;
+    cudaEventRecord((cudaEvent_t)net->clConfig->evStop, streamOf(net));
+    if (cudaEventSynchronize((cudaEvent_t)net->clConfig->evStop) != cudaSuccess) return -1.0;
+    cudaEventElapsedTime(&ms, (cudaEvent_t)net->clConfig->evStart, (cudaEvent_t)net->clConfig->evStop);
+    return (gdouble)ms;
+}
+
+/* The whole node schedule is one straight launch sequence on one stream, so it can be
+ * captured once and replayed; batch-1 graphs with dozens of small nodes are launch bound. */
+extern "C" gboolean dR_captureBegin(dR_Graph *net)
+{
+    return check(net, cudaStreamBeginCapture(streamOf(net), cudaStreamCaptureModeThreadLocal), "cudaStreamBeginCapture");
+}
+
+extern "C" gboolean dR_captureEnd(dR_Graph *net)
+{
+    cudaGraph_t g = NULL;
+    cudaGraphExec_t ex = NULL;
+    if (!check(net, cudaStreamEndCapture(streamOf(net), &g), "cudaStreamEndCapture")) return FALSE;
+    gboolean ok = check(net, cudaGraphInstantiate(&ex, g, 0), "cudaGraphInstantiate");
+    cudaGraphDestroy(g);
+    if (ok) net->graphExec = ex;
+    return ok;
+}
+
+extern "C" gboolean dR_captureLaunch(dR_Graph *net)
+{
+    return check(net, cudaGraphLaunch((cudaGraphExec_t)net->graphExec, streamOf(net)), "cudaGraphLaunch");
+}
+
+extern "C" void dR_captureDestroy(dR_Graph *net)
+{
+    if (net->graphExec) { cudaGraphExecDestroy((cudaGraphExec_t)net->graphExec); net->graphExec = NULL; }
+}
+
+extern "C" gint dR_getDeviceStatus(dR_Graph *net)
+{
+    int st[4] = {0, 0, 0, 0};
+    if (!net->statusWord) return 0;
+    cl_mem m = net->statusWord;
+    dR_downloadArray(net, (gchar *)"", &m, 0, sizeof st, st);
+    if (st[0]) dR_zeroBuffer(net, net->statusWord, 4);
+    net->deviceStatus = st[0];
+    return st[0];
+}

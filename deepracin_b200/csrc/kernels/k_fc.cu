@@ -1,0 +1,163 @@
+/*
+ * Fully connected layer, exact FP32.  The weight matrix [Nin][Nout] is the only large
+ * operand (VGG fc6: 411 MB) and is read exactly once per batch:
+ *   - batch <= 16: weight-streaming kernel; a warp owns 128 output columns and walks a
+ *     K-slice with 128-bit loads, keeping batch x 4 accumulators per lane; the CTA's warps
+ *     split the slice and combine through shared memory; K is split across CTAs so that a few
+ *     hundred CTAs keep HBM busy.  HBM-bound: Nin*Nout*4 bytes per call.
+ *   - larger batches: the FFMA GEMM core, batched over K-slices.
+ * Both write per-slice partial sums to scratch; a second launch adds them, the bias and
+ * applies the activation -- the same two-step shape as the reference's
+ * matrixVectorMultFirst / matrixVectorMultSecond (Kernels/dR_fcl.cl:59-120).
+ */
+#include "k_common.cuh"
+#include "k_gemm_f32.cuh"
+
+#define FC_COLS 128        /* output columns per CTA (32 lanes x float4) */
+#define FC_WARPS 8
+#define FC_MAXB 16
+#define FC_KSTAGE 256      /* input values staged in shared memory per step */
+
+template <int NB>
+__global__ void __launch_bounds__(FC_WARPS * 32) k_fc_stream(const float *__restrict__ in, const float *__restrict__ w, float *__restrict__ partial,
+                                                            int nb, int Nin, int Nout, int kchunk)
+{
+    __shared__ float xs[NB][FC_KSTAGE];
+    __shared__ float4 red[FC_WARPS][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int col = blockIdx.x * FC_COLS + lane * 4;
+    const int kbeg = blockIdx.y * kchunk;
+    const int kend = min(Nin, kbeg + kchunk);
+    const bool colok = col < Nout;      /* Nout % 4 == 0 is guaranteed by the launcher */
+    float4 acc[NB];
+#pragma unroll
+    for (int b = 0; b < NB; b++) acc[b] = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    for (int k0 = kbeg; k0 < kend; k0 += FC_KSTAGE) {
+        const int kn = min(FC_KSTAGE, kend - k0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < NB * FC_KSTAGE; i += blockDim.x) {
+            const int b = i / FC_KSTAGE, k = i % FC_KSTAGE;
+            xs[b][k] = (b < nb && k < kn) ? in[(size_t)b * Nin + k0 + k] : 0.f;
+        }
+        __syncthreads();
+        if (colok) {
+            /* warp `warp` takes rows warp, warp+8, ...; four rows in flight per lane */
+            int k = warp;
+            for (; k + 3 * FC_WARPS < kn; k += 4 * FC_WARPS) {
+                float4 w0 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k) * Nout + col));
+                float4 w1 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k + FC_WARPS) * Nout + col));
+                float4 w2 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k + 2 * FC_WARPS) * Nout + col));
+                float4 w3 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k + 3 * FC_WARPS) * Nout + col));
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    const float x0 = xs[b][k], x1 = xs[b][k + FC_WARPS], x2 = xs[b][k + 2 * FC_WARPS], x3 = xs[b][k + 3 * FC_WARPS];
+                    acc[b].x = fmaf(x0, w0.x, acc[b].x); acc[b].y = fmaf(x0, w0.y, acc[b].y); acc[b].z = fmaf(x0, w0.z, acc[b].z); acc[b].w = fmaf(x0, w0.w, acc[b].w);
+                    acc[b].x = fmaf(x1, w1.x, acc[b].x); acc[b].y = fmaf(x1, w1.y, acc[b].y); acc[b].z = fmaf(x1, w1.z, acc[b].z); acc[b].w = fmaf(x1, w1.w, acc[b].w);
+                    acc[b].x = fmaf(x2, w2.x, acc[b].x); acc[b].y = fmaf(x2, w2.y, acc[b].y); acc[b].z = fmaf(x2, w2.z, acc[b].z); acc[b].w = fmaf(x2, w2.w, acc[b].w);
+                    acc[b].x = fmaf(x3, w3.x, acc[b].x); acc[b].y = fmaf(x3, w3.y, acc[b].y); acc[b].z = fmaf(x3, w3.z, acc[b].z); acc[b].w = fmaf(x3, w3.w, acc[b].w);
+                }
+            }
+            for (; k < kn; k += FC_WARPS) {
+                float4 w0 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k) * Nout + col));
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    const float x0 = xs[b][k];
+                    acc[b].x = fmaf(x0, w0.x, acc[b].x); acc[b].y = fmaf(x0, w0.y, acc[b].y); acc[b].z = fmaf(x0, w0.z, acc[b].z); acc[b].w = fmaf(x0, w0.w, acc[b].w);
+                }
+            }
+        }
+    }
+    /* combine the CTA's warps, one batch row at a time */
+#pragma unroll
+    for (int b = 0; b < NB; b++) {
+        __syncthreads();
+        red[warp][lane] = acc[b];
+        __syncthreads();
+        if (warp == 0 && b < nb && colok) {
+            float4 s = red[0][lane];
+#pragma unroll
+            for (int wv = 1; wv < FC_WARPS; wv++) {
+                const float4 t = red[wv][lane];
+                s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+            }
+            *reinterpret_cast<float4 *>(partial + ((size_t)blockIdx.y * nb + b) * Nout + col) = s;
+        }
+    }
+}
+
+/* out[b][o] = clamp(act(bias[o] + sum_s partial[s][b][o])) -- step two of the reference (Kernels/dR_fcl.cl:99-120) */
+__global__ void k_fc_reduce(const float *__restrict__ partial, const float *__restrict__ bias, float *__restrict__ out,
+                            int total, int Nout, int splits, int act)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float s = 0.f;
+    for (int p = 0; p < splits; p++) s += partial[(size_t)p * total + i];
+    if (bias) s += bias[i % Nout];
+    out[i] = act ? fminf(fmaxf(s, 0.0f), FLT_MAX) : fminf(fmaxf(s, -FLT_MAX), FLT_MAX);
+}
+
+static int fc_splits(int n, int Nin, int Nout)
+{
+    /* aim for roughly 4 CTAs per SM; keep slices a multiple of 64 rows and at least 256 long */
+    const int colBlocks = n <= FC_MAXB && Nout % 4 == 0 ? (Nout + FC_COLS - 1) / FC_COLS
+                                                        : ((Nout + 127) / 128) * ((n + 127) / 128);
+    int splits = (4 * 148 + colBlocks - 1) / colBlocks;
+    const int maxSplits = Nin / 256 > 0 ? Nin / 256 : 1;
+    if (splits > maxSplits) splits = maxSplits;
+    if (splits < 1) splits = 1;
+    if (splits > 64) splits = 64;
+    return splits;
+}
+
+static int fc_kchunk(int Nin, int splits)
+{
+    int kc = (Nin + splits - 1) / splits;
+    kc = (kc + 63) / 64 * 64;
+    return kc;
+}
+
+extern "C" size_t dRk_fc_scratch_floats(int n, int Nin, int Nout)
+{
+    if (n <= 0 || Nin <= 0 || Nout <= 0) return 0;
+    const int splits = fc_splits(n, Nin, Nout);
+    return (size_t)splits * n * Nout;
+}
+
+extern "C" int dRk_fc_f32(dRk_stream stream, const float *in, const float *w, const float *bias, float *out, float *scratch,
+                          int n, int Nin, int Nout, int act)
+{
+    if (n <= 0 || Nin <= 0 || Nout <= 0 || !scratch) return -1;
+    cudaStream_t st = drk_stream(stream);
+    int splits = fc_splits(n, Nin, Nout);
+    const int kchunk = fc_kchunk(Nin, splits);
+    splits = (Nin + kchunk - 1) / kchunk;       /* drop empty trailing slices */
+    int rc;
+    if (n <= FC_MAXB && Nout % 4 == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)scratch % 16) == 0) {
+        dim3 grid((Nout + FC_COLS - 1) / FC_COLS, splits);
+        if (n <= 1) k_fc_stream<1><<<grid, FC_WARPS * 32, 0, st>>>(in, w, scratch, n, Nin, Nout, kchunk);
+        else if (n <= 2) k_fc_stream<2><<<grid, FC_WARPS * 32, 0, st>>>(in, w, scratch, n, Nin, Nout, kchunk);
+        else if (n <= 4) k_fc_stream<4><<<grid, FC_WARPS * 32, 0, st>>>(in, w, scratch, n, Nin, Nout, kchunk);
+        else if (n <= 8) k_fc_stream<8><<<grid, FC_WARPS * 32, 0, st>>>(in, w, scratch, n, Nin, Nout, kchunk);
+        else k_fc_stream<16><<<grid, FC_WARPS * 32, 0, st>>>(in, w, scratch, n, Nin, Nout, kchunk);
+        DRK_COUNT_LAUNCH();
+        rc = DRK_LAUNCH_RESULT();
+    } else {
+        /* K-sliced GEMM: slice z multiplies A[:, z*kchunk : ...] by B[z*kchunk : ..., :]; the last slice may be shorter,
+           so it is launched separately when Nin is not a multiple of kchunk */
+        const int full = Nin / kchunk, tail = Nin - full * kchunk;
+        rc = 0;
+        if (full > 0)
+            rc = drk_gemm_f32_launch(st, in, w, NULL, scratch, n, Nout, kchunk, Nin, Nout, Nout, 0, 0, full,
+                                     (size_t)kchunk, (size_t)kchunk * Nout, (size_t)n * Nout, NULL);
+        if (rc == 0 && tail > 0)
+            rc = drk_gemm_f32_launch(st, in + (size_t)full * kchunk, w + (size_t)full * kchunk * Nout, NULL,
+                                     scratch + (size_t)full * n * Nout, n, Nout, tail, Nin, Nout, Nout, 0, 0, 1, 0, 0, 0, NULL);
+    }
+    if (rc != 0) return rc;
+    const int total = n * Nout;
+    k_fc_reduce<<<(total + 255) / 256, 256, 0, st>>>(scratch, bias, out, total, Nout, splits, act);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}

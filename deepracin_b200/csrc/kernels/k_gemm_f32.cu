@@ -1,0 +1,262 @@
+/*
+ * Exact-FP32 (FFMA) GEMM core of the CNN-layer path, used three ways:
+ *   - implicit-GEMM convolution: A rows are output pixels gathered on the fly from the
+ *     N-HWC input (zero padded), B is the packed filter matrix [kh*kw*Cin][Cout];
+ *   - dense GEMM for the 16 transform-domain products of the Winograd path;
+ *   - dense split-K GEMM for fully connected layers at larger batch sizes.
+ * CTA tile BM x BN x 16, 256 threads, TM x TN accumulators per thread, operands staged in
+ * shared memory (A stored k-major so both operands are read as float4), next tile
+ * prefetched into registers while the current one is multiplied.  Bound: FP32 FFMA issue
+ * rate for K >= ~100, HBM for the first VGG layer (K = 27).
+ */
+#include "k_common.cuh"
+#include "k_gemm_f32.cuh"
+
+#define BK 16
+
+template <int BM, int BN, int TM, int TN, bool CONV>
+__global__ void __launch_bounds__(256) k_gemm_f32(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias,
+                                                  float *__restrict__ C, int M, int N, int K, int lda, int ldb, int ldc, int coff, int act,
+                                                  size_t strideA, size_t strideB, size_t strideC, int vecA, int vecB, int vecC, drk_ConvGeom g)
+{
+    constexpr int LDA_S = BM + 4;
+    constexpr int A_UNITS = BM * BK / 4 / 256 > 0 ? BM * BK / 4 / 256 : 1;   /* float4 units per thread */
+    constexpr int B_UNITS = BN * BK / 4 / 256 > 0 ? BN * BK / 4 / 256 : 1;
+    constexpr int A_ACTIVE = BM * BK / 4;   /* total units */
+    constexpr int B_ACTIVE = BN * BK / 4;
+    constexpr int RCH = TM / 4, CCH = TN / 4;
+    __shared__ __align__(16) float As[2][BK][LDA_S];
+    __shared__ __align__(16) float Bs[2][BK][BN];
+
+    const int tid = threadIdx.x;
+    const int tx = tid % (BN / TN), ty = tid / (BN / TN);
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    A += (size_t)blockIdx.z * strideA;
+    B += (size_t)blockIdx.z * strideB;
+    C += (size_t)blockIdx.z * strideC;
+
+    /* per-thread description of the A rows it stages */
+    int a_row[A_UNITS], a_kseg[A_UNITS];
+    bool a_ok[A_UNITS];
+    size_t a_base[A_UNITS];             /* dense: row offset; conv: image offset */
+    int a_iy0[A_UNITS], a_ix0[A_UNITS];
+#pragma unroll
+    for (int i = 0; i < A_UNITS; i++) {
+        const int u = tid + i * 256;
+        a_row[i] = u / (BK / 4);
+        a_kseg[i] = (u % (BK / 4)) * 4;
+        const int m = m0 + a_row[i];
+        a_ok[i] = u < A_ACTIVE && m < M;
+        a_base[i] = 0; a_iy0[i] = 0; a_ix0[i] = 0;
+        if (a_ok[i]) {
+            if (CONV) {
+                const int ox = m % g.Wo;
+                const int t = m / g.Wo;
+                const int oy = t % g.Ho;
+                const int b = t / g.Ho;
+                a_base[i] = (size_t)b * g.H * g.W;
+                a_iy0[i] = oy * g.sy - g.py;
+                a_ix0[i] = ox * g.sx - g.px;
+            } else {
+                a_base[i] = (size_t)m * lda;
+            }
+        }
+    }
+    int b_krow[B_UNITS], b_n[B_UNITS];
+#pragma unroll
+    for (int i = 0; i < B_UNITS; i++) {
+        const int u = tid + i * 256;
+        b_krow[i] = u / (BN / 4);
+        b_n[i] = (u % (BN / 4)) * 4;
+    }
+
+    float4 ra[A_UNITS], rb[B_UNITS];
+
+    auto load_tiles = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < A_UNITS; i++) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int k = k0 + a_kseg[i];
+            if (a_ok[i] && k < K) {
+                if (CONV) {
+                    if (vecA) {
+                        const int tap = k / g.Cin, c = k - tap * g.Cin;
+                        const int ky = tap / g.kw, kx = tap - ky * g.kw;
+                        const int iy = a_iy0[i] + ky, ix = a_ix0[i] + kx;
+                        if (iy >= 0 && iy < g.H && ix >= 0 && ix < g.W)
+                            v = *reinterpret_cast<const float4 *>(A + (a_base[i] + (size_t)iy * g.W + ix) * g.ldi + c);
+                    } else {
+                        float t[4];
+#pragma unroll
+                        for (int j = 0; j < 4; j++) {
+                            t[j] = 0.f;
+                            const int kk = k + j;
+                            if (kk < K) {
+                                const int tap = kk / g.Cin, c = kk - tap * g.Cin;
+                                const int ky = tap / g.kw, kx = tap - ky * g.kw;
+                                const int iy = a_iy0[i] + ky, ix = a_ix0[i] + kx;
+                                if (iy >= 0 && iy < g.H && ix >= 0 && ix < g.W) t[j] = A[(a_base[i] + (size_t)iy * g.W + ix) * g.ldi + c];
+                            }
+                        }
+                        v = make_float4(t[0], t[1], t[2], t[3]);
+                    }
+                } else {
+                    const float *p = A + a_base[i] + k;
+                    if (vecA && k + 3 < K) v = *reinterpret_cast<const float4 *>(p);
+                    else {
+                        v.x = p[0];
+                        if (k + 1 < K) v.y = p[1];
+                        if (k + 2 < K) v.z = p[2];
+                        if (k + 3 < K) v.w = p[3];
+                    }
+                }
+            }
+            ra[i] = v;
+        }
+#pragma unroll
+        for (int i = 0; i < B_UNITS; i++) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int k = k0 + b_krow[i], n = n0 + b_n[i];
+            if (tid + i * 256 < B_ACTIVE && k < K && n < N) {
+                const float *p = B + (size_t)k * ldb + n;
+                if (vecB && n + 3 < N) v = *reinterpret_cast<const float4 *>(p);
+                else {
+                    v.x = p[0];
+                    if (n + 1 < N) v.y = p[1];
+                    if (n + 2 < N) v.z = p[2];
+                    if (n + 3 < N) v.w = p[3];
+                }
+            }
+            rb[i] = v;
+        }
+    };
+    auto store_tiles = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < A_UNITS; i++) {
+            if (tid + i * 256 < A_ACTIVE) {
+                As[buf][a_kseg[i] + 0][a_row[i]] = ra[i].x;
+                As[buf][a_kseg[i] + 1][a_row[i]] = ra[i].y;
+                As[buf][a_kseg[i] + 2][a_row[i]] = ra[i].z;
+                As[buf][a_kseg[i] + 3][a_row[i]] = ra[i].w;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < B_UNITS; i++)
+            if (tid + i * 256 < B_ACTIVE) *reinterpret_cast<float4 *>(&Bs[buf][b_krow[i]][b_n[i]]) = rb[i];
+    };
+
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; i++)
+#pragma unroll
+        for (int j = 0; j < TN; j++) acc[i][j] = 0.f;
+
+    const int numKT = (K + BK - 1) / BK;
+    load_tiles(0);
+    store_tiles(0);
+    __syncthreads();
+    int cur = 0;
+    for (int kt = 0; kt < numKT; kt++) {
+        if (kt + 1 < numKT) load_tiles((kt + 1) * BK);
+#pragma unroll
+        for (int k = 0; k < BK; k++) {
+            float a[TM], b[TN];
+#pragma unroll
+            for (int r = 0; r < RCH; r++) {
+                const float4 t = *reinterpret_cast<const float4 *>(&As[cur][k][r * (BM / RCH) + ty * 4]);
+                a[r * 4 + 0] = t.x; a[r * 4 + 1] = t.y; a[r * 4 + 2] = t.z; a[r * 4 + 3] = t.w;
+            }
+#pragma unroll
+            for (int c = 0; c < CCH; c++) {
+                const float4 t = *reinterpret_cast<const float4 *>(&Bs[cur][k][c * (BN / CCH) + tx * 4]);
+                b[c * 4 + 0] = t.x; b[c * 4 + 1] = t.y; b[c * 4 + 2] = t.z; b[c * 4 + 3] = t.w;
+            }
+#pragma unroll
+            for (int i = 0; i < TM; i++)
+#pragma unroll
+                for (int j = 0; j < TN; j++) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+        }
+        if (kt + 1 < numKT) {
+            store_tiles(cur ^ 1);
+            __syncthreads();
+            cur ^= 1;
+        }
+    }
+
+    /* epilogue: bias, activation, store at (pixel stride ldc, channel offset coff) */
+#pragma unroll
+    for (int r = 0; r < RCH; r++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            const int m = m0 + r * (BM / RCH) + ty * 4 + i;
+            if (m >= M) continue;
+            float *crow = C + (size_t)m * ldc + coff;
+#pragma unroll
+            for (int c = 0; c < CCH; c++) {
+                const int n = n0 + c * (BN / CCH) + tx * 4;
+                if (n >= N) continue;
+                float v[4];
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    float t = acc[r * 4 + i][c * 4 + j];
+                    if (bias && n + j < N) t += bias[n + j];
+                    v[j] = drk_act(t, act);
+                }
+                if (vecC && n + 3 < N) *reinterpret_cast<float4 *>(crow + n) = make_float4(v[0], v[1], v[2], v[3]);
+                else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) if (n + j < N) crow[n + j] = v[j];
+                }
+            }
+        }
+}
+
+static bool aligned16(const void *p) { return ((uintptr_t)p % 16) == 0; }
+
+int drk_gemm_f32_launch(cudaStream_t st, const float *A, const float *B, const float *bias, float *C, int M, int N, int K,
+                        int lda, int ldb, int ldc, int coff, int act, int batch, size_t sA, size_t sB, size_t sC, const drk_ConvGeom *geom)
+{
+    if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -1;
+    drk_ConvGeom g;
+    memset(&g, 0, sizeof g);
+    int vecA;
+    if (geom) {
+        g = *geom;
+        vecA = g.Cin % 4 == 0 && g.ldi % 4 == 0 && aligned16(A);
+    } else {
+        vecA = lda % 4 == 0 && aligned16(A) && sA % 4 == 0;
+    }
+    const int vecB = ldb % 4 == 0 && aligned16(B) && sB % 4 == 0;
+    const int vecC = ldc % 4 == 0 && coff % 4 == 0 && aligned16(C) && sC % 4 == 0;
+    const long big = (long)((M + 127) / 128) * ((N + 127) / 128) * batch;
+    const bool small = big < 120 || N <= 64 || M <= 64;
+    dim3 grid;
+    if (small) grid = dim3((N + 63) / 64, (M + 63) / 64, batch);
+    else grid = dim3((N + 127) / 128, (M + 127) / 128, batch);
+    if (grid.y > 65535u || grid.z > 65535u) return -2;
+    if (geom) {
+        if (small) k_gemm_f32<64, 64, 4, 4, true><<<grid, 256, 0, st>>>(A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecA, vecB, vecC, g);
+        else k_gemm_f32<128, 128, 8, 8, true><<<grid, 256, 0, st>>>(A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecA, vecB, vecC, g);
+    } else {
+        if (small) k_gemm_f32<64, 64, 4, 4, false><<<grid, 256, 0, st>>>(A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecA, vecB, vecC, g);
+        else k_gemm_f32<128, 128, 8, 8, false><<<grid, 256, 0, st>>>(A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecA, vecB, vecC, g);
+    }
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}
+
+extern "C" int dRk_conv2d_f32(dRk_stream stream, const float *in, const float *wpack, const float *bias, float *out,
+                              int n, int W, int H, int Cin, int Cout, int kw, int kh, int sx, int sy, int act,
+                              int ldi, int ldo, int coff)
+{
+    if (n <= 0 || W <= 0 || H <= 0 || Cin <= 0 || Cout <= 0 || kw <= 0 || kh <= 0 || sx <= 0 || sy <= 0) return -1;
+    if (ldi < Cin || ldo < coff + Cout) return -3;
+    drk_ConvGeom g;
+    g.W = W; g.H = H; g.Cin = Cin; g.kw = kw; g.kh = kh; g.sx = sx; g.sy = sy;
+    g.Wo = W / sx; g.Ho = H / sy; g.px = kw / 2; g.py = kh / 2; g.ldi = ldi;
+    if (g.Wo <= 0 || g.Ho <= 0) return -1;
+    const long long M = (long long)n * g.Ho * g.Wo;
+    if (M > 0x7fffffffLL) return -2;
+    return drk_gemm_f32_launch(drk_stream(stream), in, wpack, bias, out, (int)M, Cout, kw * kh * Cin, 0, Cout, ldo, coff, act,
+                               1, 0, 0, 0, &g);
+}

@@ -1,0 +1,18 @@
+/* Internal interface of the FP32 GEMM core (k_gemm_f32.cu). */
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+
+/* geometry of an implicit-GEMM convolution: A row m = (image, oy, ox), column k = (ky, kx, c) */
+struct drk_ConvGeom {
+    int W, H, Cin, kw, kh, sx, sy, Wo, Ho, px, py, ldi;
+};
+
+/*
+ * C[z][m*ldc + coff + n] = act(bias[n] + sum_k A[z](m,k) * B[z][k*ldb + n]),  z < batch.
+ * geom == NULL: A is dense row-major with leading dimension lda; otherwise A is gathered
+ * from an N-HWC tensor.  sA/sB/sC are the per-z strides in floats.
+ */
+int drk_gemm_f32_launch(cudaStream_t st, const float *A, const float *B, const float *bias, float *C, int M, int N, int K,
+                        int lda, int ldb, int ldc, int coff, int act, int batch, size_t sA, size_t sB, size_t sC,
+                        const drk_ConvGeom *geom);

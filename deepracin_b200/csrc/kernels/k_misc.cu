@@ -1,0 +1,290 @@
+/*
+ * Memory-bound kernels of the CNN-layer path: interface-layout conversion, pooling,
+ * softmax, element-wise math, slice / crop-or-pad / concat placement.  All are HBM-bound
+ * streaming kernels over N-HWC activations with 128-bit accesses where alignment allows.
+ */
+#include "k_common.cuh"
+
+thread_local long g_dRk_launches = 0;
+extern "C" long dRk_launch_count(void) { return g_dRk_launches; }
+extern "C" void dRk_launch_count_reset(void) { g_dRk_launches = 0; }
+
+/* ------------------------------------------------------------------ layout
+ * Per image a [rows][cols] -> [cols][rows] transpose through a padded 32x32 shared tile;
+ * CHW->HWC is rows=C, cols=H*W, HWC->CHW the reverse. */
+__global__ void k_transpose(const float *__restrict__ src, float *__restrict__ dst, int rows, int cols)
+{
+    __shared__ float tile[32][33];
+    const size_t img = (size_t)blockIdx.z * rows * cols;
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        int r = r0 + j, c = c0 + threadIdx.x;
+        if (r < rows && c < cols) tile[j][threadIdx.x] = src[img + (size_t)r * cols + c];
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+        int c = c0 + j, r = r0 + threadIdx.x;
+        if (r < rows && c < cols) dst[img + (size_t)c * rows + r] = tile[threadIdx.x][j];
+    }
+}
+
+static int transpose_launch(dRk_stream s, const float *src, float *dst, int n, int rows, int cols)
+{
+    if (n <= 0 || rows <= 0 || cols <= 0) return -1;
+    dim3 block(32, 8), grid((cols + 31) / 32, (rows + 31) / 32, n);
+    if (grid.y > 65535u || grid.z > 65535u) return -2;
+    k_transpose<<<grid, block, 0, drk_stream(s)>>>(src, dst, rows, cols);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}
+
+extern "C" int dRk_chw_to_hwc(dRk_stream s, const float *src, float *dst, int n, int W, int H, int C)
+{
+    return transpose_launch(s, src, dst, n, C, W * H);
+}
+
+extern "C" int dRk_hwc_to_chw(dRk_stream s, const float *src, float *dst, int n, int W, int H, int C)
+{
+    return transpose_launch(s, src, dst, n, W * H, C);
+}
+
+/* ------------------------------------------------------------------ pooling
+ * One thread per output element group: VEC channels of one output pixel.  Reads outside the
+ * image in x/y contribute 0 (they take part in max and in the average's divisor). */
+template <int VEC>
+__global__ void k_pool(const float *__restrict__ in, float *__restrict__ out, int n, int W, int H, int C, int Wo, int Ho, int Co,
+                       int sx, int sy, int sz, int stx, int sty, int stz, int type, int ldi)
+{
+    const int cg = Co / VEC;
+    const size_t total = (size_t)n * Ho * Wo * cg;
+    const float inv = 1.0f / (float)(sx * sy * sz);
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        int g = (int)(i % cg);
+        size_t p = i / cg;
+        int x = (int)(p % Wo);
+        size_t q = p / Wo;
+        int y = (int)(q % Ho);
+        int b = (int)(q / Ho);
+        float res[VEC];
+#pragma unroll
+        for (int v = 0; v < VEC; v++) res[v] = type == 0 ? -FLT_MAX : 0.0f;
+        for (int dz = 0; dz < sz; dz++)
+            for (int dy = 0; dy < sy; dy++) {
+                const int iy = y * sty + dy;
+                for (int dx = 0; dx < sx; dx++) {
+                    const int ix = x * stx + dx;
+                    float val[VEC];
+                    if (ix < W && iy < H) {
+                        const float *src = in + (((size_t)b * H + iy) * W + ix) * ldi;
+                        if (VEC == 4) {
+                            float4 t = *reinterpret_cast<const float4 *>(src + g * 4);
+                            val[0] = t.x; val[1 % VEC] = t.y; val[2 % VEC] = t.z; val[3 % VEC] = t.w;
+                        } else {
+                            int iz = g * stz + dz;
+                            val[0] = iz < C ? src[iz] : 0.0f;
+                        }
+                    } else {
+#pragma unroll
+                        for (int v = 0; v < VEC; v++) val[v] = 0.0f;
+                    }
+#pragma unroll
+                    for (int v = 0; v < VEC; v++) res[v] = type == 0 ? fmaxf(res[v], val[v]) : res[v] + val[v];
+                }
+            }
+        if (type != 0) {
+#pragma unroll
+            for (int v = 0; v < VEC; v++) res[v] = res[v] * inv;
+        }
+        float *dst = out + p * Co + (size_t)g * VEC;
+        if (VEC == 4) *reinterpret_cast<float4 *>(dst) = make_float4(res[0], res[1 % VEC], res[2 % VEC], res[3 % VEC]);
+        else dst[0] = res[0];
+    }
+}
+
+extern "C" int dRk_pool(dRk_stream s, const float *in, float *out, int n, int W, int H, int C, int sx, int sy, int sz,
+                        int stx, int sty, int stz, int type, int ldi)
+{
+    if (n <= 0 || W <= 0 || H <= 0 || C <= 0 || sx <= 0 || sy <= 0 || sz <= 0 || stx <= 0 || sty <= 0 || stz <= 0) return -1;
+    const int Wo = (W + stx - 1) / stx, Ho = (H + sty - 1) / sty, Co = (C + stz - 1) / stz;
+    const bool vec = sz == 1 && stz == 1 && C % 4 == 0 && ldi % 4 == 0 && ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    const size_t total = (size_t)n * Ho * Wo * (vec ? Co / 4 : Co);
+    const unsigned blocks = drk_blocks(total, 256, 148u * 32u);
+    if (vec) k_pool<4><<<blocks, 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, Wo, Ho, Co, sx, sy, sz, stx, sty, stz, type, ldi);
+    else k_pool<1><<<blocks, 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, Wo, Ho, Co, sx, sy, sz, stx, sty, stz, type, ldi);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}
+
+/* ------------------------------------------------------------------ softmax
+ * One CTA per image: block-wide max, then sum of exp(x - max), then normalise.  Warp
+ * shuffles inside a warp, one shared-memory hop across warps. */
+__device__ __forceinline__ float block_reduce(float v, bool is_max, float *red)
+{
+    for (int o = 16; o > 0; o >>= 1) {
+        float t = __shfl_xor_sync(0xffffffffu, v, o);
+        v = is_max ? fmaxf(v, t) : v + t;
+    }
+    const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+    __syncthreads();
+    if (l == 0) red[w] = v;
+    __syncthreads();
+    v = l < nw ? red[l] : (is_max ? -FLT_MAX : 0.0f);
+    for (int o = 16; o > 0; o >>= 1) {
+        float t = __shfl_xor_sync(0xffffffffu, v, o);
+        v = is_max ? fmaxf(v, t) : v + t;
+    }
+    return v;
+}
+
+__global__ void k_softmax(const float *__restrict__ in, float *__restrict__ out, int len)
+{
+    __shared__ float red[32];
+    const float *x = in + (size_t)blockIdx.x * len;
+    float *y = out + (size_t)blockIdx.x * len;
+    float m = -FLT_MAX;
+    for (int i = threadIdx.x; i < len; i += blockDim.x) m = fmaxf(m, x[i]);
+    m = block_reduce(m, true, red);
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < len; i += blockDim.x) sum += expf(x[i] - m);
+    sum = block_reduce(sum, false, red);
+    const float inv = 1.0f / sum;
+    for (int i = threadIdx.x; i < len; i += blockDim.x) y[i] = expf(x[i] - m) * inv;
+}
+
+extern "C" int dRk_softmax(dRk_stream s, const float *in, float *out, int n, int len)
+{
+    if (n <= 0 || len <= 0) return -1;
+    k_softmax<<<n, len >= 4096 ? 1024 : 256, 0, drk_stream(s)>>>(in, out, len);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}
+
+/* ------------------------------------------------------------- element-wise */
+__device__ __forceinline__ float ew1(float v, int op, float s)
+{
+    switch (op) {
+    case 0: return v + s;
+    case 1: return v - s;
+    case 2: return v * s;
+    case 3: return v / s;
+    case 4: return logf(v);
+    case 5: return expf(v);
+    case 6: return sqrtf(v);
+    case 7: return s;
+    case 8: return powf(v, s);
+    }
+    return v;
+}
+
+__device__ __forceinline__ float ew2(float a, float b, int op)
+{
+    switch (op) {
+    case 0: return a + b;
+    case 1: return a - b;
+    case 2: return a * b;
+    case 3: return a / b;
+    case 4: return powf(a, b);
+    }
+    return a;
+}
+
+__global__ void k_elemwise1(const float *__restrict__ in, float *__restrict__ out, size_t len, int op, float s, int vec)
+{
+    const size_t stride = (size_t)gridDim.x * blockDim.x, t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t done = 0;
+    if (vec) {
+        const size_t n4 = len / 4;
+        for (size_t i = t0; i < n4; i += stride) {
+            float4 v = reinterpret_cast<const float4 *>(in)[i];
+            v.x = ew1(v.x, op, s); v.y = ew1(v.y, op, s); v.z = ew1(v.z, op, s); v.w = ew1(v.w, op, s);
+            reinterpret_cast<float4 *>(out)[i] = v;
+        }
+        done = n4 * 4;
+    }
+    for (size_t i = done + t0; i < len; i += stride) out[i] = ew1(in[i], op, s);
+}
+
+__global__ void k_elemwise2(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out, size_t len, int op, int vec)
+{
+    const size_t stride = (size_t)gridDim.x * blockDim.x, t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    size_t done = 0;
+    if (vec) {
+        const size_t n4 = len / 4;
+        for (size_t i = t0; i < n4; i += stride) {
+            float4 u = reinterpret_cast<const float4 *>(a)[i], w = reinterpret_cast<const float4 *>(b)[i];
+            u.x = ew2(u.x, w.x, op); u.y = ew2(u.y, w.y, op); u.z = ew2(u.z, w.z, op); u.w = ew2(u.w, w.w, op);
+            reinterpret_cast<float4 *>(out)[i] = u;
+        }
+        done = n4 * 4;
+    }
+    for (size_t i = done + t0; i < len; i += stride) out[i] = ew2(a[i], b[i], op);
+}
+
+extern "C" int dRk_elemwise1(dRk_stream s, const float *in, float *out, size_t len, int op, float scalar)
+{
+    if (len == 0 || op < 0 || op > 8) return -1;
+    const int vec = ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    k_elemwise1<<<drk_blocks(len / 4 + 1, 256, 148u * 16u), 256, 0, drk_stream(s)>>>(in, out, len, op, scalar, vec);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}
+
+extern "C" int dRk_elemwise2(dRk_stream s, const float *a, const float *b, float *out, size_t len, int op)
+{
+    if (len == 0 || op < 0 || op > 4) return -1;
+    const int vec = ((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    k_elemwise2<<<drk_blocks(len / 4 + 1, 256, 148u * 16u), 256, 0, drk_stream(s)>>>(a, b, out, len, op, vec);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}
+
+/* ------------------------------------------- slice / crop-or-pad / concat
+ * One generic strided-copy kernel: the destination box (w,h,c) at offset (dx,dy,dz) of a
+ * (DW,DH,DC) tensor takes source coordinates (x+ox, y+oy, z+oz) of a (W,H,C) tensor with
+ * pixel stride ldi; positions outside the source read 0. */
+__global__ void k_copy_box(const float *__restrict__ in, float *__restrict__ out, int n, int W, int H, int C, int ldi,
+                           int ox, int oy, int oz, int w, int h, int c, int DW, int DH, int DC, int dx, int dy, int dz)
+{
+    const size_t total = (size_t)n * h * w * c;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        int z = (int)(i % c);
+        size_t p = i / c;
+        int x = (int)(p % w);
+        size_t q = p / w;
+        int y = (int)(q % h);
+        int b = (int)(q / h);
+        int sx = x + ox, sy = y + oy, sz = z + oz;
+        float v = 0.0f;
+        if (sx >= 0 && sx < W && sy >= 0 && sy < H && sz >= 0 && sz < C) v = in[(((size_t)b * H + sy) * W + sx) * ldi + sz];
+        out[(((size_t)b * DH + y + dy) * DW + x + dx) * DC + z + dz] = v;
+    }
+}
+
+static int copy_box(dRk_stream s, const float *in, float *out, int n, int W, int H, int C, int ldi, int ox, int oy, int oz,
+                    int w, int h, int c, int DW, int DH, int DC, int dx, int dy, int dz)
+{
+    if (n <= 0 || w <= 0 || h <= 0 || c <= 0) return -1;
+    const size_t total = (size_t)n * h * w * c;
+    k_copy_box<<<drk_blocks(total, 256, 148u * 32u), 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, ldi, ox, oy, oz, w, h, c, DW, DH, DC, dx, dy, dz);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}
+
+extern "C" int dRk_slice(dRk_stream s, const float *in, float *out, int n, int W, int H, int C, int ox, int oy, int oz,
+                         int w, int h, int c, int ldi)
+{
+    if (ox < 0 || oy < 0 || oz < 0 || ox + w > W || oy + h > H || oz + c > C) return -3;
+    return copy_box(s, in, out, n, W, H, C, ldi, ox, oy, oz, w, h, c, w, h, c, 0, 0, 0);
+}
+
+extern "C" int dRk_croporpad(dRk_stream s, const float *in, float *out, int n, int W, int H, int C, int w, int h, int c, int ldi)
+{
+    return copy_box(s, in, out, n, W, H, C, ldi, 0, 0, 0, w, h, c, w, h, c, 0, 0, 0);
+}
+
+extern "C" int dRk_concat_place(dRk_stream s, const float *in, float *out, int n, int w, int h, int c, int dim, int off,
+                                int W, int H, int C, int ldi)
+{
+    if (dim < 0 || dim > 2) return -1;
+    return copy_box(s, in, out, n, w, h, c, ldi, 0, 0, 0, w, h, c, W, H, C, dim == 0 ? off : 0, dim == 1 ? off : 0, dim == 2 ? off : 0);
+}

@@ -1,0 +1,69 @@
+/*
+ * Additions of the CUDA build to the deepRacin API.  None of these has a counterpart in
+ * the reference: its tensors have no batch dimension (a batch is a host loop of
+ * dR_feedData + dR_apply, examples/vgg16/vgg_deployed.c:141-166), its kernel variant is
+ * fixed by filter shape (src/dR_nodes_conv2d.c:36-81) and it runs on one device.
+ */
+#ifndef DR_B200_H
+#define DR_B200_H
+#include "dR_types.h"
+#ifdef __cplusplus
+extern "C" {
+#endif
+enum dR_MathMode {
+    DR_MATH_FP32 = 0,   /* every contraction in FP32 FFMA (validation-grade, the default) */
+    DR_MATH_TF32 = 1    /* dense contractions on the tcgen05 tensor cores with TF32 inputs, FP32 accumulate */
+};
+enum dR_InterfaceLayout {
+    DR_LAYOUT_CHW = 0,  /* reference layout of feed/output buffers: [C][H][W] per image */
+    DR_LAYOUT_HWC = 1   /* [H][W][C] per image: no layout conversion on feed/fetch */
+};
+/* Images per dR_apply; feed and output buffers hold n tensors back to back.  Before dR_prepare. */
+gboolean dR_setBatchSize(dR_Graph *net, gint n);
+gboolean dR_setMathMode(dR_Graph *net, gint mode);
+gboolean dR_setInterfaceLayout(dR_Graph *net, gint layout);
+/* Force a kernel family for one convolution node (dR_ConvAlgo); DR_CONV_AUTO restores the rule. */
+gboolean dR_setConvAlgo(dR_Node *node, gint algo);
+/* Graph-wide override, and switch for timing the legal variants of every conv during dR_prepare. */
+gboolean dR_setGraphConvAlgo(dR_Graph *net, gint algo);
+gboolean dR_setAutotune(dR_Graph *net, gboolean on);
+gboolean dR_setFusion(dR_Graph *net, gboolean on);
+gboolean dR_setCudaGraph(dR_Graph *net, gboolean on);
+/* CUDA device ordinal used by dR_initCL. */
+gboolean dR_setDevice(dR_Graph *net, gint ordinal);
+/* Blocks until everything issued on the graph's stream has finished. */
+gboolean dR_synchronize(dR_Graph *net);
+/* dR_apply bracketed by events on the graph's own stream; returns milliseconds (<0 on failure). */
+gdouble dR_applyTimed(dR_Graph *net, gint iterations);
+/* Kernel family / arithmetic a prepared convolution node runs (dR_ConvAlgo, 0/1). */
+gint dR_getConvAlgo(dR_Node *node);
+gint dR_getConvTensor(dR_Node *node);
+/* Last per-node GPU time in ms (profilingGPU runs), and number of kernels one dR_apply launches. */
+gdouble dR_getNodeGpuMs(dR_Node *node);
+gint dR_getLaunchCount(dR_Graph *net);
+/* Non-zero if a kernel reported a device-side status (bounded wait ran out, ...) since the last call. */
+gint dR_getDeviceStatus(dR_Graph *net);
+/* Feed / fetch with pinned host memory and no implicit synchronisation. */
+gboolean dR_feedDataAsync(dR_Graph *net, dR_Node *feednode, gfloat *pinned, size_t numfloats);
+gboolean dR_fetchOutputAsync(dR_Graph *net, gint outputIndex, gfloat *pinned, size_t numfloats);
+void *dR_allocPinned(size_t bytes);
+void dR_freePinned(void *p);
+/* Planning without a device: dR_prepare runs scheduling, fusion planning, variant selection and the buffer
+ * planner with placeholder addresses and uploads nothing; dR_apply then refuses to run.  For host-side
+ * inspection and tests of the planner; never a compute path. */
+gboolean dR_setDryRun(dR_Graph *net, gboolean on);
+/* Introspection of a prepared graph: execution order, and where each node's activations live. */
+gint dR_getScheduleLength(dR_Graph *net);
+gint dR_getScheduledNodeId(dR_Graph *net, gint position);
+size_t dR_getNodeActAddress(dR_Node *node);
+gint dR_getNodeActFloats(dR_Node *node);
+gint dR_getNodeChannelStride(dR_Node *node);
+gint dR_getNodeChannelOffset(dR_Node *node);
+gint dR_getStreamBufferCount(dR_Graph *net);
+size_t dR_getScratchFloats(dR_Graph *net);
+/* Library identification: returns a static string naming the build (arch, kernels). */
+const char *dR_b200_version(void);
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,111 @@
+/*
+ * Operator-level C ABI of the CUDA kernels (sm_100a).  Plain pointers and sizes only;
+ * every pointer is a DEVICE pointer unless stated, `stream` is a cudaStream_t passed as
+ * void*.  Every function only enqueues work and returns 0 or a cudaError_t value
+ * (negative values: argument errors).  These are the entry points the graph nodes call;
+ * each replaces one OpenCL kernel + its host-side `*_compute` launcher of the reference.
+ *
+ * Activations are N-HWC: element (image b, row y, column x, channel c) of a W x H x C
+ * tensor lives at ((b*H + y)*W + x)*ld + c, ld >= C being the pixel stride in floats.
+ */
+#ifndef DR_KERNELS_H
+#define DR_KERNELS_H
+#include <stddef.h>
+#ifdef __cplusplus
+extern "C" {
+#endif
+typedef void *dRk_stream;
+
+/* Interface layout <-> internal layout.  The reference's buffers are [C][H][W]
+ * (include/deepRACIN.h:61); its Python layer transposes on the host
+ * (python/deepracin/__init__.py.in:458-462, 487-489). */
+int dRk_chw_to_hwc(dRk_stream stream, const float *src, float *dst, int n, int W, int H, int C);
+int dRk_hwc_to_chw(dRk_stream stream, const float *src, float *dst, int n, int W, int H, int C);
+
+/*
+ * Convolution, exact FP32 (FFMA) implicit GEMM over M = n*Ho*Wo pixels, N = Cout,
+ * K = kh*kw*Cin; fused bias and ReLU(clamp to [0,FLT_MAX]) / linear.  Any odd or even
+ * filter size and any stride; padding and anchoring as include/dR_nodes_conv2d.h:47-54.
+ * Replaces the generated direct kernel (src/dR_nodes_conv2d.c:481-773, launcher :364-420)
+ * and, for 1x1 filters, Kernels/dR_conv2d1x1.cl:4-53 (launcher :1605-1672).
+ *   wpack : [kh*kw*Cin][Cout], row k = (ky*kw + kx)*Cin + c
+ *   ldi   : pixel stride of `in`;  ldo/coff : pixel stride / channel offset of `out`
+ */
+int dRk_conv2d_f32(dRk_stream stream, const float *in, const float *wpack, const float *bias, float *out,
+                   int n, int W, int H, int Cin, int Cout, int kw, int kh, int sx, int sy, int act,
+                   int ldi, int ldo, int coff);
+
+/*
+ * Winograd F(2x2,3x3) convolution, exact FP32, as three launches: input transform
+ * V = B^T d B per 4x4 tile, 16 transform-domain GEMMs M_k = V_k U_k, inverse transform
+ * A^T M A + bias + activation.  Transform matrices are the reference's
+ * (Kernels/dR_winograd2.cl:55-251); U = G g G^T is computed on the host as in
+ * src/dR_nodes_conv2d.c:1162-1240 and passed as [16][Cin][Cout].
+ * scratch must hold dRk_winograd_scratch_floats() floats.
+ */
+size_t dRk_winograd_scratch_floats(int n, int W, int H, int Cin, int Cout);
+int dRk_conv2d_winograd_f32(dRk_stream stream, const float *in, const float *U, const float *bias, float *out,
+                            float *scratch, int n, int W, int H, int Cin, int Cout, int act, int ldi, int ldo, int coff);
+
+/*
+ * Fully connected layer out[b][o] = act(bias[o] + sum_k in[b][k] * w[k][o]); `in` is the
+ * N-HWC activation, whose flattening is exactly the (y,x,z) order the reference's kernel
+ * reads through mapToDepthMajor (Kernels/dR_fcl.cl:59-120, Kernels/dR_helper.cl:131-142).
+ * Weight-streaming split-K kernel for small batches (partials in `scratch`, reduced by a
+ * second launch like the reference's matrixVectorMultSecond), FFMA GEMM for large ones.
+ * Linear output is clamped to [-FLT_MAX, FLT_MAX], ReLU to [0, FLT_MAX].
+ */
+size_t dRk_fc_scratch_floats(int n, int Nin, int Nout);
+int dRk_fc_f32(dRk_stream stream, const float *in, const float *w, const float *bias, float *out, float *scratch,
+               int n, int Nin, int Nout, int act);
+
+/* Max / average pooling with the reference's window rule (src/dR_nodes_pooling.c:277-401,
+ * launcher :138-183): top-left anchored windows, zero reads outside, average over the full
+ * window.  type 0 = max, 1 = average.  Output is dense N-HWC of ceil(in/stride) per axis. */
+int dRk_pool(dRk_stream stream, const float *in, float *out, int n, int W, int H, int C, int sx, int sy, int sz,
+             int stx, int sty, int stz, int type, int ldi);
+
+/* Softmax over each image's whole tensor, one fused kernel: exp(x - max) / sum.  Equal to
+ * the reference's computeExp + host sum + mulScalar (src/dR_nodes_math.c:620-678) wherever
+ * that is finite. */
+int dRk_softmax(dRk_stream stream, const float *in, float *out, int n, int len);
+
+/* Element-wise ops; op codes of include/dR_nodes_math.h:10-16 and :82-92
+ * (Kernels/dR_math.cl:30-342). */
+int dRk_elemwise1(dRk_stream stream, const float *in, float *out, size_t len, int op, float scalar);
+int dRk_elemwise2(dRk_stream stream, const float *a, const float *b, float *out, size_t len, int op);
+
+/* Slice (Kernels/dR_transform.cl:5-25), CropOrPad (:32-48) and the placement of one Concat
+ * input at a running offset along dim 0=x / 1=y / 2=z (generated kernel,
+ * src/dR_nodes_transform.c:468-553).  Shapes are (W,H,C) of source and destination. */
+int dRk_slice(dRk_stream stream, const float *in, float *out, int n, int W, int H, int C, int ox, int oy, int oz,
+              int w, int h, int c, int ldi);
+int dRk_croporpad(dRk_stream stream, const float *in, float *out, int n, int W, int H, int C, int w, int h, int c, int ldi);
+int dRk_concat_place(dRk_stream stream, const float *in, float *out, int n, int w, int h, int c, int dim, int off,
+                     int W, int H, int C, int ldi);
+
+/*
+ * Tensor-core convolution / GEMM: tcgen05.mma kind::tf32 with FP32 accumulators in TMEM,
+ * operands staged by TMA (cp.async.bulk.tensor) into 128B-swizzled shared memory.
+ * The plan object owns the CUtensorMap descriptors for one layer shape + buffer set.
+ *   in   : N-HWC, Cin a multiple of 8 (dense, ldi == Cin)
+ *   wT   : [Cout][kh*kw*Cin]   (K contiguous), k = (ky*kw + kx)*Cin + c
+ * Returns NULL if the shape is not supported by the tensor path (caller falls back to FFMA).
+ * `status` is a device int the kernel writes a non-zero code to if a bounded wait runs out.
+ */
+typedef struct dRk_TensorConvPlan dRk_TensorConvPlan;
+/* 1 if the tensor path can evaluate this layer shape (stride 1, 1x1 or 3x3, channel counts it can tile). */
+int dRk_tensor_conv_supported(int W, int H, int Cin, int Cout, int kw, int kh);
+dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float *wT, const float *bias, float *out,
+                                         int n, int W, int H, int Cin, int Cout, int kw, int kh, int act,
+                                         int ldo, int coff, int *status);
+int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *plan);
+void dRk_tensor_conv_free(dRk_TensorConvPlan *plan);
+
+/* Number of kernel launches issued through this ABI by the calling thread since the last reset. */
+long dRk_launch_count(void);
+void dRk_launch_count_reset(void);
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,137 @@
+"""GPU parity tests on whole graphs: the reference's pretrained SqueezeNet (known answers 292 / 611),
+synthetic SqueezeNet and VGG-style graphs against the CPU oracle running the same saved model folder,
+batching, fusion and CUDA-graph replay equivalence, and size-independent properties at the
+benchmark's full layer sizes."""
+import os
+
+import numpy as np
+import pytest
+
+import cases
+import deepracin_b200 as dr
+import nets
+import oracle
+from gpu_helpers import TOL_FP32, conv_build, rel_err, run_graph
+from oracle import graph as ograph
+
+pytestmark = pytest.mark.gpu
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_kernels.npz"))
+
+
+def load_kat_images():
+    d = oracle.staged_squeezenet_dir()
+    return d, np.stack([np.fromfile(os.path.join(d, n + "_224x224x3_rgb_hwc.f32"), dtype=np.float32).reshape(224, 224, 3)
+                        for n in ("tiger", "puzzle")])
+
+
+@pytest.mark.skipif(oracle.staged_squeezenet_dir() is None, reason="pretrained SqueezeNet fixture not staged")
+@pytest.mark.parametrize("opts", [dict(), dict(fuse=False), dict(cuda_graph=True), dict(conv_algo="direct"), dict(autotune=True)])
+def test_pretrained_squeezenet_known_answers(opts):
+    d, imgs = load_kat_images()
+    with dr.Environment() as env:
+        g = env.create_graph("HWC")
+        g.batch = 2
+        for k, v in opts.items():
+            setattr(g, k, v)
+        nodes, feeds = dr.load_graph(g, d)
+        dr.mark_as_output(nodes[-1])
+        dr.mark_as_output(nodes[-2])
+        dr.prepare(g)
+        dr.feed_data(feeds[0], imgs)
+        probs, logits = dr.apply(g)
+        probs2, _ = dr.apply(g)
+    probs, logits = probs.reshape(2, 1000), logits.reshape(2, 1000)
+    assert [int(p.argmax()) for p in probs] == [292, 611]
+    assert np.array_equal(probs, probs2.reshape(2, 1000))
+    for i, name in enumerate(("tiger", "puzzle")):
+        assert rel_err(logits[i], GOLD["kat_%s_logits" % name]) <= TOL_FP32
+        assert rel_err(probs[i], GOLD["kat_%s_softmax" % name]) <= 5e-4
+
+
+def run_vs_oracle(build, feed_hwc, tmp_path, tol=TOL_FP32, **opts):
+    """Builds the net, saves it with dR_saveGraph, runs it on the GPU and runs the saved folder on the oracle."""
+    n = feed_hwc.shape[0]
+    with dr.Environment() as env:
+        g = env.create_graph("HWC")
+        g.batch = n
+        for k, v in opts.items():
+            setattr(g, k, v)
+        x, out = build(g)
+        dr.mark_as_output(out)
+        dr.save_graph(g, str(tmp_path))
+        dr.prepare(g)
+        dr.feed_data(x, feed_hwc)
+        (got,) = dr.apply(g)
+    onodes = ograph.parse_graph(str(tmp_path / "dr_graph_export"))
+    ref = ograph.run_graph(onodes, [np.ascontiguousarray(feed_hwc.transpose(0, 3, 1, 2))])
+    got = got.reshape(ref.shape) if got.size == ref.size and got.ndim != 4 else got
+    return got, ref
+
+
+def test_synthetic_squeezenet_matches_oracle(tmp_path):
+    imgs = nets.synthetic_images("sq_img", 2, 64)
+    got, ref = run_vs_oracle(lambda g: nets.squeezenet11(g, size=64, classes=40), imgs, tmp_path)
+    got = got.reshape(ref.shape)
+    assert np.all(np.isfinite(ref))
+    assert rel_err(got, ref) <= 5e-4
+    assert np.array_equal(got.reshape(2, -1).argmax(1), ref.reshape(2, -1).argmax(1))
+
+
+def test_small_vgg_matches_oracle(tmp_path):
+    imgs = nets.synthetic_images("vgg_img", 3, 32)
+    got, ref = run_vs_oracle(lambda g: nets.vgg16(g, size=32, width_div=8, fc_dims=(512, 512, 100)), imgs, tmp_path)
+    got = got.reshape(ref.shape)
+    assert np.all(np.isfinite(ref))
+    assert rel_err(got, ref) <= 5e-4
+    assert np.array_equal(got.reshape(3, -1).argmax(1), ref.reshape(3, -1).argmax(1))
+
+
+def test_small_vgg_logits_match_oracle_per_layer_bound(tmp_path):
+    imgs = nets.synthetic_images("vgg_img2", 2, 32)
+    got, ref = run_vs_oracle(lambda g: nets.vgg16(g, size=32, width_div=8, fc_dims=(512, 512, 100), softmax=False), imgs, tmp_path)
+    assert rel_err(got.reshape(ref.shape), ref) <= 3e-4     # 16 layers deep; each layer is within 1e-4
+
+
+def test_batch_equals_loop_over_images(tmp_path):
+    """A batch of n is n independent applications (the reference's own notion of a batch)."""
+    imgs = nets.synthetic_images("loop_img", 3, 32)
+
+    def run(batch_imgs):
+        with dr.Environment() as env:
+            g = env.create_graph("HWC")
+            g.batch = batch_imgs.shape[0]
+            x, out = nets.squeezenet11(g, size=32, classes=16)
+            dr.mark_as_output(out)
+            dr.prepare(g)
+            dr.feed_data(x, batch_imgs)
+            return dr.apply(g)[0].reshape(batch_imgs.shape[0], -1)
+    whole = run(imgs)
+    single = np.concatenate([run(imgs[i:i + 1]) for i in range(3)])
+    assert rel_err(whole, single) <= 1e-6
+
+
+def test_conv_sweep_layers_direct_vs_winograd_at_full_size():
+    """Benchmark conv-sweep shapes at batch 32: both FP32 kernel families agree, and the linear layer is
+    homogeneous (conv(2x) == 2 conv(x) exactly in binary floating point)."""
+    for cin, hw in ((64, 56), (128, 28), (256, 14)):
+        x, wt, b = cases.conv_case("sweep%d" % cin, 32, cin, cin, hw, hw, 3)
+        (d,) = run_graph(conv_build(wt, b, 1, 1, algo="direct"), [x])
+        (w,) = run_graph(conv_build(wt, b, 1, 1, algo="winograd"), [x])
+        assert rel_err(w, d) <= 2e-4
+        ref0 = oracle.conv2d(x[:1], wt, b, (1, 1), 1)
+        assert rel_err(d[:1], ref0) <= TOL_FP32
+        (lin1,) = run_graph(conv_build(wt, None, 1, 0, algo="direct"), [x[:4]])
+        (lin2,) = run_graph(conv_build(wt, None, 1, 0, algo="direct"), [2.0 * x[:4]])
+        assert np.array_equal(lin2, 2.0 * lin1)
+
+
+def test_vgg_fc_stack_at_full_size():
+    """FC 25088 -> 4096 at batch 1 and 8: weight-streaming kernel against the oracle."""
+    g = cases.rng("fc6")
+    w = (g.standard_normal((25088, 4096), dtype=np.float32) * np.float32(np.sqrt(2.0 / 25088)))
+    b = (g.standard_normal(4096, dtype=np.float32) * np.float32(0.1))
+    x = g.standard_normal((8, 512, 7, 7), dtype=np.float32)
+    ref = oracle.fc(x, w, b, 1)
+    for n in (1, 8):
+        (got,) = run_graph(lambda gr, f: dr.Fully_Connected(f[0], [25088, 4096], "relu", w, b), [x[:n]])
+        assert rel_err(got, ref[:n]) <= TOL_FP32

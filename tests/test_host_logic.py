@@ -1,0 +1,215 @@
+"""CPU tests of the host side: exported C ABI, graph construction, scheduling, the buffer planner
+(dry run, no device), fusion planning, the saved-graph format and API misuse."""
+import filecmp
+import glob
+import os
+import re
+
+import numpy as np
+import pytest
+
+import deepracin_b200 as dr
+import oracle
+from deepracin_b200._lib import Shape3, Shape4
+from ctypes import pointer
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+SLOTS = ["compute", "schedule", "propagateShape", "getRequiredOutputBufferSize", "createKernel", "allocateBuffers",
+         "fillBuffers", "cleanupBuffers", "cleanupLayer", "serializeNode", "parseAppendNode", "printLayer"]
+
+
+def declared_symbols():
+    names = set()
+    for path in glob.glob(os.path.join(ROOT, "include", "*.h")):
+        text = open(path).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        text = re.sub(r"#define[^\n]*(\\\n[^\n]*)*", "", text)
+        for m in re.finditer(r"DR_DECL_NODE_SLOTS\((\w+)\)", text):
+            names.update("%s_%s" % (m.group(1), s) for s in SLOTS)
+        for m in re.finditer(r"\b((?:dRk?|concat_and_free_old)\w*)\s*\(", text):
+            name = m.group(1)
+            before = text[max(0, m.start() - 2):m.start()]
+            if "(*" in text[max(0, m.start() - 3):m.start()] or before.endswith("*)"):
+                continue
+            names.add(name)
+    return sorted(n for n in names if not n.startswith("DR_"))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    missing = [n for n in declared_symbols() if not hasattr(dr.lib, n)]
+    assert len(declared_symbols()) > 150
+    assert missing == []
+
+
+def small_net(env, batch=1, fuse=True):
+    g = env.create_graph("HWC")
+    g.batch = batch
+    g.fuse = fuse
+    r = np.random.default_rng(0)
+    x = dr.feed_node(g, [16, 16, 3])
+    c1 = dr.Conv2d(x, [3, 3, 3, 8], [1, 1, 1, 1], "relu", r.standard_normal((3, 3, 3, 8)).astype(np.float32), np.zeros(8, np.float32))
+    p1 = dr.Pooling(c1, "max", [1, 3, 3, 1], [1, 2, 2, 1])
+    sq = dr.Conv2d(p1, [1, 1, 8, 4], [1, 1, 1, 1], "relu", r.standard_normal((1, 1, 8, 4)).astype(np.float32), np.zeros(4, np.float32))
+    e1 = dr.Conv2d(sq, [1, 1, 4, 8], [1, 1, 1, 1], "relu", r.standard_normal((1, 1, 4, 8)).astype(np.float32), np.zeros(8, np.float32))
+    e3 = dr.Conv2d(sq, [3, 3, 4, 8], [1, 1, 1, 1], "relu", r.standard_normal((3, 3, 4, 8)).astype(np.float32), np.zeros(8, np.float32))
+    cat = dr.Concat([e1, e3], 2)
+    gp = dr.Pooling(cat, "average", [1, 8, 8, 1], [1, 8, 8, 1])
+    fc = dr.Fully_Connected(gp, [16, 10], "linear", r.standard_normal((16, 10)).astype(np.float32), np.zeros(10, np.float32))
+    sm = dr.Softmax(fc)
+    dr.mark_as_output(sm)
+    return g, dict(x=x, c1=c1, p1=p1, sq=sq, e1=e1, e3=e3, cat=cat, gp=gp, fc=fc, sm=sm)
+
+
+def dry_prepare(g):
+    assert dr.lib.dR_setDryRun(g.ptr, 1)
+    dr.lib.dR_setBatchSize(g.ptr, g.batch)
+    dr.lib.dR_setFusion(g.ptr, 1 if g.fuse else 0)
+    assert dr.lib.dR_prepare(g.ptr)
+
+
+def shape_of(node):
+    s = dr.lib.dR_getOutputShape(node.ptr).contents
+    return (s.s0, s.s1, s.s2)
+
+
+def test_shapes_schedule_and_fusion_plan():
+    with dr.Environment() as env:
+        g, n = small_net(env)
+        dry_prepare(g)
+        assert shape_of(n["c1"]) == (16, 16, 8)
+        assert shape_of(n["p1"]) == (8, 8, 8)            # ceil(16/2)
+        assert shape_of(n["cat"]) == (8, 8, 16)
+        assert shape_of(n["gp"]) == (1, 1, 16)
+        assert shape_of(n["sm"]) == (10, 1, 1)
+        order = [dr.lib.dR_getScheduledNodeId(g.ptr, i) for i in range(dr.lib.dR_getScheduleLength(g.ptr))]
+        assert order == sorted(order) and len(order) == 9   # feed node is not scheduled
+        # both expand convolutions write straight into the Concat's buffer at their channel offsets
+        cat_addr = dr.lib.dR_getNodeActAddress(n["cat"].ptr)
+        assert dr.lib.dR_getNodeActAddress(n["e1"].ptr) == cat_addr
+        assert dr.lib.dR_getNodeActAddress(n["e3"].ptr) == cat_addr
+        assert (dr.lib.dR_getNodeChannelStride(n["e1"].ptr), dr.lib.dR_getNodeChannelOffset(n["e1"].ptr)) == (16, 0)
+        assert (dr.lib.dR_getNodeChannelStride(n["e3"].ptr), dr.lib.dR_getNodeChannelOffset(n["e3"].ptr)) == (16, 8)
+        assert not dr.lib.dR_apply(g.ptr)                   # a dry run can never compute
+
+
+def test_fusion_can_be_switched_off():
+    with dr.Environment() as env:
+        g, n = small_net(env, fuse=False)
+        dry_prepare(g)
+        addrs = {k: dr.lib.dR_getNodeActAddress(v.ptr) for k, v in n.items()}
+        assert addrs["e1"] != addrs["cat"] and addrs["e3"] != addrs["cat"]
+        assert dr.lib.dR_getNodeChannelStride(n["e1"].ptr) == 8
+
+
+@pytest.mark.parametrize("fuse", [True, False])
+def test_buffer_planner_never_aliases_live_tensors(fuse):
+    """Walk the schedule: a node's output buffer must differ from every buffer that is still to be read."""
+    with dr.Environment() as env:
+        g, n = small_net(env, batch=3, fuse=fuse)
+        dry_prepare(g)
+        names = ["c1", "p1", "sq", "e1", "e3", "cat", "gp", "fc", "sm"]
+        consumers = {"x": ["c1"], "c1": ["p1"], "p1": ["sq"], "sq": ["e1", "e3"], "e1": ["cat"], "e3": ["cat"], "cat": ["gp"],
+                     "gp": ["fc"], "fc": ["sm"], "sm": []}
+        addr = {k: dr.lib.dR_getNodeActAddress(v.ptr) for k, v in n.items()}
+        size = {k: dr.lib.dR_getNodeActFloats(v.ptr) for k, v in n.items()}
+        for k in names:
+            w, h, c = shape_of(n[k])
+            assert size[k] >= w * h * c
+        done = set()
+        for k in names:
+            live = [p for p in ["x"] + names if p != k and (p in done or p == "x") and any(q not in done for q in consumers[p])]
+            for p in live:
+                shared_concat = fuse and {k, p} <= {"e1", "e3", "cat"}
+                assert addr[k] != addr[p] or shared_concat, (k, p)
+            done.add(k)
+        assert dr.lib.dR_getStreamBufferCount(g.ptr) <= 8
+
+
+def test_save_load_roundtrip(tmp_path):
+    with dr.Environment() as env:
+        g, _ = small_net(env)
+        dr.save_graph(g, str(tmp_path / "a"))
+        g2 = env.create_graph("HWC")
+        nodes, feeds = dr.load_graph(g2, str(tmp_path / "a" / "dr_graph_export"))
+        assert len(nodes) == 10 and len(feeds) == 1
+        dr.save_graph(g2, str(tmp_path / "b"))
+        da, db = str(tmp_path / "a" / "dr_graph_export"), str(tmp_path / "b" / "dr_graph_export")
+        files = sorted(os.listdir(da))
+        assert files == sorted(os.listdir(db)) and "graph.dr" in files
+        match, mismatch, errors = filecmp.cmpfiles(da, db, files, shallow=False)
+        assert mismatch == [] and errors == []
+        text = open(os.path.join(da, "graph.dr")).read().split("\n")
+        assert text[0] == "deepRACIN graph: 10 nodes, 1 feed nodes"
+        assert text[1] == "Node 0: DataFeedNode" and text[2] == "params: 16 16 3"
+        assert text[6] == "Node 1: Conv2D" and text[7] == "params: 1 1 3 3 3 8 1 1 1 1"
+        assert text[10] == "variable_files: 0.var 1.var"
+
+
+@pytest.mark.skipif(oracle.staged_squeezenet_dir() is None, reason="pretrained SqueezeNet fixture not staged")
+def test_reference_model_folder_reloads_byte_identically(tmp_path):
+    """graph.dr written by the reference -> our reader -> our writer gives the same bytes."""
+    src = oracle.staged_squeezenet_dir()
+    with dr.Environment() as env:
+        g = env.create_graph("HWC")
+        nodes, feeds = dr.load_graph(g, src)
+        assert len(nodes) == 48 and len(feeds) == 1
+        dr.save_graph(g, str(tmp_path))
+        out = str(tmp_path / "dr_graph_export")
+        assert open(os.path.join(out, "graph.dr"), "rb").read() == open(os.path.join(src, "graph.dr"), "rb").read()
+        for i in range(52):
+            assert filecmp.cmp(os.path.join(out, "%d.var" % i), os.path.join(src, "%d.var" % i), shallow=False)
+        dry_prepare(g)
+        assert shape_of(nodes[47]) == (1, 1, 1000)
+        assert shape_of(nodes[8]) == (224, 224, 64) and shape_of(nodes[10]) == (56, 56, 64)
+
+
+def test_api_misuse_is_reported_not_fatal(tmp_path, capfd):
+    with dr.Environment() as env:
+        g = env.create_graph("HWC")
+        assert not dr.lib.dR_apply(g.ptr)                          # apply before prepare
+        assert dr.lib.dR_getOutputBuffers(g.ptr, None) == 0
+        dr.lib.dR_setDryRun(g.ptr, 1)
+        assert not dr.lib.dR_prepare(g.ptr)                        # no feed node
+        with pytest.raises(RuntimeError):
+            dr.load_graph(env.create_graph("HWC"), str(tmp_path))    # no graph.dr there
+        g3 = env.create_graph("HWC")
+        x = dr.feed_node(g3, [8, 8, 4])
+        w = np.zeros((3, 3, 5, 6), np.float32)
+        dr.Conv2d(x, [3, 3, 5, 6], [1, 1, 1, 1], "relu", w, None)   # filter expects 5 channels, input has 4
+        dr.lib.dR_setDryRun(g3.ptr, 1)
+        assert not dr.lib.dR_prepare(g3.ptr)
+        g4 = env.create_graph("HWC")
+        x = dr.feed_node(g4, [4, 4, 2])
+        dr.Fully_Connected(x, [30, 5], "relu", np.zeros((30, 5), np.float32), None)   # 4*4*2 != 30
+        dr.lib.dR_setDryRun(g4.ptr, 1)
+        assert not dr.lib.dR_prepare(g4.ptr)
+        g5 = env.create_graph("HWC")
+        x = dr.feed_node(g5, [4, 4, 2])
+        c = dr.Node(dr.lib.dR_Conv2d(g5.ptr, x.ptr, pointer(Shape4(3, 3, 2, 2)), pointer(Shape4(1, 1, 1, 1)), 1, 0), g5, "Conv2D", [])
+        dr.lib.dR_setDryRun(g5.ptr, 1)
+        assert not dr.lib.dR_prepare(g5.ptr)                       # weights never set
+        assert not dr.lib.dR_setBatchSize(g5.ptr, 0)
+    out = capfd.readouterr().out
+    assert "dR_prepare first" in out or "dR_prepare" in out
+
+
+def test_unsupported_constructors_return_null():
+    with dr.Environment() as env:
+        g = env.create_graph("HWC")
+        x = dr.feed_node(g, [4, 4, 3])
+        assert not dr.lib.dR_RGB2gray(g.ptr, x.ptr)
+        assert not dr.lib.dR_ResolveRoI(g.ptr, x.ptr, pointer(Shape3(2, 2, 3)))
+
+
+def test_truncated_model_files_fail_cleanly(tmp_path):
+    with dr.Environment() as env:
+        g, _ = small_net(env)
+        dr.save_graph(g, str(tmp_path))
+        d = str(tmp_path / "dr_graph_export")
+        os.remove(os.path.join(d, "1.var"))
+        with pytest.raises(RuntimeError):
+            dr.load_graph(env.create_graph("HWC"), d)
+        text = open(os.path.join(d, "graph.dr")).read()
+        open(os.path.join(d, "graph.dr"), "w").write(text[: len(text) // 2].rsplit("\n", 2)[0])
+        with pytest.raises(RuntimeError):
+            dr.load_graph(env.create_graph("HWC"), d)
