@@ -94,7 +94,7 @@ def fc(x, w, b, act=1):
     x, w, b = _c(x), _c(w), _c(b)
     n, c, h, wd = x.shape
     nout = w.shape[1]
-    out = np.empty((n, nout, 1, 1), np.float32)
+    out = np.empty((n, 1, 1, nout), np.float32)     # the reference's FC output shape is (W=Nout, H=1, C=1)
     restate_lib().dro_fc(_p(x), n, wd, h, c, _p(w), _p(b), nout, int(act), _p(out))
     return out
 
@@ -191,7 +191,7 @@ def ref_fc(x, w, b, act=1, lms=REF_LMS, mws=REF_MWS):
     x, w, b = _c(x), _c(w), _c(b)
     n, c, h, wd = x.shape
     nout = w.shape[1]
-    out = np.zeros((n, nout, 1, 1), np.float32)
+    out = np.zeros((n, 1, 1, nout), np.float32)
     r = ref_lib().drref_fc(_p(x), n, wd, h, c, _p(w), _p(b), nout, int(act), ctypes.c_long(lms), ctypes.c_long(mws), _p(out))
     if r < 0:
         raise RuntimeError("shape hits the reference FC kernels' partition-tail bug; not runnable")
