@@ -1,0 +1,79 @@
+"""GPU parity tests of the tensor-core (tcgen05, TF32) convolution path against the CPU oracle.
+Bound: max|err| <= 3e-3 * max|ref| per layer output, and equal softmax top-1 on whole networks."""
+import numpy as np
+import pytest
+
+import cases
+import deepracin_b200 as dr
+import nets
+import oracle
+from gpu_helpers import TOL_TF32, conv_build, rel_err, run_graph
+
+pytestmark = pytest.mark.gpu
+
+TENSOR_SHAPES = [
+    # name, n, cin, cout, h, w, k
+    ("t_64_56", 2, 64, 64, 56, 56, 3),
+    ("t_64_224", 1, 64, 64, 224, 224, 3),
+    ("t_128_112", 1, 64, 128, 112, 112, 3),
+    ("t_256_28", 3, 128, 256, 28, 28, 3),
+    ("t_512_14", 5, 256, 512, 14, 14, 3),
+    ("t_odd_30x20", 2, 32, 64, 20, 30, 3),
+    ("t_odd_13x17", 3, 64, 192, 17, 13, 3),
+    ("t_1x1_256_512", 2, 256, 512, 28, 28, 1),
+    ("t_1x1_odd", 3, 32, 64, 9, 7, 1),
+]
+
+
+@pytest.mark.parametrize("name,n,cin,cout,h,w,k", TENSOR_SHAPES)
+@pytest.mark.parametrize("act,bias", [(1, True), (0, False)])
+def test_tensor_conv_matches_oracle(name, n, cin, cout, h, w, k, act, bias):
+    x, wt, b = cases.conv_case(name, n, cin, cout, h, w, k, bias)
+    ref = oracle.conv2d(x, wt, b, (1, 1), act)
+    with dr.Environment() as env:
+        g = env.create_graph("CHW")
+        g.batch = n
+        g.math = "tf32"
+        f = dr.feed_node(g, [cin, h, w])
+        o = conv_build(wt, b, 1, act)(g, [f])
+        dr.mark_as_output(o)
+        dr.prepare(g)
+        assert dr.lib.dR_getConvAlgo(o.ptr) == 4 and dr.lib.dR_getConvTensor(o.ptr) == 1
+        dr.feed_data(f, x)
+        got = dr.apply(g)[0].reshape(ref.shape)
+        assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    assert rel_err(got, ref) <= TOL_TF32
+
+
+def test_tensor_path_falls_back_where_it_cannot_tile():
+    """3 input channels (first VGG layer), 5x5 filters and strided layers stay on the FP32 kernels."""
+    with dr.Environment() as env:
+        g = env.create_graph("CHW")
+        g.math = "tf32"
+        f = dr.feed_node(g, [3, 16, 16])
+        z = np.zeros
+        a = dr.Conv2d(f, [3, 3, 3, 64], [1, 1, 1, 1], "relu", z((3, 3, 3, 64), np.float32), None)
+        b = dr.Conv2d(a, [3, 3, 64, 64], [1, 1, 1, 1], "relu", z((3, 3, 64, 64), np.float32), None)
+        c = dr.Conv2d(b, [5, 5, 64, 64], [1, 1, 1, 1], "relu", z((5, 5, 64, 64), np.float32), None)
+        d = dr.Conv2d(c, [3, 3, 64, 64], [1, 2, 2, 1], "relu", z((3, 3, 64, 64), np.float32), None)
+        dr.mark_as_output(d)
+        dr.prepare(g)
+        assert [dr.lib.dR_getConvAlgo(n.ptr) for n in (a, b, c, d)] == [2, 4, 1, 1]
+
+
+def test_tf32_network_agrees_with_fp32_on_top1():
+    imgs = nets.synthetic_images("tf32_net", 4, 64)
+    outs = {}
+    for math in ("fp32", "tf32"):
+        with dr.Environment() as env:
+            g = env.create_graph("HWC")
+            g.batch = 4
+            g.math = math
+            x, out = nets.vgg16(g, size=64, width_div=2, fc_dims=(1024, 1024, 200))
+            dr.mark_as_output(out)
+            dr.prepare(g)
+            dr.feed_data(x, imgs)
+            outs[math] = dr.apply(g)[0].reshape(4, -1)
+            assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    assert np.array_equal(outs["fp32"].argmax(1), outs["tf32"].argmax(1))
+    assert rel_err(outs["tf32"], outs["fp32"]) <= 2e-2     # probabilities after 16 TF32 layers
