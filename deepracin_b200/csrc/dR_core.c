@@ -214,6 +214,10 @@ gboolean dR_propagateShapesAndSchedule(dR_Graph *net)
  */
 gboolean dR_planFusion(dR_Graph *net)
 {
+    for (dR_ListElement *e = net->feed_layers->first; e; e = e->next) {
+        dR_Node *f = (dR_Node *)e->element;
+        f->elided = FALSE; f->act_coffset = 0; f->act_cstride = f->oshape.s2;
+    }
     for (dR_ListElement *e = net->scheduledLayers->first; e; e = e->next) {
         dR_Node *l = (dR_Node *)e->element;
         l->elided = FALSE; l->act_coffset = 0; l->act_cstride = l->oshape.s2;
