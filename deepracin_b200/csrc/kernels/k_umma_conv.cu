@@ -26,6 +26,7 @@
  */
 #include <cuda.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 #include "k_common.cuh"
 
@@ -44,6 +45,7 @@ struct UmmaParams {
     long long total_sub;            /* n * tiles_x * tiles_y (3x3) or pixel count (1x1) */
     int m_tiles, n_tiles;
     int kslabs;                     /* Cin / 32 */
+    int stage_tx;                   /* bytes one stage receives: A boxes + B box */
     const float *bias;
     float *out;
     int ldo, coff, act;
@@ -209,7 +211,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                     for (int ks = 0; ks < p.kslabs; ks++) {
                         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
                         const uint32_t sa = base + stage * C::STAGE_BYTES, sb = sa + A_STAGE_BYTES;
-                        mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
+                        mbar_expect_tx(full_bar(stage), (uint32_t)p.stage_tx);
                         if (p.S == 0) {
                             tma_load_2d(sa, &mapA, ks * BK, mt * BM, full_bar(stage));
                         } else {
@@ -360,21 +362,34 @@ struct dRk_TensorConvPlan {
     int grid;
 };
 
-/* sub-box geometry of a 128-pixel tile for a W x H image: S boxes of TW x TH, TW*TH a multiple of 8 */
+/*
+ * Sub-box geometry of a CTA's pixel tile for a W x H image: S boxes of TW x TH pixels, TW*TH a multiple
+ * of 8 (each box must start on a swizzle-atom boundary), S*TW*TH <= 128.  When the boxes do not fill
+ * all 128 rows the remaining rows of the MMA tile are never loaded nor stored (idle tensor-pipe rows);
+ * that is cheaper than covering a 28- or 14-pixel-wide image with many 4-pixel-wide boxes, whose short
+ * contiguous runs make the TMA loads slow.
+ */
 static void pick_subtile(int W, int H, int *TW, int *TH, int *S)
 {
     double best = 1e30;
-    for (int s = 1; s <= 8; s *= 2)
-        for (int tw = 32; tw >= 1; tw /= 2) {
-            const int sub = BM / s;
-            if (sub % tw) continue;
-            const int th = sub / tw;
-            if ((tw * th) % 8) continue;
-            if (th > 256) continue;
-            const double cover = (double)((W + tw - 1) / tw * tw) * ((H + th - 1) / th * th) / ((double)W * H);
-            const double cost = cover * (1.0 + 0.01 * s);       /* prefer fewer boxes among equal coverage */
-            if (cost < best) { best = cost; *TW = tw; *TH = th; *S = s; }
+    int widths[8] = {32, 16, 8, 4, 2, 1, 0, 0};
+    int nw = 6;
+    if (W <= 128 && W != 32 && W != 16 && W != 8 && W != 4) widths[nw++] = W;
+    for (int wi = 0; wi < nw; wi++) {
+        const int tw = widths[wi];
+        for (int th = 1; th <= BM; th++) {
+            const int rows = tw * th;
+            if (rows > BM) break;
+            if (rows % 8) continue;
+            for (int s = 1; s * rows <= BM && s <= 8; s++) {
+                const double cover = (double)((W + tw - 1) / tw * tw) * ((H + th - 1) / th * th) / ((double)W * H);
+                const double idle = (double)BM / (s * rows);
+                double cost = cover * idle * (1.0 + 0.3 * (s - 1));   /* every extra box is one more TMA instruction per stage: measured 27% slower with two */
+                if (rows < 32) cost *= 2.0;                   /* tiny boxes: the fixed cost dominates */
+                if (cost < best) { best = cost; *TW = tw; *TH = th; *S = s; }
+            }
         }
+    }
 }
 
 extern "C" int dRk_tensor_conv_supported(int W, int H, int Cin, int Cout, int kw, int kh)
@@ -448,6 +463,10 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else {
         pick_subtile(W, H, &p.TW, &p.TH, &p.S);
+        if (const char *ov = getenv("DRK_TILE")) {          /* experiment hook: "tw,th,s" */
+            int a = 0, b = 0, c = 0;
+            if (sscanf(ov, "%d,%d,%d", &a, &b, &c) == 3 && a > 0 && b > 0 && c > 0 && (a * b) % 8 == 0 && a * b * c <= BM) { p.TW = a; p.TH = b; p.S = c; }
+        }
         p.tiles_x = (W + p.TW - 1) / p.TW;
         p.tiles_y = (H + p.TH - 1) / p.TH;
         p.total_sub = (long long)n * p.tiles_x * p.tiles_y;
@@ -471,6 +490,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }
     if (r != CUDA_SUCCESS) { fprintf(stderr, "tensor conv plan: filter tensor map rejected (%d)\n", (int)r); free(pl); return NULL; }
+    p.stage_tx = (p.S == 0 ? A_STAGE_BYTES : p.S * p.TW * p.TH * BK * 4) + pl->BN * BK * 4;
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
     pl->grid = (int)(tiles < sms ? tiles : sms);
     return pl;

@@ -1,0 +1,123 @@
+"""Single-layer microbenchmarks through the C API of libdeepracin.so (one node per graph).
+
+  python deepracin_b200/layer_bench.py conv CIN COUT HW BATCH [--k 3] [--math tf32|fp32] [--algo auto|direct|winograd|1x1|tensor]
+  python deepracin_b200/layer_bench.py fc NIN NOUT BATCH [--math ...]
+  python deepracin_b200/layer_bench.py sweep           # the conv-sweep and 1x1/FC configurations of the benchmark spec
+
+Times `--iters` launches with CUDA events on the library's stream after `--warmup` launches and prints
+one JSON line per layer: ms, direct-convolution TFLOP/s (Winograd gets no discount), minimum HBM
+bytes (input + output + weights once) and the GB/s they imply.  Inputs N(0,1), He-normal weights,
+small biases, ReLU.  Meant to be run under `ncu -k regex:...` for kernel-level profiles as well.
+"""
+import argparse
+import json
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import deepracin_b200 as dr  # noqa: E402
+
+
+def _rng(name):
+    import zlib
+    return np.random.Generator(np.random.PCG64(zlib.crc32(name.encode())))
+
+
+def time_graph(g, iters, warmup):
+    lib = dr.lib
+    for _ in range(warmup):
+        lib.dR_apply(g.ptr)
+    lib.dR_synchronize(g.ptr)
+    lib.dR_timerStart(g.ptr)
+    for _ in range(iters):
+        lib.dR_apply(g.ptr)
+    return lib.dR_timerStopMs(g.ptr) / iters
+
+
+def conv_layer(cin, cout, hw, batch, k=3, math="tf32", algo="auto", iters=20, warmup=5, act="relu"):
+    r = _rng("lb_conv_%d_%d_%d_%d" % (cin, cout, hw, k))
+    w = (r.standard_normal((k, k, cin, cout), dtype=np.float32) * np.float32(np.sqrt(2.0 / (k * k * cin))))
+    b = (r.standard_normal(cout, dtype=np.float32) * np.float32(0.1))
+    x = r.standard_normal((batch, hw, hw, cin), dtype=np.float32)
+    with dr.Environment() as env:
+        g = env.create_graph("HWC")
+        g.batch = batch
+        g.math = math
+        f = dr.feed_node(g, [hw, hw, cin])
+        o = dr.Conv2d(f, [k, k, cin, cout], [1, 1, 1, 1], act, w, b, algo=None if algo == "auto" else algo)
+        dr.mark_as_output(o)
+        dr.lib.dR_setInterfaceLayout(g.ptr, 1)
+        dr.prepare(g)
+        dr.feed_data(f, x)
+        ms = time_graph(g, iters, warmup)
+        chosen = dr.lib.dR_getConvAlgo(o.ptr)
+        status = dr.lib.dR_getDeviceStatus(g.ptr)
+    flops = 2.0 * k * k * cin * cout * hw * hw * batch
+    bytes_min = 4.0 * (batch * hw * hw * (cin + cout) + k * k * cin * cout)
+    return {"layer": "conv%dx%d %d->%d @%dx%d batch %d" % (k, k, cin, cout, hw, hw, batch), "math": math,
+            "algo": ["auto", "direct", "winograd", "1x1", "tensor"][chosen], "ms": ms, "tflops": flops / ms / 1e9,
+            "min_bytes": bytes_min, "gbs_at_min_bytes": bytes_min / ms / 1e6, "flop_per_byte": flops / bytes_min, "device_status": status}
+
+
+def fc_layer(nin, nout, batch, math="fp32", iters=20, warmup=5):
+    r = _rng("lb_fc_%d_%d" % (nin, nout))
+    w = (r.standard_normal((nin, nout), dtype=np.float32) * np.float32(np.sqrt(2.0 / nin)))
+    b = (r.standard_normal(nout, dtype=np.float32) * np.float32(0.1))
+    x = r.standard_normal((batch, 1, 1, nin), dtype=np.float32)
+    with dr.Environment() as env:
+        g = env.create_graph("HWC")
+        g.batch = batch
+        g.math = math
+        f = dr.feed_node(g, [1, 1, nin])
+        o = dr.Fully_Connected(f, [nin, nout], "relu", w, b)
+        dr.mark_as_output(o)
+        dr.prepare(g)
+        dr.feed_data(f, x)
+        ms = time_graph(g, iters, warmup)
+    flops = 2.0 * nin * nout * batch
+    bytes_min = 4.0 * (nin * nout + batch * (nin + nout))
+    return {"layer": "fc %d->%d batch %d" % (nin, nout, batch), "math": math, "ms": ms, "tflops": flops / ms / 1e9,
+            "min_bytes": bytes_min, "gbs_at_min_bytes": bytes_min / ms / 1e6, "flop_per_byte": flops / bytes_min}
+
+
+def sweep(iters, warmup):
+    out = []
+    for cin, hw in ((64, 56), (128, 28), (256, 14)):
+        for math, algo in (("fp32", "direct"), ("fp32", "winograd"), ("tf32", "auto")):
+            out.append(conv_layer(cin, cin, hw, 32, 3, math, algo, iters, warmup))
+    for math in ("fp32", "tf32"):
+        out.append(conv_layer(256, 512, 28, 64, 1, math, "auto", iters, warmup))
+    for batch in (1, 8, 64):
+        for nin, nout in ((25088, 4096), (4096, 4096), (4096, 1000)):
+            out.append(fc_layer(nin, nout, batch, "fp32", iters, warmup))
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("what", choices=["conv", "fc", "sweep"])
+    ap.add_argument("dims", nargs="*", type=int)
+    ap.add_argument("--k", type=int, default=3)
+    ap.add_argument("--math", default="tf32")
+    ap.add_argument("--algo", default="auto")
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    a = ap.parse_args()
+    if a.what == "conv":
+        cin, cout, hw, batch = a.dims
+        res = [conv_layer(cin, cout, hw, batch, a.k, a.math, a.algo, a.iters, a.warmup)]
+    elif a.what == "fc":
+        nin, nout, batch = a.dims
+        res = [fc_layer(nin, nout, batch, a.math, a.iters, a.warmup)]
+    else:
+        res = sweep(a.iters, a.warmup)
+    for r in res:
+        print(json.dumps(r))
+
+
+if __name__ == "__main__":
+    main()
