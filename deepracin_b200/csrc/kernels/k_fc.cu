@@ -10,6 +10,7 @@
  * applies the activation -- the same two-step shape as the reference's
  * matrixVectorMultFirst / matrixVectorMultSecond (Kernels/dR_fcl.cl:59-120).
  */
+#include <stdio.h>
 #include "k_common.cuh"
 #include "k_gemm_f32.cuh"
 
@@ -160,4 +161,53 @@ extern "C" int dRk_fc_f32(dRk_stream stream, const float *in, const float *w, co
     k_fc_reduce<<<(total + 255) / 256, 256, 0, st>>>(scratch, bias, out, total, Nout, splits, act);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
+}
+
+/*
+ * Fully connected layer for callers that must not allocate.
+ *
+ * Some embedders of this library are not allowed to create device memory once they are running:
+ * control loops with a memory budget that is frozen after start-up, and plug-in hosts that own
+ * every device allocation themselves and only lend the library a stream plus input/output
+ * pointers.  They cannot give dRk_fc_f32 the split-K scratch it needs, so this entry point brings
+ * its own: a fixed array that is part of the library image (DRK_FC_STATIC_SCRATCH_FLOATS floats,
+ * 8 MiB, resident on every GPU that loads the library until the process exits).
+ *
+ * The first call on each device looks the array's device address up (once, with that device
+ * current) and remembers it; make that first call before starting any stream capture.  After that
+ * a call only enqueues the same two kernels as dRk_fc_f32 -- no cudaMalloc, cudaFree or any other
+ * allocating routine.  Shapes whose partial sums do not fit the array are refused with -4 and a
+ * message naming the limit.  All calls on a device share the array: it keeps whatever the last
+ * call left in it (every element a call reads was written by that same call first, so nothing has
+ * to be cleared), and two calls that may overlap on the GPU (different streams) would race on it.
+ */
+#define DRK_FC_STATIC_SCRATCH_FLOATS (2u << 20)
+static __device__ __align__(256) float g_fc_static_scratch[DRK_FC_STATIC_SCRATCH_FLOATS];
+static float *g_fc_static_scratch_addr[64];     /* device address per device ordinal, filled on first use */
+
+extern "C" int dRk_fc_f32_noalloc(dRk_stream stream, const float *in, const float *w, const float *bias, float *out,
+                                  int n, int Nin, int Nout, int act)
+{
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= 64) return -1;
+    if (!g_fc_static_scratch_addr[dev]) {
+        /* in host code the array's name is only a handle; the kernels need its device address */
+        float *addr = NULL;
+        e = cudaGetSymbolAddress((void **)&addr, g_fc_static_scratch);
+        if (e != cudaSuccess || !addr) {
+            fprintf(stderr, "dRk_fc_f32_noalloc: cannot resolve the built-in scratch array on device %d: %s\n", dev, cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : -1;
+        }
+        g_fc_static_scratch_addr[dev] = addr;
+    }
+    const size_t need = dRk_fc_scratch_floats(n, Nin, Nout);
+    if (need == 0) return -1;
+    if (need > DRK_FC_STATIC_SCRATCH_FLOATS) {
+        fprintf(stderr, "dRk_fc_f32_noalloc: batch %d x %d -> %d needs %zu scratch floats, the built-in array holds %u; "
+                        "use dRk_fc_f32 with caller-provided scratch\n", n, Nin, Nout, need, DRK_FC_STATIC_SCRATCH_FLOATS);
+        return -4;
+    }
+    return dRk_fc_f32(stream, in, w, bias, out, g_fc_static_scratch_addr[dev], n, Nin, Nout, act);
 }

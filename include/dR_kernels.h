@@ -59,6 +59,17 @@ size_t dRk_fc_scratch_floats(int n, int Nin, int Nout);
 int dRk_fc_f32(dRk_stream stream, const float *in, const float *w, const float *bias, float *out, float *scratch,
                int n, int Nin, int Nout, int act);
 
+/*
+ * dRk_fc_f32 for callers that must not allocate device memory while running (embedders with a memory
+ * budget frozen after start-up, plug-in hosts that own every device allocation).  No counterpart in the
+ * reference.  The split-K scratch is a fixed 8 MiB array inside the library (2 Mi floats, resident on
+ * every GPU that loads the library); shapes needing more (dRk_fc_scratch_floats) are refused with -4.
+ * The first call on a device resolves the array's address -- make it before any stream capture; calls
+ * share the array, so calls that may overlap on the GPU race.  Allocates nothing.
+ */
+int dRk_fc_f32_noalloc(dRk_stream stream, const float *in, const float *w, const float *bias, float *out,
+                       int n, int Nin, int Nout, int act);
+
 /* Max / average pooling with the reference's window rule (src/dR_nodes_pooling.c:277-401,
  * launcher :138-183): top-left anchored windows, zero reads outside, average over the full
  * window.  type 0 = max, 1 = average.  Output is dense N-HWC of ceil(in/stride) per axis. */
