@@ -10,10 +10,12 @@
 #include "dR_b200.h"
 #include "dR_core.h"
 #include "dR_kernels.h"
+#include "dR_nodes_pooling.h"
 
 typedef struct {
     cl_mem wbuf[5];                 /* packed weights per dR_ConvAlgo */
     dRk_TensorConvPlan *plan;       /* tensor path: TMA descriptors for this layer's buffers */
+    gboolean fusedPool;             /* the following 2x2/2 max pooling is evaluated in this node's epilogue */
 } dR_ConvDevice;
 
 static dR_ConvDevice *dev(dR_Conv2d_Data *c) { return (dR_ConvDevice *)c->tmaDescs; }
@@ -174,6 +176,8 @@ static gint staticRule(dR_Graph *net, dR_Node *layer)
 {
     dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
     if (net->config->mathMode == DR_MATH_TF32 && tensorLegal(layer)) return DR_CONV_TENSOR;
+    /* a handful of input channels (RGB first layer): bound by writing the output, a direct kernel wins */
+    if (is3x3s1(c) && c->shape.s2 <= 4) return DR_CONV_DIRECT;
     if (is3x3s1(c)) return DR_CONV_WINOGRAD;
     if (is1x1s1(c)) return DR_CONV_ONEBYONE;
     return DR_CONV_DIRECT;
@@ -195,6 +199,24 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
     }
     c->chosenAlgo = want != DR_CONV_AUTO ? want : staticRule(net, layer);
     c->chosenTensor = c->chosenAlgo == DR_CONV_TENSOR;
+    /* conv -> 2x2/2 max pool with no other reader: the tensor kernel's epilogue stores the pooled tensor
+       directly into the pooling node's buffer and the pooling node launches nothing */
+    dev(c)->fusedPool = FALSE;
+    if (c->chosenTensor && net->config->fuseGraph && is3x3s1(c) && !layer->output && !layer->elided && layer->next_layers->length == 1 &&
+        layer->oshape.s0 % 2 == 0 && layer->oshape.s1 % 2 == 0) {
+        dR_Node *nx = (dR_Node *)layer->next_layers->first->element;
+        if (nx->type == tPooling && nx->previous_layers->length == 1) {
+            dR_Pooling_Data *pl = (dR_Pooling_Data *)nx->layer;
+            if (pl->poolingType == tMax && pl->shape.s1 == 2 && pl->shape.s2 == 2 && pl->shape.s3 == 1 &&
+                pl->stride.s1 == 2 && pl->stride.s2 == 2 && pl->stride.s3 == 1) {
+                dev(c)->fusedPool = TRUE;
+                pl->useLMEM = TRUE;                 /* marks "computed by the producer" for dR_pooling_compute */
+                layer->elided = TRUE;
+                layer->act_cstride = layer->oshape.s2;
+                layer->act_coffset = 0;
+            }
+        }
+    }
     /* scratch for every variant the autotuner may try */
     layer->scratchFloats = 0;
     if (c->chosenAlgo == DR_CONV_WINOGRAD || (net->config->autotune && is3x3s1(c)))
@@ -286,7 +308,7 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
     case DR_CONV_TENSOR:
         if (!d->plan) {
             d->plan = dRk_tensor_conv_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR], bias, dst, n, W, H, c->shape.s2, c->shape.s3,
-                                           c->shape.s0, c->shape.s1, act, layer->act_cstride, layer->act_coffset, (int *)net->statusWord);
+                                           c->shape.s0, c->shape.s1, act, layer->act_cstride, layer->act_coffset, d->fusedPool ? 1 : 0, (int *)net->statusWord);
             if (!d->plan) { g_print("Conv2d Layer %d: tensor-core plan could not be built\n", layer->layerID); return FALSE; }
         }
         net->clConfig->clError = dRk_tensor_conv_run(s, d->plan);
@@ -319,6 +341,7 @@ gboolean dR_conv2d_autotune(dR_Graph *net)
         if (layer->type != tConv2d) continue;
         dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
         if (c->algo != DR_CONV_AUTO || net->config->convAlgo != DR_CONV_AUTO) continue;
+        if (dev(c)->fusedPool) continue;            /* only the tensor kernel can store the pooled tensor */
         gint best = c->chosenAlgo;
         gdouble bestMs = 1e30;
         for (gint algo = DR_CONV_DIRECT; algo <= DR_CONV_TENSOR; algo++) {

@@ -105,6 +105,7 @@ gboolean dR_pooling_compute(dR_Graph *net, dR_Node *layer)
 {
     dR_Pooling_Data *p = (dR_Pooling_Data *)layer->layer;
     dR_Node *in = dR_firstInput(layer);
+    if (p->useLMEM) return TRUE;        /* the producing convolution already stored the pooled tensor here */
     dR_beginCLKernel(net);
     net->clConfig->clError = dRk_pool(net->clConfig->clCommandQueue, dR_actPtr(in) + in->act_coffset, dR_actPtr(layer), net->config->batchSize,
                                       p->ishape.s0, p->ishape.s1, p->ishape.s2, p->shape.s1, p->shape.s2, p->shape.s3,

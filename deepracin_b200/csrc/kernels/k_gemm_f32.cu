@@ -251,6 +251,10 @@ extern "C" int dRk_conv2d_f32(dRk_stream stream, const float *in, const float *w
 {
     if (n <= 0 || W <= 0 || H <= 0 || Cin <= 0 || Cout <= 0 || kw <= 0 || kh <= 0 || sx <= 0 || sy <= 0) return -1;
     if (ldi < Cin || ldo < coff + Cout) return -3;
+    if (kw == 3 && kh == 3 && sx == 1 && sy == 1) {        /* output-bound layers with a handful of input channels */
+        int rc = 0;
+        if (drk_conv3x3_smallcin_launch(drk_stream(stream), in, wpack, bias, out, n, W, H, Cin, Cout, act, ldi, ldo, coff, &rc)) return rc;
+    }
     drk_ConvGeom g;
     g.W = W; g.H = H; g.Cin = Cin; g.kw = kw; g.kh = kh; g.sx = sx; g.sy = sy;
     g.Wo = W / sx; g.Ho = H / sy; g.px = kw / 2; g.py = kh / 2; g.ldi = ldi;

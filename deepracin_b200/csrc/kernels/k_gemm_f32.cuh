@@ -16,3 +16,7 @@ struct drk_ConvGeom {
 int drk_gemm_f32_launch(cudaStream_t st, const float *A, const float *B, const float *bias, float *C, int M, int N, int K,
                         int lda, int ldb, int ldc, int coff, int act, int batch, size_t sA, size_t sB, size_t sC,
                         const drk_ConvGeom *geom);
+
+/* 3x3 stride-1 convolution specialised for Cin <= 4 (k_conv_first.cu); returns 0 when it does not take the shape */
+int drk_conv3x3_smallcin_launch(cudaStream_t st, const float *in, const float *wpack, const float *bias, float *out, int n, int W, int H,
+                                int Cin, int Cout, int act, int ldi, int ldo, int coff, int *rc);

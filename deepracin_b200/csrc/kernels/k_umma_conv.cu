@@ -49,6 +49,7 @@ struct UmmaParams {
     const float *bias;
     float *out;
     int ldo, coff, act;
+    int pool;                       /* 1: store max over 2x2 pixel windows (fused 2x2/2 max pooling) */
     int *status;
 };
 
@@ -300,7 +301,13 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                 const int tyi = rem / p.tiles_x, txi = rem - tyi * p.tiles_x;
                 const int y = tyi * p.TH + dy, x = txi * p.TW + dx;
                 valid = q < p.S && img < p.n && y < p.H && x < p.W;
-                pix = ((size_t)img * p.H + y) * p.W + x;
+                if (p.pool) {
+                    /* window (x&~1, y&~1): the lane with even x and even y stores; its three partners are lanes ^1, ^TW, ^(TW+1) */
+                    valid = valid && !(dx & 1) && !(dy & 1);
+                    pix = ((size_t)img * (p.H >> 1) + (y >> 1)) * (p.W >> 1) + (x >> 1);
+                } else {
+                    pix = ((size_t)img * p.H + y) * p.W + x;
+                }
             }
             float *dst = p.out + pix * p.ldo + p.coff + nt * BN;
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
@@ -310,8 +317,18 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(taddr + (uint32_t)c0, r);
+                const int col = nt * BN + c0;
+                if (p.pool) {
+                    /* bias and activation are monotone, so max commutes with them: reduce the raw accumulators */
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        float v = __uint_as_float(r[j]);
+                        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+                        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, p.TW));
+                        r[j] = __float_as_uint(v);
+                    }
+                }
                 if (valid) {
-                    const int col = nt * BN + c0;
 #pragma unroll
                     for (int j = 0; j < 32; j += 4) {
                         float4 v;
@@ -369,7 +386,7 @@ struct dRk_TensorConvPlan {
  * that is cheaper than covering a 28- or 14-pixel-wide image with many 4-pixel-wide boxes, whose short
  * contiguous runs make the TMA loads slow.
  */
-static void pick_subtile(int W, int H, int *TW, int *TH, int *S)
+static void pick_subtile(int W, int H, int pool, int *TW, int *TH, int *S)
 {
     double best = 1e30;
     int widths[8] = {32, 16, 8, 4, 2, 1, 0, 0};
@@ -377,11 +394,15 @@ static void pick_subtile(int W, int H, int *TW, int *TH, int *S)
     if (W <= 128 && W != 32 && W != 16 && W != 8 && W != 4) widths[nw++] = W;
     for (int wi = 0; wi < nw; wi++) {
         const int tw = widths[wi];
+        /* fused 2x2 pooling exchanges partners by warp shuffles: box width a power of two <= 16, even height */
+        if (pool && (tw > 16 || tw < 2 || (tw & (tw - 1)))) continue;
         for (int th = 1; th <= BM; th++) {
+            if (pool && (th & 1)) continue;
             const int rows = tw * th;
             if (rows > BM) break;
             if (rows % 8) continue;
-            for (int s = 1; s * rows <= BM && s <= 8; s++) {
+            if (pool && (32 % tw || ((32 / tw) & 1))) continue;
+            for (int s = 1; s * rows <= BM && s <= (pool ? 1 : 8); s++) {
                 const double cover = (double)((W + tw - 1) / tw * tw) * ((H + th - 1) / th * th) / ((double)W * H);
                 const double idle = (double)BM / (s * rows);
                 double cost = cover * idle * (1.0 + 0.3 * (s - 1));   /* every extra box is one more TMA instruction per stage: measured 27% slower with two */
@@ -435,9 +456,10 @@ static int launch_umma(cudaStream_t st, dRk_TensorConvPlan *pl)
 }
 
 extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float *wT, const float *bias, float *out, int n, int W, int H,
-                                                    int Cin, int Cout, int kw, int kh, int act, int ldo, int coff, int *status)
+                                                    int Cin, int Cout, int kw, int kh, int act, int ldo, int coff, int fuse_pool2, int *status)
 {
     if (!dRk_tensor_conv_supported(W, H, Cin, Cout, kw, kh) || n <= 0) return NULL;
+    if (fuse_pool2 && (kw != 3 || (W & 1) || (H & 1))) return NULL;
     if (ldo % 4 || coff % 4 || ((uintptr_t)out % 16) || ((uintptr_t)in % 16) || ((uintptr_t)wT % 16) || (bias && ((uintptr_t)bias % 16))) return NULL;
     PFN_encodeTiled enc = get_encode();
     if (!enc) return NULL;
@@ -449,7 +471,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     p.n = n; p.W = W; p.H = H; p.Cin = Cin; p.Cout = Cout;
     p.taps = kw * kh; p.kw = kw; p.pad = kw / 2;
     p.kslabs = Cin / BK;
-    p.bias = bias; p.out = out; p.ldo = ldo; p.coff = coff; p.act = act; p.status = status;
+    p.bias = bias; p.out = out; p.ldo = ldo; p.coff = coff; p.act = act; p.status = status; p.pool = fuse_pool2 ? 1 : 0;
     const cuuint32_t ones[4] = {1, 1, 1, 1};
     CUresult r;
     if (kw == 1) {
@@ -462,10 +484,10 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
         r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)in, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else {
-        pick_subtile(W, H, &p.TW, &p.TH, &p.S);
+        pick_subtile(W, H, fuse_pool2, &p.TW, &p.TH, &p.S);
         if (const char *ov = getenv("DRK_TILE")) {          /* experiment hook: "tw,th,s" */
             int a = 0, b = 0, c = 0;
-            if (sscanf(ov, "%d,%d,%d", &a, &b, &c) == 3 && a > 0 && b > 0 && c > 0 && (a * b) % 8 == 0 && a * b * c <= BM) { p.TW = a; p.TH = b; p.S = c; }
+            if (!fuse_pool2 && sscanf(ov, "%d,%d,%d", &a, &b, &c) == 3 && a > 0 && b > 0 && c > 0 && (a * b) % 8 == 0 && a * b * c <= BM) { p.TW = a; p.TH = b; p.S = c; }
         }
         p.tiles_x = (W + p.TW - 1) / p.TW;
         p.tiles_y = (H + p.TH - 1) / p.TH;

@@ -103,13 +103,15 @@ int dRk_concat_place(dRk_stream stream, const float *in, float *out, int n, int 
  *   wT   : [Cout][kh*kw*Cin]   (K contiguous), k = (ky*kw + kx)*Cin + c
  * Returns NULL if the shape is not supported by the tensor path (caller falls back to FFMA).
  * `status` is a device int the kernel writes a non-zero code to if a bounded wait runs out.
+ * fuse_pool2 = 1 (3x3 layers, even W and H): the epilogue stores the maximum over each 2x2 pixel window,
+ * i.e. `out` is the (W/2) x (H/2) result of the 2x2/2 max-pooling node that follows the convolution.
  */
 typedef struct dRk_TensorConvPlan dRk_TensorConvPlan;
 /* 1 if the tensor path can evaluate this layer shape (stride 1, 1x1 or 3x3, channel counts it can tile). */
 int dRk_tensor_conv_supported(int W, int H, int Cin, int Cout, int kw, int kh);
 dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float *wT, const float *bias, float *out,
                                          int n, int W, int H, int Cin, int Cout, int kw, int kh, int act,
-                                         int ldo, int coff, int *status);
+                                         int ldo, int coff, int fuse_pool2, int *status);
 int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *plan);
 void dRk_tensor_conv_free(dRk_TensorConvPlan *plan);
 

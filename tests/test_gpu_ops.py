@@ -21,6 +21,9 @@ CONV_SHAPES = [
     ("c3_small", 1, 3, 8, 7, 10, 3, 1),
     ("c3_16", 2, 16, 16, 12, 12, 3, 1),
     ("c3_odd_channels", 1, 5, 6, 9, 13, 3, 1),
+    ("c3_first_layer", 2, 3, 64, 17, 23, 3, 1),      # RGB first layer: the few-input-channel kernel
+    ("c3_cin4", 1, 4, 32, 9, 10, 3, 1),
+    ("c3_cin1", 3, 1, 16, 8, 9, 3, 1),
     ("c3_wide", 3, 32, 72, 17, 19, 3, 1),
     ("c3_deep", 1, 128, 64, 14, 14, 3, 1),
     ("c1_64to16", 2, 64, 16, 20, 20, 1, 1),

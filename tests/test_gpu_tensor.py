@@ -58,7 +58,7 @@ def test_tensor_path_falls_back_where_it_cannot_tile():
         d = dr.Conv2d(c, [3, 3, 64, 64], [1, 2, 2, 1], "relu", z((3, 3, 64, 64), np.float32), None)
         dr.mark_as_output(d)
         dr.prepare(g)
-        assert [dr.lib.dR_getConvAlgo(n.ptr) for n in (a, b, c, d)] == [2, 4, 1, 1]
+        assert [dr.lib.dR_getConvAlgo(n.ptr) for n in (a, b, c, d)] == [1, 4, 1, 1]
 
 
 def test_tf32_network_agrees_with_fp32_on_top1():
@@ -77,3 +77,28 @@ def test_tf32_network_agrees_with_fp32_on_top1():
             assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
     assert np.array_equal(outs["fp32"].argmax(1), outs["tf32"].argmax(1))
     assert rel_err(outs["tf32"], outs["fp32"]) <= 2e-2     # probabilities after 16 TF32 layers
+
+
+@pytest.mark.parametrize("n,cin,cout,h,w", [(1, 64, 64, 56, 56), (2, 128, 256, 28, 28), (3, 256, 512, 14, 14), (2, 32, 64, 12, 20), (1, 64, 64, 224, 224)])
+def test_conv_with_fused_maxpool_matches_oracle(n, cin, cout, h, w):
+    """conv3x3 + ReLU followed by 2x2/2 max pooling: the tensor kernel's epilogue stores the pooled tensor."""
+    x, wt, b = cases.conv_case("fusedpool_%d_%d" % (cin, h), n, cin, cout, h, w, 3, True)
+    ref = oracle.pool(oracle.conv2d(x, wt, b, (1, 1), 1), (2, 2, 1), (2, 2, 1), 0)
+    res = {}
+    for fuse in (True, False):
+        with dr.Environment() as env:
+            g = env.create_graph("CHW")
+            g.batch = n
+            g.math = "tf32"
+            g.fuse = fuse
+            f = dr.feed_node(g, [cin, h, w])
+            c = conv_build(wt, b, 1, 1)(g, [f])
+            o = dr.Pooling(c, "max", [1, 2, 2, 1], [1, 2, 2, 1])
+            dr.mark_as_output(o)
+            dr.prepare(g)
+            dr.feed_data(f, x)
+            res[fuse] = dr.apply(g)[0].reshape(ref.shape)
+            assert dr.lib.dR_getLaunchCount(g.ptr) == (3 if fuse else 4)     # feed layout, conv(+pool), [pool], output layout
+            assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    assert rel_err(res[True], ref) <= TOL_TF32
+    assert np.array_equal(res[True], res[False])        # same accumulators, max commutes with bias + ReLU
