@@ -355,6 +355,215 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
+/*
+ * Halo variant for 3x3 layers whose image tiles exactly into 14 x 8 pixel blocks (224, 112, 56 ...).
+ *
+ * The plain kernel above re-stages the A tile for each of the nine taps, and the SM's shared-memory
+ * port (TMA writes + MMA operand reads, 128 B/clk) is what bounds it.  Here the (14+2) x (8+2) haloed
+ * input block of a 32-channel slab is staged ONCE (one TMA box, 160 rows of 128 B, pitch 16 pixels)
+ * and all nine taps read it: output pixel (ty, tx) of the block is MMA row m = ty*16 + tx, and tap
+ * (ky, kx) reads shared-memory rows m + ky*16 + kx -- a contiguous 128-row window of the same buffer,
+ * addressed by moving the matrix descriptor's start address by (ky*16 + kx) rows.  Rows with
+ * tx >= 14 are idle (12.5 % of the tensor pipe), A traffic into shared memory drops 7.2x.
+ * B tiles stream through their own ring, nine per A slab.
+ */
+#define HALO_TW 14
+#define HALO_TH 8
+#define HALO_P 16
+#define HALO_ROWS ((HALO_TH + 2) * HALO_P)             /* 160 rows loaded per slab */
+#define HALO_A_BYTES (HALO_ROWS * BK * 4)              /* 20480 */
+#define HALO_A_SLOT (21 * 1024)                        /* 168 rows: taps of the two idle tail rows read up to row 161 */
+#define HALO_NA 3
+
+template <int BN>
+struct HaloCfg {
+    static constexpr int B_STAGE_BYTES = BN * BK * 4;
+    static constexpr int NB_RAW = (SMEM_BUDGET - 2048 - HALO_NA * HALO_A_SLOT) / B_STAGE_BYTES;
+    static constexpr int NB = NB_RAW > 10 ? 10 : NB_RAW;
+    static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
+    static constexpr int SMEM_BYTES = HALO_NA * HALO_A_SLOT + NB * B_STAGE_BYTES + 1024 + 512;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(UMMA_THREADS, 1)
+k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const UmmaParams p)
+{
+    using C = HaloCfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *gen = smem_raw + (base - raw);
+    const uint32_t a_base = base, b_base = base + HALO_NA * HALO_A_SLOT;
+    const uint32_t bars = b_base + C::NB * C::B_STAGE_BYTES;
+    constexpr int NBARS = 2 * HALO_NA + 2 * C::NB + 4;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + HALO_NA * HALO_A_SLOT + C::NB * C::B_STAGE_BYTES + 8 * NBARS);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    auto afull = [&](int s) { return bars + 8u * s; };
+    auto aempty = [&](int s) { return bars + 8u * (HALO_NA + s); };
+    auto bfull = [&](int s) { return bars + 8u * (2 * HALO_NA + s); };
+    auto bempty = [&](int s) { return bars + 8u * (2 * HALO_NA + C::NB + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * HALO_NA + 2 * C::NB + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * HALO_NA + 2 * C::NB + 2 + a); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int per = p.tiles_x * p.tiles_y;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < HALO_NA; s++) { mbar_init(afull(s), 1); mbar_init(aempty(s), 1); }
+        for (int s = 0; s < C::NB; s++) { mbar_init(bfull(s), 1); mbar_init(bempty(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&mapA) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&mapB) : "memory");
+            int as = 0, bs = 0;
+            uint32_t aph = 0, bph = 0;
+            long long a_issued = 0, b_issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int mt = t / p.n_tiles, nt = t - mt * p.n_tiles;
+                const int img = mt / per, rem = mt - img * per;
+                const int tyi = rem / p.tiles_x, txi = rem - tyi * p.tiles_x;
+                for (int ks = 0; ks < p.kslabs && ok; ks++) {
+                    if (!mbar_wait(aempty(as), aph ^ 1u, abort_flag, p.status, 5)) { ok = false; break; }
+                    mbar_expect_tx(afull(as), HALO_A_BYTES);
+                    tma_load_4d(a_base + as * HALO_A_SLOT, &mapA, ks * BK, txi * HALO_TW - 1, tyi * HALO_TH - 1, img, afull(as));
+                    a_issued++;
+                    if (++as == HALO_NA) { as = 0; aph ^= 1u; }
+                    for (int tap = 0; tap < 9; tap++) {
+                        if (!mbar_wait(bempty(bs), bph ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+                        mbar_expect_tx(bfull(bs), C::B_STAGE_BYTES);
+                        tma_load_2d(b_base + bs * C::B_STAGE_BYTES, &mapB, tap * p.Cin + ks * BK, nt * BN, bfull(bs));
+                        b_issued++;
+                        if (++bs == C::NB) { bs = 0; bph ^= 1u; }
+                    }
+                }
+            }
+            if (!ok) {      /* drain what is still in flight (bounded) before the CTA's shared memory is released */
+                long long pend = a_issued < HALO_NA ? a_issued : HALO_NA;
+                int s = as; uint32_t ph = aph;
+                for (long long i = 0; i < pend; i++) {
+                    if (--s < 0) { s = HALO_NA - 1; ph ^= 1u; }
+                    const long long t0 = clock64();
+                    while (!mbar_try(afull(s), ph) && clock64() - t0 < WAIT_CYCLES) { }
+                }
+                pend = b_issued < C::NB ? b_issued : C::NB;
+                s = bs; ph = bph;
+                for (long long i = 0; i < pend; i++) {
+                    if (--s < 0) { s = C::NB - 1; ph ^= 1u; }
+                    const long long t0 = clock64();
+                    while (!mbar_try(bfull(s), ph) && clock64() - t0 < WAIT_CYCLES) { }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN);
+            int as = 0, bs = 0;
+            uint32_t aph = 0, bph = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int ks = 0; ks < p.kslabs && ok; ks++) {
+                    if (!mbar_wait(afull(as), aph, abort_flag, p.status, 6)) { ok = false; break; }
+                    const uint32_t sa = a_base + as * HALO_A_SLOT;
+                    for (int tap = 0; tap < 9; tap++) {
+                        if (!mbar_wait(bfull(bs), bph, abort_flag, p.status, 3)) { ok = false; break; }
+                        tc_fence_after();
+                        const int ky = tap / 3, kx = tap - ky * 3;
+                        const uint64_t adesc = make_smem_desc(sa + (uint32_t)((ky * HALO_P + kx) * BK * 4));
+                        const uint64_t bdesc = make_smem_desc(b_base + bs * C::B_STAGE_BYTES);
+#pragma unroll
+                        for (int j = 0; j < BK / 8; j++)
+                            umma_tf32(d_tmem, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, (ks | tap | j) ? 1u : 0u);
+                        umma_commit(bempty(bs));
+                        if (++bs == C::NB) { bs = 0; bph ^= 1u; }
+                    }
+                    if (ok) umma_commit(aempty(as));
+                    if (++as == HALO_NA) { as = 0; aph ^= 1u; }
+                }
+                if (ok) umma_commit(tfull_bar(acc));
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int row = quarter * 32 + lane;
+        const int dy = row / HALO_P, dx = row - dy * HALO_P;
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
+            const int mt = t / p.n_tiles, nt = t - mt * p.n_tiles;
+            const int acc = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            const int img = mt / per, rem = mt - img * per;
+            const int tyi = rem / p.tiles_x, txi = rem - tyi * p.tiles_x;
+            const int y = tyi * HALO_TH + dy, x = txi * HALO_TW + dx;
+            bool valid = dx < HALO_TW && dy < HALO_TH && y < p.H && x < p.W;
+            size_t pix;
+            if (p.pool) {
+                valid = valid && !(dx & 1) && !(dy & 1);
+                pix = ((size_t)img * (p.H >> 1) + (y >> 1)) * (p.W >> 1) + (x >> 1);
+            } else {
+                pix = ((size_t)img * p.H + y) * p.W + x;
+            }
+            float *dst = p.out + pix * p.ldo + p.coff + nt * BN;
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + (uint32_t)c0, r);
+                const int col = nt * BN + c0;
+                if (p.pool) {
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        float v = __uint_as_float(r[j]);
+                        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+                        v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, HALO_P));
+                        r[j] = __float_as_uint(v);
+                    }
+                }
+                if (valid) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4) {
+                        float4 v;
+                        v.x = __uint_as_float(r[j + 0]); v.y = __uint_as_float(r[j + 1]);
+                        v.z = __uint_as_float(r[j + 2]); v.w = __uint_as_float(r[j + 3]);
+                        if (p.bias) {
+                            const float4 b = __ldg(reinterpret_cast<const float4 *>(p.bias + col + j));
+                            v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                        }
+                        v.x = drk_act(v.x, p.act); v.y = drk_act(v.y, p.act); v.z = drk_act(v.z, p.act); v.w = drk_act(v.w, p.act);
+                        *reinterpret_cast<float4 *>(dst + c0 + j) = v;
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
 /* ------------------------------------------------------------------------- host side */
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                     const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -377,6 +586,7 @@ struct dRk_TensorConvPlan {
     UmmaParams p;
     int BN;
     int grid;
+    int halo;           /* 1: k_umma_conv_halo (one haloed A tile per channel slab, reused by all nine taps) */
 };
 
 /*
@@ -422,6 +632,13 @@ extern "C" int dRk_tensor_conv_supported(int W, int H, int Cin, int Cout, int kw
     return 1;
 }
 
+/* fraction of the halo kernel's MMA rows that produce output pixels for a W x H image (14 x 8 blocks, 16-pixel pitch) */
+static double halo_fill(int W, int H)
+{
+    const double tx = (W + HALO_TW - 1) / HALO_TW, ty = (H + HALO_TH - 1) / HALO_TH;
+    return (double)W * H / (tx * ty * BM);
+}
+
 static int pick_bn(int Cout, long long m_tiles, int sms)
 {
     /* largest N tile that divides Cout, unless a smaller one fills the SMs noticeably better */
@@ -439,6 +656,20 @@ static int pick_bn(int Cout, long long m_tiles, int sms)
     }
     if (!best) best = Cout % 64 == 0 ? 64 : 32;
     return best;
+}
+
+template <int BN>
+static int launch_umma_halo(cudaStream_t st, dRk_TensorConvPlan *pl)
+{
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(k_umma_conv_halo<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, HaloCfg<BN>::SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    k_umma_conv_halo<BN><<<pl->grid, UMMA_THREADS, HaloCfg<BN>::SMEM_BYTES, st>>>(pl->mapA, pl->mapB, pl->p);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
 }
 
 template <int BN>
@@ -483,6 +714,17 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
         const cuuint32_t box[2] = {BK, BM};
         r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)in, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else if (halo_fill(W, H) >= 0.55 && !getenv("DRK_NO_HALO")) {
+        pl->halo = 1;
+        p.TW = HALO_TW; p.TH = HALO_TH; p.S = 1;
+        p.tiles_x = (W + HALO_TW - 1) / HALO_TW; p.tiles_y = (H + HALO_TH - 1) / HALO_TH;
+        p.total_sub = (long long)n * p.tiles_x * p.tiles_y;
+        p.m_tiles = (int)p.total_sub;
+        const cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)n};
+        const cuuint64_t strides[3] = {(cuuint64_t)Cin * 4, (cuuint64_t)W * Cin * 4, (cuuint64_t)H * W * Cin * 4};
+        const cuuint32_t box[4] = {BK, HALO_P, HALO_TH + 2, 1};
+        r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void *)in, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else {
         pick_subtile(W, H, fuse_pool2, &p.TW, &p.TH, &p.S);
         if (const char *ov = getenv("DRK_TILE")) {          /* experiment hook: "tw,th,s" */
@@ -522,6 +764,14 @@ extern "C" int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *pl)
 {
     if (!pl) return -1;
     cudaStream_t st = drk_stream(stream);
+    if (pl->halo) {
+        switch (pl->BN) {
+        case 256: return launch_umma_halo<256>(st, pl);
+        case 128: return launch_umma_halo<128>(st, pl);
+        case 64: return launch_umma_halo<64>(st, pl);
+        }
+        return -1;
+    }
     switch (pl->BN) {
     case 256: return launch_umma<256>(st, pl);
     case 128: return launch_umma<128>(st, pl);
