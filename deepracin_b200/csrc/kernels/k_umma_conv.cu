@@ -564,6 +564,207 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     if (warp == 1) tmem_dealloc(tmem_base, C::TMEM_COLS);
 }
 
+/*
+ * Transposed halo variant for layers with few output channels (Cout <= 128).
+ *
+ * A tcgen05.mma streams its A operand (128 rows x 32 B) into the tensor core in about the time a
+ * 128 x 256 x 8 product takes, so an instruction with N < 256 runs at N/256 of the pipe's rate
+ * (measured: ~93 ns per instruction for N = 64, 128 and 256 alike).  With pixels on M and output
+ * channels on N a 64-channel layer can therefore use a quarter of the pipe.  This variant computes the
+ * transposed product instead: M = output channels (the filter tile, rows past Cout are TMA zero fill),
+ * N = 256 pixels -- a 14 x 16 pixel block read from its haloed (14+2) x (16+2) input block exactly
+ * as in the halo kernel above, now through the B descriptor.  The accumulator is [channel][pixel]:
+ * each epilogue lane owns one channel, a warp stores 32 consecutive channels of one pixel per
+ * instruction, and the fused 2x2 max pooling is a maximum over four registers of the same lane.
+ */
+#define SWAP_TH 16
+#define SWAP_N 256
+#define SWAP_HALO_ROWS ((SWAP_TH + 2) * HALO_P)        /* 288 rows loaded per slab */
+#define SWAP_HALO_BYTES (SWAP_HALO_ROWS * BK * 4)      /* 36864 */
+#define SWAP_HALO_SLOT (38 * 1024)                     /* 304 rows >= 256 + 2*16 + 2 */
+#define SWAP_NH 2
+#define SWAP_W_BYTES (BM * BK * 4)                     /* filter stage: 128 rows x 128 B */
+#define SWAP_NW 9
+#define SWAP_SMEM (SWAP_NH * SWAP_HALO_SLOT + SWAP_NW * SWAP_W_BYTES + 1024 + 512)
+
+__global__ void __launch_bounds__(UMMA_THREADS, 1)
+k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW, const UmmaParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *gen = smem_raw + (base - raw);
+    const uint32_t h_base = base, w_base = base + SWAP_NH * SWAP_HALO_SLOT;
+    const uint32_t bars = w_base + SWAP_NW * SWAP_W_BYTES;
+    constexpr int NBARS = 2 * SWAP_NH + 2 * SWAP_NW + 4;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + SWAP_NH * SWAP_HALO_SLOT + SWAP_NW * SWAP_W_BYTES + 8 * NBARS);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    auto hfull = [&](int s) { return bars + 8u * s; };
+    auto hempty = [&](int s) { return bars + 8u * (SWAP_NH + s); };
+    auto wfull = [&](int s) { return bars + 8u * (2 * SWAP_NH + s); };
+    auto wempty = [&](int s) { return bars + 8u * (2 * SWAP_NH + SWAP_NW + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + 2 + a); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = p.m_tiles * p.n_tiles;
+    const int per = p.tiles_x * p.tiles_y;
+    constexpr int TMEM_COLS = 2 * SWAP_N;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < SWAP_NH; s++) { mbar_init(hfull(s), 1); mbar_init(hempty(s), 1); }
+        for (int s = 0; s < SWAP_NW; s++) { mbar_init(wfull(s), 1); mbar_init(wempty(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&mapX) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&mapW) : "memory");
+            int hs = 0, ws = 0;
+            uint32_t hph = 0, wph = 0;
+            long long h_issued = 0, w_issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int mt = t / p.n_tiles, nt = t - mt * p.n_tiles;
+                const int img = mt / per, rem = mt - img * per;
+                const int tyi = rem / p.tiles_x, txi = rem - tyi * p.tiles_x;
+                for (int ks = 0; ks < p.kslabs && ok; ks++) {
+                    if (!mbar_wait(hempty(hs), hph ^ 1u, abort_flag, p.status, 5)) { ok = false; break; }
+                    mbar_expect_tx(hfull(hs), SWAP_HALO_BYTES);
+                    tma_load_4d(h_base + hs * SWAP_HALO_SLOT, &mapX, ks * BK, txi * HALO_TW - 1, tyi * SWAP_TH - 1, img, hfull(hs));
+                    h_issued++;
+                    if (++hs == SWAP_NH) { hs = 0; hph ^= 1u; }
+                    for (int tap = 0; tap < 9; tap++) {
+                        if (!mbar_wait(wempty(ws), wph ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+                        mbar_expect_tx(wfull(ws), SWAP_W_BYTES);
+                        tma_load_2d(w_base + ws * SWAP_W_BYTES, &mapW, tap * p.Cin + ks * BK, nt * BM, wfull(ws));
+                        w_issued++;
+                        if (++ws == SWAP_NW) { ws = 0; wph ^= 1u; }
+                    }
+                }
+            }
+            if (!ok) {
+                long long pend = h_issued < SWAP_NH ? h_issued : SWAP_NH;
+                int s = hs; uint32_t ph = hph;
+                for (long long i = 0; i < pend; i++) {
+                    if (--s < 0) { s = SWAP_NH - 1; ph ^= 1u; }
+                    const long long t0 = clock64();
+                    while (!mbar_try(hfull(s), ph) && clock64() - t0 < WAIT_CYCLES) { }
+                }
+                pend = w_issued < SWAP_NW ? w_issued : SWAP_NW;
+                s = ws; ph = wph;
+                for (long long i = 0; i < pend; i++) {
+                    if (--s < 0) { s = SWAP_NW - 1; ph ^= 1u; }
+                    const long long t0 = clock64();
+                    while (!mbar_try(wfull(s), ph) && clock64() - t0 < WAIT_CYCLES) { }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(SWAP_N);
+            int hs = 0, ws = 0;
+            uint32_t hph = 0, wph = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * SWAP_N);
+                for (int ks = 0; ks < p.kslabs && ok; ks++) {
+                    if (!mbar_wait(hfull(hs), hph, abort_flag, p.status, 6)) { ok = false; break; }
+                    const uint32_t sh = h_base + hs * SWAP_HALO_SLOT;
+                    for (int tap = 0; tap < 9; tap++) {
+                        if (!mbar_wait(wfull(ws), wph, abort_flag, p.status, 3)) { ok = false; break; }
+                        tc_fence_after();
+                        const int ky = tap / 3, kx = tap - ky * 3;
+                        const uint64_t adesc = make_smem_desc(w_base + ws * SWAP_W_BYTES);
+                        const uint64_t bdesc = make_smem_desc(sh + (uint32_t)((ky * HALO_P + kx) * BK * 4));
+#pragma unroll
+                        for (int j = 0; j < BK / 8; j++)
+                            umma_tf32(d_tmem, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, (ks | tap | j) ? 1u : 0u);
+                        umma_commit(wempty(ws));
+                        if (++ws == SWAP_NW) { ws = 0; wph ^= 1u; }
+                    }
+                    if (ok) umma_commit(hempty(hs));
+                    if (++hs == SWAP_NH) { hs = 0; hph ^= 1u; }
+                }
+                if (ok) umma_commit(tfull_bar(acc));
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
+            const int mt = t / p.n_tiles, nt = t - mt * p.n_tiles;
+            const int acc = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            const int img = mt / per, rem = mt - img * per;
+            const int tyi = rem / p.tiles_x, txi = rem - tyi * p.tiles_x;
+            const int ch = nt * BM + quarter * 32 + lane;        /* the output channel this lane owns */
+            const bool chok = ch < p.Cout;
+            const float bv = (p.bias && chok) ? __ldg(p.bias + ch) : 0.0f;
+            /* ReLU = clamp to [0, FLT_MAX]; linear = clamp to [-inf, +inf] (a no-op): same two instructions either way */
+            const float lo = p.act ? 0.0f : -INFINITY, hi = p.act ? FLT_MAX : INFINITY;
+            float *obase = p.out + p.coff + ch;
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * SWAP_N);
+#pragma unroll 1
+            for (int c0 = 0; c0 < SWAP_N; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + (uint32_t)c0, r);
+                if (!chok) continue;
+                const int y0 = tyi * SWAP_TH + (c0 >> 4);          /* this chunk holds block rows y0 and y0 + 1 */
+                const int x0 = txi * HALO_TW;
+                if (p.pool) {
+                    const int yo = y0 >> 1;
+                    if (yo < (p.H >> 1)) {
+                        float *orow = obase + ((size_t)img * (p.H >> 1) + yo) * (size_t)(p.W >> 1) * p.ldo;
+#pragma unroll
+                        for (int px = 0; px < HALO_TW / 2; px++) {
+                            const int xo = (x0 >> 1) + px;
+                            float v = fmaxf(fmaxf(__uint_as_float(r[2 * px]), __uint_as_float(r[2 * px + 1])),
+                                            fmaxf(__uint_as_float(r[16 + 2 * px]), __uint_as_float(r[16 + 2 * px + 1])));
+                            if (xo < (p.W >> 1)) orow[(size_t)xo * p.ldo] = fminf(fmaxf(v + bv, lo), hi);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int dy = 0; dy < 2; dy++) {
+                        const int y = y0 + dy;
+                        if (y >= p.H) break;
+                        float *optr = obase + (((size_t)img * p.H + y) * p.W + x0) * (size_t)p.ldo;
+                        const int nx = min(HALO_TW, p.W - x0);
+#pragma unroll
+                        for (int dx = 0; dx < HALO_TW; dx++) {
+                            if (dx < nx) *optr = fminf(fmaxf(__uint_as_float(r[dy * 16 + dx]) + bv, lo), hi);
+                            optr += p.ldo;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
 /* ------------------------------------------------------------------------- host side */
 typedef CUresult (*PFN_encodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
                                     const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -587,6 +788,7 @@ struct dRk_TensorConvPlan {
     int BN;
     int grid;
     int halo;           /* 1: k_umma_conv_halo (one haloed A tile per channel slab, reused by all nine taps) */
+    int swap;           /* 1: k_umma_conv_swap (channels on M, 256 pixels on N) for Cout <= 128 */
 };
 
 /*
@@ -637,6 +839,13 @@ static double halo_fill(int W, int H)
 {
     const double tx = (W + HALO_TW - 1) / HALO_TW, ty = (H + HALO_TH - 1) / HALO_TH;
     return (double)W * H / (tx * ty * BM);
+}
+
+/* same for the transposed variant's 14 x 16 blocks (256 MMA columns per block) */
+static double swap_fill(int W, int H)
+{
+    const double tx = (W + HALO_TW - 1) / HALO_TW, ty = (H + SWAP_TH - 1) / SWAP_TH;
+    return (double)W * H / (tx * ty * SWAP_N);
 }
 
 static int pick_bn(int Cout, long long m_tiles, int sms)
@@ -714,6 +923,17 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
         const cuuint32_t box[2] = {BK, BM};
         r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)in, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else if (Cout <= BM && swap_fill(W, H) >= 0.8 && !getenv("DRK_NO_SWAP") && !getenv("DRK_NO_HALO")) {
+        pl->swap = 1;
+        p.TW = HALO_TW; p.TH = SWAP_TH; p.S = 1;
+        p.tiles_x = (W + HALO_TW - 1) / HALO_TW; p.tiles_y = (H + SWAP_TH - 1) / SWAP_TH;
+        p.total_sub = (long long)n * p.tiles_x * p.tiles_y;
+        p.m_tiles = (int)p.total_sub;
+        const cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)n};
+        const cuuint64_t strides[3] = {(cuuint64_t)Cin * 4, (cuuint64_t)W * Cin * 4, (cuuint64_t)H * W * Cin * 4};
+        const cuuint32_t box[4] = {BK, HALO_P, SWAP_TH + 2, 1};
+        r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void *)in, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else if (halo_fill(W, H) >= 0.55 && !getenv("DRK_NO_HALO")) {
         pl->halo = 1;
         p.TW = HALO_TW; p.TH = HALO_TH; p.S = 1;
@@ -742,9 +962,9 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }
     if (r != CUDA_SUCCESS) { fprintf(stderr, "tensor conv plan: activation tensor map rejected (%d)\n", (int)r); free(pl); return NULL; }
-    pl->BN = pick_bn(Cout, p.m_tiles, sms);
+    pl->BN = pl->swap ? BM : pick_bn(Cout, p.m_tiles, sms);
     if (pl->BN == 32) { free(pl); return NULL; }
-    p.n_tiles = Cout / pl->BN;
+    p.n_tiles = pl->swap ? (Cout + BM - 1) / BM : Cout / pl->BN;
     {
         const cuuint64_t K = (cuuint64_t)p.taps * Cin;
         const cuuint64_t dims[2] = {K, (cuuint64_t)Cout};
@@ -764,6 +984,17 @@ extern "C" int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *pl)
 {
     if (!pl) return -1;
     cudaStream_t st = drk_stream(stream);
+    if (pl->swap) {
+        static bool attr_done = false;
+        if (!attr_done) {
+            cudaError_t e = cudaFuncSetAttribute(k_umma_conv_swap, cudaFuncAttributeMaxDynamicSharedMemorySize, SWAP_SMEM);
+            if (e != cudaSuccess) return (int)e;
+            attr_done = true;
+        }
+        k_umma_conv_swap<<<pl->grid, UMMA_THREADS, SWAP_SMEM, st>>>(pl->mapA, pl->mapB, pl->p);
+        DRK_COUNT_LAUNCH();
+        return DRK_LAUNCH_RESULT();
+    }
     if (pl->halo) {
         switch (pl->BN) {
         case 256: return launch_umma_halo<256>(st, pl);
