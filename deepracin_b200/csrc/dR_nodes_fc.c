@@ -7,6 +7,7 @@
 #include "dR_nodes_fc.h"
 #include "dR_core.h"
 #include "dR_kernels.h"
+#include "dR_b200.h"
 
 /* reference src/dR_nodes_fc.c:6-48 */
 dR_Node *dR_FullyConnected(dR_Graph *net, dR_Node *inputLayer, dR_Shape2 *sh, dR_ActivationType acttype, gboolean useB)
@@ -92,7 +93,10 @@ gint32 dR_fc_getRequiredOutputBufferSize(dR_Node *layer) { return layer->oshape.
 gboolean dR_fc_createKernel(dR_Graph *net, dR_Node *layer)
 {
     dR_FC_Data *fc = (dR_FC_Data *)layer->layer;
-    layer->scratchFloats = dRk_fc_scratch_floats(net->config->batchSize, fc->shape.s0, fc->shape.s1);
+    /* TF32 mode, batches of 16..128: split-K GEMM on the tensor cores; otherwise the FP32 weight-streaming kernels */
+    fc->chosenTensor = net->config->mathMode == DR_MATH_TF32 && dRk_tensor_fc_supported(net->config->batchSize, fc->shape.s0, fc->shape.s1);
+    layer->scratchFloats = fc->chosenTensor ? dRk_tensor_fc_scratch_floats(net->config->batchSize, fc->shape.s0, fc->shape.s1)
+                                            : dRk_fc_scratch_floats(net->config->batchSize, fc->shape.s0, fc->shape.s1);
     return TRUE;
 }
 
@@ -101,7 +105,8 @@ gboolean dR_fc_allocateBuffers(dR_Graph *net, dR_Node *layer)
     dR_FC_Data *fc = (dR_FC_Data *)layer->layer;
     gboolean ret;
     if (!fc->hasVariables) { g_print("FullyConnected Layer %d has no weights (call dR_FullyConnected_setVariables)\n", layer->layerID); return FALSE; }
-    ret = dR_createFloatBufferL(net, &fc->weightsBuf, (size_t)fc->shape.s0 * fc->shape.s1);
+    if (fc->chosenTensor) ret = dR_createFloatBufferL(net, &fc->weightsBufT, (size_t)fc->shape.s0 * fc->shape.s1);
+    else ret = dR_createFloatBufferL(net, &fc->weightsBuf, (size_t)fc->shape.s0 * fc->shape.s1);
     if (fc->useBias) ret &= dR_createFloatBuffer(net, &fc->biasBuf, fc->shape.s1, CL_MEM_READ_ONLY);
     return ret;
 }
@@ -109,7 +114,19 @@ gboolean dR_fc_allocateBuffers(dR_Graph *net, dR_Node *layer)
 gboolean dR_fc_fillBuffers(dR_Graph *net, dR_Node *layer)
 {
     dR_FC_Data *fc = (dR_FC_Data *)layer->layer;
-    gboolean ret = dR_uploadArray(net, "", fc->weights, 0, (size_t)fc->shape.s0 * fc->shape.s1 * sizeof(cl_float), fc->weightsBuf);
+    gboolean ret;
+    if (fc->chosenTensor) {
+        /* K-major packing [Nout][Nin] for the TMA-fed B operand */
+        const size_t nin = (size_t)fc->shape.s0, nout = (size_t)fc->shape.s1;
+        gfloat *t = (gfloat *)g_malloc(nin * nout * sizeof(gfloat));
+        for (size_t k0 = 0; k0 < nin; k0 += 64)
+            for (size_t o = 0; o < nout; o++)
+                for (size_t k = k0; k < nin && k < k0 + 64; k++) t[o * nin + k] = fc->weights[k * nout + o];
+        ret = dR_uploadArray(net, "", t, 0, nin * nout * sizeof(cl_float), fc->weightsBufT);
+        g_free(t);
+    } else {
+        ret = dR_uploadArray(net, "", fc->weights, 0, (size_t)fc->shape.s0 * fc->shape.s1 * sizeof(cl_float), fc->weightsBuf);
+    }
     if (fc->useBias) ret &= dR_uploadArray(net, "", fc->biases, 0, (size_t)fc->shape.s1 * sizeof(cl_float), fc->biasBuf);
     return ret;
 }
@@ -121,6 +138,16 @@ gboolean dR_fc_compute(dR_Graph *net, dR_Node *layer)
     dR_Node *in = dR_firstInput(layer);
     if (in->act_cstride != in->oshape.s2) { g_print("FullyConnected Layer %d: input must be dense\n", layer->layerID); return FALSE; }
     dR_beginCLKernel(net);
+    if (fc->chosenTensor) {
+        if (!fc->tmaDescs) {
+            fc->tmaDescs = dRk_tensor_fc_plan(dR_actPtr(in), (const float *)fc->weightsBufT, fc->useBias ? (const float *)fc->biasBuf : NULL,
+                                              dR_actPtr(layer), (float *)net->scratch, net->config->batchSize, fc->shape.s0, fc->shape.s1,
+                                              fc->activation == tReLU ? 1 : 0, (int *)net->statusWord);
+            if (!fc->tmaDescs) { g_print("FullyConnected Layer %d: tensor-core plan could not be built\n", layer->layerID); return FALSE; }
+        }
+        net->clConfig->clError = dRk_tensor_fc_run(net->clConfig->clCommandQueue, (dRk_TensorFcPlan *)fc->tmaDescs);
+        return dR_finishCLKernel(net, "deepRACIN:FullyConnected");
+    }
     net->clConfig->clError = dRk_fc_f32(net->clConfig->clCommandQueue, dR_actPtr(in), (const float *)fc->weightsBuf,
                                         fc->useBias ? (const float *)fc->biasBuf : NULL, dR_actPtr(layer), (float *)net->scratch,
                                         net->config->batchSize, fc->shape.s0, fc->shape.s1, fc->activation == tReLU ? 1 : 0);
@@ -132,6 +159,8 @@ gboolean dR_fc_cleanupBuffers(dR_Graph *net, dR_Node *layer)
     dR_FC_Data *fc = (dR_FC_Data *)layer->layer;
     gboolean ret = TRUE;
     if (fc->weightsBuf) { ret &= dR_clMemoryBufferCleanup(net, fc->weightsBuf); fc->weightsBuf = NULL; }
+    if (fc->weightsBufT) { ret &= dR_clMemoryBufferCleanup(net, fc->weightsBufT); fc->weightsBufT = NULL; }
+    if (fc->tmaDescs) { dRk_tensor_fc_free((dRk_TensorFcPlan *)fc->tmaDescs); fc->tmaDescs = NULL; }
     if (fc->biasBuf) { ret &= dR_clMemoryBufferCleanup(net, fc->biasBuf); fc->biasBuf = NULL; }
     return ret;
 }

@@ -99,6 +99,13 @@ __global__ void k_fc_reduce(const float *__restrict__ partial, const float *__re
     out[i] = act ? fminf(fmaxf(s, 0.0f), FLT_MAX) : fminf(fmaxf(s, -FLT_MAX), FLT_MAX);
 }
 
+int drk_fc_reduce_launch(cudaStream_t st, const float *partial, const float *bias, float *out, int total, int Nout, int splits, int act)
+{
+    k_fc_reduce<<<(total + 255) / 256, 256, 0, st>>>(partial, bias, out, total, Nout, splits, act);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}
+
 static int fc_splits(int n, int Nin, int Nout)
 {
     /* aim for roughly 4 CTAs per SM; keep slices a multiple of 64 rows and at least 256 long */

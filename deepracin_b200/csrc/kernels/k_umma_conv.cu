@@ -50,6 +50,8 @@ struct UmmaParams {
     float *out;
     int ldo, coff, act;
     int pool;                       /* 1: store max over 2x2 pixel windows (fused 2x2/2 max pooling) */
+    int ksplit, kper;               /* split-K (flat GEMM mode): ksplit partial products over kper slabs each */
+    long long split_stride;         /* floats between the partial outputs of consecutive K parts */
     int *status;
 };
 
@@ -181,8 +183,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     auto tempty_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + 2 + a); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int total_tiles = p.m_tiles * p.n_tiles;
-    const int kiters = p.taps * p.kslabs;
+    const int total_tiles = p.m_tiles * p.n_tiles * p.ksplit;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
@@ -206,10 +207,12 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
             long long issued = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
-                const int mt = t / p.n_tiles, nt = t - mt * p.n_tiles;
+                const int ksi = t % p.ksplit, tt = t / p.ksplit;
+                const int mt = tt / p.n_tiles, nt = tt - mt * p.n_tiles;
+                const int ks0 = ksi * p.kper, ks1 = min(p.kslabs, ks0 + p.kper);
                 for (int tap = 0; tap < p.taps && ok; tap++) {
                     const int ky = tap / p.kw, kx = tap - ky * p.kw;
-                    for (int ks = 0; ks < p.kslabs; ks++) {
+                    for (int ks = ks0; ks < ks1; ks++) {
                         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
                         const uint32_t sa = base + stage * C::STAGE_BYTES, sb = sa + A_STAGE_BYTES;
                         mbar_expect_tx(full_bar(stage), (uint32_t)p.stage_tx);
@@ -259,6 +262,8 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                 if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                const int ksi = t % p.ksplit;
+                const int kiters = p.taps * (min(p.kslabs, (ksi + 1) * p.kper) - ksi * p.kper);
                 for (int k = 0; k < kiters; k++) {
                     if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, 3)) { ok = false; break; }
                     tc_fence_after();
@@ -280,7 +285,8 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
         int it = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
-            const int mt = t / p.n_tiles, nt = t - mt * p.n_tiles;
+            const int ksi = t % p.ksplit, tt = t / p.ksplit;
+            const int mt = tt / p.n_tiles, nt = tt - mt * p.n_tiles;
             const int acc = it & 1;
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
             /* where does this thread's pixel live? */
@@ -309,7 +315,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                     pix = ((size_t)img * p.H + y) * p.W + x;
                 }
             }
-            float *dst = p.out + pix * p.ldo + p.coff + nt * BN;
+            float *dst = p.out + (size_t)ksi * p.split_stride + pix * p.ldo + p.coff + nt * BN;
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
@@ -912,6 +918,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     p.taps = kw * kh; p.kw = kw; p.pad = kw / 2;
     p.kslabs = Cin / BK;
     p.bias = bias; p.out = out; p.ldo = ldo; p.coff = coff; p.act = act; p.status = status; p.pool = fuse_pool2 ? 1 : 0;
+    p.ksplit = 1; p.kper = p.kslabs; p.split_stride = 0;
     const cuuint32_t ones[4] = {1, 1, 1, 1};
     CUresult r;
     if (kw == 1) {
@@ -1012,3 +1019,89 @@ extern "C" int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *pl)
 }
 
 extern "C" void dRk_tensor_conv_free(dRk_TensorConvPlan *pl) { free(pl); }
+
+/*
+ * Fully connected layer on the tensor cores (TF32 mode, larger batches): the activations [n][Nin] are the
+ * A operand of a flat GEMM (rows past the batch are TMA zero fill), the K-major weights [Nout][Nin] the
+ * B operand with N = 256 per tile; K is split over enough CTAs to occupy every SM, the partial products
+ * land in `scratch` ([ksplit][n][Nout]) and the reduce kernel of the FP32 path adds bias and activation.
+ * Bound: HBM (weights read once).  Replaces matrixVectorMultFirst/Second (Kernels/dR_fcl.cl:59-120).
+ */
+int drk_fc_reduce_launch(cudaStream_t st, const float *partial, const float *bias, float *out, int total, int Nout, int splits, int act);
+
+struct dRk_TensorFcPlan {
+    dRk_TensorConvPlan conv;
+    const float *bias;
+    float *out, *scratch;
+    int n, Nout, act;
+};
+
+extern "C" int dRk_tensor_fc_supported(int n, int Nin, int Nout)
+{
+    return n >= 16 && n <= BM && Nin % BK == 0 && Nout % 256 == 0 && Nin >= 8 * BK;
+}
+
+extern "C" size_t dRk_tensor_fc_scratch_floats(int n, int Nin, int Nout)
+{
+    if (!dRk_tensor_fc_supported(n, Nin, Nout)) return 0;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    int ksplit = sms / (Nout / 256);
+    if (ksplit < 1) ksplit = 1;
+    const int kslabs = Nin / BK;
+    if (ksplit > kslabs / 8) ksplit = kslabs / 8 > 0 ? kslabs / 8 : 1;
+    return (size_t)ksplit * n * Nout;
+}
+
+extern "C" dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wT, const float *bias, float *out, float *scratch,
+                                                int n, int Nin, int Nout, int act, int *status)
+{
+    if (!dRk_tensor_fc_supported(n, Nin, Nout) || !scratch) return NULL;
+    if (((uintptr_t)in % 16) || ((uintptr_t)wT % 16) || ((uintptr_t)scratch % 16)) return NULL;
+    PFN_encodeTiled enc = get_encode();
+    if (!enc) return NULL;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    dRk_TensorFcPlan *fp = (dRk_TensorFcPlan *)calloc(1, sizeof(dRk_TensorFcPlan));
+    dRk_TensorConvPlan *pl = &fp->conv;
+    UmmaParams &p = pl->p;
+    p.n = n; p.W = 1; p.H = 1; p.Cin = Nin; p.Cout = Nout;
+    p.taps = 1; p.kw = 1; p.pad = 0; p.kslabs = Nin / BK;
+    p.S = 0; p.TW = BM; p.TH = 1; p.tiles_x = p.tiles_y = 1;
+    p.total_sub = n; p.m_tiles = 1; p.n_tiles = Nout / 256;
+    p.bias = NULL; p.out = scratch; p.ldo = Nout; p.coff = 0; p.act = 0; p.pool = 0; p.status = status;
+    p.ksplit = sms / p.n_tiles;
+    if (p.ksplit < 1) p.ksplit = 1;
+    if (p.ksplit > p.kslabs / 8) p.ksplit = p.kslabs / 8 > 0 ? p.kslabs / 8 : 1;
+    p.kper = (p.kslabs + p.ksplit - 1) / p.ksplit;
+    p.ksplit = (p.kslabs + p.kper - 1) / p.kper;          /* no empty parts */
+    p.split_stride = (long long)n * Nout;
+    pl->BN = 256;
+    p.stage_tx = A_STAGE_BYTES + 256 * BK * 4;
+    const cuuint32_t ones[2] = {1, 1};
+    const cuuint64_t adims[2] = {(cuuint64_t)Nin, (cuuint64_t)n}, astr[1] = {(cuuint64_t)Nin * 4};
+    const cuuint32_t abox[2] = {BK, BM};
+    CUresult r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)in, adims, astr, abox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const cuuint64_t bdims[2] = {(cuuint64_t)Nin, (cuuint64_t)Nout};
+    const cuuint32_t bbox[2] = {BK, 256};
+    if (r == CUDA_SUCCESS)
+        r = enc(&pl->mapB, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)wT, bdims, astr, bbox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { fprintf(stderr, "tensor fc plan: tensor map rejected (%d)\n", (int)r); free(fp); return NULL; }
+    const long long tiles = (long long)p.n_tiles * p.ksplit;
+    pl->grid = (int)(tiles < sms ? tiles : sms);
+    fp->bias = bias; fp->out = out; fp->scratch = scratch; fp->n = n; fp->Nout = Nout; fp->act = act;
+    return fp;
+}
+
+extern "C" int dRk_tensor_fc_run(dRk_stream stream, dRk_TensorFcPlan *fp)
+{
+    if (!fp) return -1;
+    int rc = launch_umma<256>(drk_stream(stream), &fp->conv);
+    if (rc) return rc;
+    return drk_fc_reduce_launch(drk_stream(stream), fp->scratch, fp->bias, fp->out, fp->n * fp->Nout, fp->Nout, fp->conv.p.ksplit, fp->act);
+}
+
+extern "C" void dRk_tensor_fc_free(dRk_TensorFcPlan *fp) { free(fp); }

@@ -115,6 +115,17 @@ dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float *wT, const
 int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *plan);
 void dRk_tensor_conv_free(dRk_TensorConvPlan *plan);
 
+/* Fully connected layer on the tensor cores (TF32 inputs, FP32 accumulate) for batches of 16..128 with
+ * Nin % 32 == 0 and Nout % 256 == 0: split-K flat GEMM + the reduce step of dRk_fc_f32.  wT is [Nout][Nin]
+ * (K contiguous); scratch holds dRk_tensor_fc_scratch_floats() floats.  Same reference kernels as dRk_fc_f32. */
+typedef struct dRk_TensorFcPlan dRk_TensorFcPlan;
+int dRk_tensor_fc_supported(int n, int Nin, int Nout);
+size_t dRk_tensor_fc_scratch_floats(int n, int Nin, int Nout);
+dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wT, const float *bias, float *out, float *scratch,
+                                     int n, int Nin, int Nout, int act, int *status);
+int dRk_tensor_fc_run(dRk_stream stream, dRk_TensorFcPlan *plan);
+void dRk_tensor_fc_free(dRk_TensorFcPlan *plan);
+
 /* Number of kernel launches issued through this ABI by the calling thread since the last reset. */
 long dRk_launch_count(void);
 void dRk_launch_count_reset(void);

@@ -102,3 +102,15 @@ def test_conv_with_fused_maxpool_matches_oracle(n, cin, cout, h, w):
             assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
     assert rel_err(res[True], ref) <= TOL_TF32
     assert np.array_equal(res[True], res[False])        # same accumulators, max commutes with bias + ReLU
+
+
+@pytest.mark.parametrize("n,c,h,w,nout,act", [(64, 64, 4, 4, 256, 1), (16, 512, 7, 7, 512, 0), (33, 32, 2, 8, 768, 1)])
+def test_tensor_fc_matches_oracle(n, c, h, w, nout, act):
+    """TF32 mode, batch >= 16: fully connected layers run as a split-K GEMM on the tensor cores."""
+    x, wt, b = cases.fc_case("tfc_%d_%d" % (c * h * w, nout), n, c, h, w, nout, True)
+    ref = oracle.fc(x, wt, b, act)
+    (got,) = run_graph(lambda g, f: dr.Fully_Connected(f[0], [c * h * w, nout], "relu" if act else "linear", wt, b), [x], math="tf32")
+    assert rel_err(got, ref) <= TOL_TF32
+    (exact,) = run_graph(lambda g, f: dr.Fully_Connected(f[0], [c * h * w, nout], "relu" if act else "linear", wt, b), [x], math="fp32")
+    assert rel_err(exact, ref) <= 1e-4
+    assert not np.array_equal(got, exact)       # the two arithmetic classes really are different kernels
