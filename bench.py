@@ -106,6 +106,7 @@ def build_net(dr, nets, env, net, batch, math, size):
         x, out = nets.squeezenet11(g, size=size)
     dr.mark_as_output(out)
     dr.lib.dR_setInterfaceLayout(g.ptr, 1)     # synthetic inputs are N-HWC: no layout conversion in the timed region
+    g.feed_overlap = True                      # e2e: the next batch's H2D copy runs on a second stream under the current batch's kernels
     return g, x, out
 
 
@@ -113,15 +114,10 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    dist = None
-    if world > 1:
-        import torch
-        import torch.distributed as dist
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from deepracin_b200 import replicas
+    dist = replicas.init("nccl") if world > 1 else None
     import deepracin_b200 as dr
     import nets
-    from ctypes import c_void_p
 
     lib = dr.lib
     size = 224
@@ -149,12 +145,7 @@ def run_ours(args):
                 torch.cuda.synchronize()
 
         def reduce_max(v):
-            if dist is None:
-                return v
-            import torch
-            t = torch.tensor([v], dtype=torch.float64, device="cuda")
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            return float(t.item())
+            return replicas.max_over_ranks(dist, v, cuda=True)
 
         for _ in range(args.warmup):
             if not lib.dR_apply(g.ptr):
@@ -187,6 +178,7 @@ def run_ours(args):
         ms_e2e = reduce_max(ms_e2e)
         status = lib.dR_getDeviceStatus(g.ptr)
         probs = host_out.reshape(batch, nclass).copy()
+        all_probs = replicas.gather_outputs(dist, probs, batch * world, cuda=True)      # outputs of every replica, in image order
         launches_per_apply = lib.dR_getLaunchCount(g.ptr)
 
         line = None
@@ -234,15 +226,13 @@ def run_ours(args):
                 "gpu_launches": launches_per_apply * args.steps,
                 "clocks": clocks, "roofline": roof,
                 "conv_tflops": achieved, "device_status": status,
-                "top1_sample": [int(v) for v in probs.argmax(1)[:4]],
+                "top1_sample": [int(v) for v in probs.argmax(1)[:4]], "gathered_outputs": list(all_probs.shape),
             }
             if world == 1 and not args.no_cpu_baseline:
                 line["cpu_baseline"] = cpu_baseline(args.net, budget_s=args.cpu_budget)
         lib.dR_freePinned(pin_in)
         lib.dR_freePinned(pin_out)
-    if dist is not None:
-        dist.barrier()
-        dist.destroy_process_group()
+    replicas.finish(dist)
     if line is not None:
         print(json.dumps(line))
 

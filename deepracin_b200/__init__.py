@@ -10,7 +10,8 @@ fed [C][H][W] buffers and weights are transposed HWIO -> [Cin][Cout][kh][kw]
 (__init__.py.in:458-462, 487-489, 559-562).
 
 Additions: ``Graph.batch`` (images per ``apply``; arrays gain a leading batch axis),
-``Graph.math`` ('fp32' | 'tf32'), ``Graph.conv_algo``, ``Graph.autotune``.
+``Graph.math`` ('fp32' | 'tf32'), ``Graph.conv_algo``, ``Graph.autotune``, ``Graph.cuda_graph``,
+``Graph.feed_overlap``.
 
 All computation happens in ``libdeepracin.so`` on the GPU; there is no CPU path here.
 """
@@ -83,6 +84,7 @@ class Graph:
         self.autotune = False
         self.fuse = True
         self.cuda_graph = False
+        self.feed_overlap = False
         self.prepared = False
 
     def gpu_ms(self, iterations=1):
@@ -149,6 +151,7 @@ def prepare(graph):
     lib.dR_setAutotune(graph.ptr, 1 if graph.autotune else 0)
     lib.dR_setFusion(graph.ptr, 1 if graph.fuse else 0)
     lib.dR_setCudaGraph(graph.ptr, 1 if graph.cuda_graph else 0)
+    lib.dR_setFeedOverlap(graph.ptr, 1 if graph.feed_overlap else 0)
     if env.graph_with_cl_context == -1:
         model_path = graph.model_path if graph.model_path is not None else env.model_path
         os.makedirs(model_path, exist_ok=True)

@@ -72,6 +72,7 @@ _SIGS = {
     "dR_setAutotune": (c_int, [c_void_p, c_int]),
     "dR_setFusion": (c_int, [c_void_p, c_int]),
     "dR_setCudaGraph": (c_int, [c_void_p, c_int]),
+    "dR_setFeedOverlap": (c_int, [c_void_p, c_int]),
     "dR_setDevice": (c_int, [c_void_p, c_int]),
     "dR_synchronize": (c_int, [c_void_p]),
     "dR_applyTimed": (c_double, [c_void_p, c_int]),

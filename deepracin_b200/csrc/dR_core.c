@@ -118,7 +118,9 @@ gboolean dR_datafeednode_allocateBuffers(dR_Graph *net, dR_Node *layer)
 {
     /* the interface buffer; user-supplied buffers (dR_setDataFeedNodeBuffer) are left alone */
     if (layer->outputBuf->outputBuf) return TRUE;
-    return dR_createFloatBufferL(net, &layer->outputBuf->buf, (size_t)layer->outputBuf->size * net->config->batchSize);
+    if (!dR_createFloatBufferL(net, &layer->outputBuf->buf, (size_t)layer->outputBuf->size * net->config->batchSize)) return FALSE;
+    if (net->config->feedOverlap && !net->config->useCudaGraph) return dR_feedOverlapInit(net, layer);
+    return TRUE;
 }
 
 gint32 dR_datafeednode_getRequiredOutputBufferSize(dR_Node *layer)
@@ -409,6 +411,7 @@ gboolean dR_generateAndCompileKernels(dR_Graph *net)
 /* reference src/dR_core.c:421-459 */
 void dR_cleanupBuffers(dR_Graph *net)
 {
+    for (dR_ListElement *e = net->feed_layers->first; e; e = e->next) dR_feedOverlapCleanup(net, (dR_Node *)e->element);
     for (dR_ListElement *e = net->streamBufferHandlers->first; e; e = e->next) {
         dR_MemoryHandler *h = (dR_MemoryHandler *)e->element;
         if (!h->outputBuf && h->buf) { dR_clMemoryBufferCleanup(net, h->buf); h->buf = NULL; }

@@ -198,6 +198,7 @@ extern "C" gboolean dR_cleanupCL(dR_Graph *net)
     dR_ClConfig *c = net->clConfig;
     if (c->cleanupDone) return TRUE;
     if (c->evStart) { cudaEventDestroy((cudaEvent_t)c->evStart); cudaEventDestroy((cudaEvent_t)c->evStop); c->evStart = c->evStop = NULL; }
+    if (c->copyStream) { cudaStreamDestroy((cudaStream_t)c->copyStream); c->copyStream = NULL; }
     if (c->ownsStream && c->clCommandQueue) cudaStreamDestroy(streamOf(net));
     c->clCommandQueue = NULL;
     g_free(c->clDeviceName);
@@ -267,4 +268,81 @@ extern "C" gint dR_getDeviceStatus(dR_Graph *net)
     if (st[0]) dR_zeroBuffer(net, net->statusWord, 4);
     net->deviceStatus = st[0];
     return st[0];
+}
+
+/* --------------------------------------------------------------- double-buffered feeding */
+extern "C" gboolean dR_feedOverlapInit(dR_Graph *net, dR_Node *feed)
+{
+    dR_DataFeedNode_Data *d = (dR_DataFeedNode_Data *)feed->layer;
+    dR_ClConfig *c = net->clConfig;
+    if (net->config->dryRun) return TRUE;
+    if (!c->copyStream) {
+        cudaStream_t s;
+        if (!check(net, cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "cudaStreamCreate (copy stream)")) return FALSE;
+        c->copyStream = s;
+    }
+    d->feedBuf[0] = feed->outputBuf->buf;
+    if (!dR_createFloatBufferL(net, &d->feedBuf[1], (size_t)feed->outputBuf->size * net->config->batchSize)) return FALSE;
+    for (int i = 0; i < 2; i++) {
+        cudaEvent_t a, b;
+        if (!check(net, cudaEventCreateWithFlags(&a, cudaEventDisableTiming), "cudaEventCreate") ||
+            !check(net, cudaEventCreateWithFlags(&b, cudaEventDisableTiming), "cudaEventCreate")) return FALSE;
+        d->evReady[i] = a; d->evFree[i] = b;
+        cudaEventRecord(b, streamOf(net));      /* both buffers start out free */
+    }
+    d->current = 0; d->pending = -1;
+    return TRUE;
+}
+
+extern "C" gboolean dR_feedOverlapCopy(dR_Graph *net, dR_Node *feed, void *src, size_t numBytes)
+{
+    dR_DataFeedNode_Data *d = (dR_DataFeedNode_Data *)feed->layer;
+    cudaStream_t cs = (cudaStream_t)net->clConfig->copyStream;
+    const int idx = d->pending >= 0 ? d->pending : (d->current ^ 1);   /* a second feed before an apply overwrites the pending one */
+    if (!check(net, cudaStreamWaitEvent(cs, (cudaEvent_t)d->evFree[idx], 0), "cudaStreamWaitEvent")) return FALSE;
+    if (!check(net, cudaMemcpyAsync(d->feedBuf[idx], src, numBytes, cudaMemcpyHostToDevice, cs), "cudaMemcpyAsync H2D (copy stream)")) return FALSE;
+    if (!check(net, cudaEventRecord((cudaEvent_t)d->evReady[idx], cs), "cudaEventRecord")) return FALSE;
+    d->pending = idx;
+    return TRUE;
+}
+
+extern "C" gboolean dR_feedOverlapBeforeApply(dR_Graph *net)
+{
+    for (dR_ListElement *e = net->feed_layers->first; e; e = e->next) {
+        dR_Node *f = (dR_Node *)e->element;
+        dR_DataFeedNode_Data *d = (dR_DataFeedNode_Data *)f->layer;
+        if (!d->evReady[0] || d->pending < 0) continue;
+        if (!check(net, cudaStreamWaitEvent(streamOf(net), (cudaEvent_t)d->evReady[d->pending], 0), "cudaStreamWaitEvent")) return FALSE;
+        d->current = d->pending;
+        d->pending = -1;
+        f->outputBuf->buf = d->feedBuf[d->current];
+        f->outputBuf->bufptr = &f->outputBuf->buf;
+    }
+    return TRUE;
+}
+
+extern "C" gboolean dR_feedOverlapAfterApply(dR_Graph *net)
+{
+    for (dR_ListElement *e = net->feed_layers->first; e; e = e->next) {
+        dR_DataFeedNode_Data *d = (dR_DataFeedNode_Data *)((dR_Node *)e->element)->layer;
+        if (!d->evReady[0]) continue;
+        if (!check(net, cudaEventRecord((cudaEvent_t)d->evFree[d->current], streamOf(net)), "cudaEventRecord")) return FALSE;
+    }
+    return TRUE;
+}
+
+extern "C" void dR_feedOverlapCleanup(dR_Graph *net, dR_Node *feed)
+{
+    dR_DataFeedNode_Data *d = (dR_DataFeedNode_Data *)feed->layer;
+    if (!d->evReady[0]) return;
+    if (net->clConfig->copyStream) cudaStreamSynchronize((cudaStream_t)net->clConfig->copyStream);
+    for (int i = 0; i < 2; i++) {
+        cudaEventDestroy((cudaEvent_t)d->evReady[i]);
+        cudaEventDestroy((cudaEvent_t)d->evFree[i]);
+        d->evReady[i] = d->evFree[i] = NULL;
+    }
+    /* the stream-buffer list frees whichever buffer the handler currently points at; free the other one here */
+    cl_mem other = d->feedBuf[0] == feed->outputBuf->buf ? d->feedBuf[1] : d->feedBuf[0];
+    if (other) cudaFree(other);
+    d->feedBuf[0] = d->feedBuf[1] = NULL;
 }

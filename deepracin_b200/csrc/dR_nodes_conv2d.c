@@ -16,6 +16,8 @@ typedef struct {
     cl_mem wbuf[5];                 /* packed weights per dR_ConvAlgo */
     dRk_TensorConvPlan *plan;       /* tensor path: TMA descriptors for this layer's buffers */
     gboolean fusedPool;             /* the following 2x2/2 max pooling is evaluated in this node's epilogue */
+    const float *planSrc;           /* buffers the plan's tensor maps were encoded for */
+    float *planDst;
 } dR_ConvDevice;
 
 static dR_ConvDevice *dev(dR_Conv2d_Data *c) { return (dR_ConvDevice *)c->tmaDescs; }
@@ -306,7 +308,9 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
                                                          c->shape.s2, c->shape.s3, act, in->act_cstride, layer->act_cstride, layer->act_coffset);
         break;
     case DR_CONV_TENSOR:
+        if (d->plan && (d->planSrc != src || d->planDst != dst)) { dRk_tensor_conv_free(d->plan); d->plan = NULL; }     /* buffers moved (alternating feed buffers) */
         if (!d->plan) {
+            d->planSrc = src; d->planDst = dst;
             d->plan = dRk_tensor_conv_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR], bias, dst, n, W, H, c->shape.s2, c->shape.s3,
                                            c->shape.s0, c->shape.s1, act, layer->act_cstride, layer->act_coffset, d->fusedPool ? 1 : 0, (int *)net->statusWord);
             if (!d->plan) { g_print("Conv2d Layer %d: tensor-core plan could not be built\n", layer->layerID); return FALSE; }

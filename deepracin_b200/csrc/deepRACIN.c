@@ -202,8 +202,10 @@ gboolean dR_apply(dR_Graph *net)
             if (!dR_captureEnd(net) || !ok) return FALSE;
         }
         if (!dR_captureLaunch(net)) return FALSE;
-    } else if (!launchSchedule(net)) {
-        return FALSE;
+    } else {
+        if (net->config->feedOverlap && !dR_feedOverlapBeforeApply(net)) return FALSE;
+        if (!launchSchedule(net)) return FALSE;
+        if (net->config->feedOverlap && !dR_feedOverlapAfterApply(net)) return FALSE;
     }
     if (net->config->profilingGPU) {
         g_print("GPU Profiling: Sum of all kernel run times: %2.3fms \n", net->clConfig->totalKernelGPUTime);
@@ -325,6 +327,7 @@ gboolean dR_setGraphConvAlgo(dR_Graph *net, gint algo)
 
 gboolean dR_setAutotune(dR_Graph *net, gboolean on) { if (!beforePrepare(net, "dR_setAutotune")) return FALSE; net->config->autotune = on; return TRUE; }
 gboolean dR_setFusion(dR_Graph *net, gboolean on) { if (!beforePrepare(net, "dR_setFusion")) return FALSE; net->config->fuseGraph = on; return TRUE; }
+gboolean dR_setFeedOverlap(dR_Graph *net, gboolean on) { if (!beforePrepare(net, "dR_setFeedOverlap")) return FALSE; net->config->feedOverlap = on; return TRUE; }
 gboolean dR_setCudaGraph(dR_Graph *net, gboolean on) { if (!beforePrepare(net, "dR_setCudaGraph")) return FALSE; net->config->useCudaGraph = on; return TRUE; }
 
 gboolean dR_setDevice(dR_Graph *net, gint ordinal)
@@ -369,6 +372,8 @@ gint dR_getLaunchCount(dR_Graph *net)
 gboolean dR_feedDataAsync(dR_Graph *net, dR_Node *feednode, gfloat *pinned, size_t numfloats)
 {
     if (!net->prepared || !feednode || feednode->type != tDataFeedNode) return FALSE;
+    if (net->config->feedOverlap && ((dR_DataFeedNode_Data *)feednode->layer)->evReady[0])
+        return dR_feedOverlapCopy(net, feednode, pinned, numfloats * sizeof(cl_float));
     return dR_uploadArrayAsync(net, pinned, numfloats * sizeof(cl_float), *feednode->outputBuf->bufptr);
 }
 

@@ -43,6 +43,10 @@ gdouble dR_getNodeGpuMs(dR_Node *node);
 gint dR_getLaunchCount(dR_Graph *net);
 /* Non-zero if a kernel reported a device-side status (bounded wait ran out, ...) since the last call. */
 gint dR_getDeviceStatus(dR_Graph *net);
+/* Double-buffered feeding: dR_feedDataAsync copies on a second stream into the feed node's other interface
+ * buffer while the previous batch is still being computed; the next dR_apply waits for that copy and reads it.
+ * Before dR_prepare; not combined with CUDA-graph replay or caller-supplied feed buffers. */
+gboolean dR_setFeedOverlap(dR_Graph *net, gboolean on);
 /* Feed / fetch with pinned host memory and no implicit synchronisation. */
 gboolean dR_feedDataAsync(dR_Graph *net, dR_Node *feednode, gfloat *pinned, size_t numfloats);
 gboolean dR_fetchOutputAsync(dR_Graph *net, gint outputIndex, gfloat *pinned, size_t numfloats);

@@ -52,6 +52,12 @@ void dR_hostFreePinned(void *p);
 /* Non-blocking copies on the graph's stream (host memory should be pinned). */
 gboolean dR_uploadArrayAsync(dR_Graph *net, void *srcHostMem, size_t numBytes, cl_mem destDeviceMem);
 gboolean dR_downloadArrayAsync(dR_Graph *net, cl_mem srcDeviceMem, size_t numBytes, void *destHostMem);
+/* Double-buffered feeding (see dR_setFeedOverlap): second stream + events, copy, and the two hooks dR_apply calls. */
+gboolean dR_feedOverlapInit(dR_Graph *net, dR_Node *feed);
+gboolean dR_feedOverlapCopy(dR_Graph *net, dR_Node *feed, void *srcHostMem, size_t numBytes);
+gboolean dR_feedOverlapBeforeApply(dR_Graph *net);
+gboolean dR_feedOverlapAfterApply(dR_Graph *net);
+void dR_feedOverlapCleanup(dR_Graph *net, dR_Node *feed);
 /* device-side memset of floats to zero on the stream */
 gboolean dR_zeroBuffer(dR_Graph *net, cl_mem mem, size_t numFloats);
 /* Timing helpers for the autotuner: record start/stop on the stream, return elapsed ms. */

@@ -84,6 +84,12 @@ struct dR_DataFeedNode_Data {
     dR_Shape3 shape;
     cl_mem dataBuffer;
     dR_List *next_layers;
+    /* ---- b200 additions: double-buffered feeding (dR_setFeedOverlap) ---- */
+    cl_mem feedBuf[2];       /* the two interface buffers the copy stream alternates between */
+    void *evReady[2];        /* copy into feedBuf[i] finished (recorded on the copy stream) */
+    void *evFree[2];         /* the apply that read feedBuf[i] finished (recorded on the compute stream) */
+    gint current;            /* buffer the graph reads in the next apply */
+    gint pending;            /* buffer a dR_feedDataAsync filled since the last apply, or -1 */
 };
 
 struct dR_Node {
@@ -157,6 +163,7 @@ struct dR_ClConfig {
     /* ---- b200 additions ---- */
     gboolean ownsStream;               /* stream was created by dR_initCL (destroyed at cleanup) */
     void *evStart, *evStop;            /* cudaEvent_t pair for per-node profiling */
+    void *copyStream;                  /* second stream for overlapped feeds */
     gint smCount;
     size_t smemPerBlockOptin;
 };
@@ -177,6 +184,7 @@ struct dR_Config {
     gboolean autotune;       /* time the legal conv variants per layer during dR_prepare */
     gboolean fuseGraph;      /* enable concat elision / preamble folding */
     gboolean useCudaGraph;   /* replay the node schedule from a captured CUDA graph */
+    gboolean feedOverlap;    /* dR_feedDataAsync copies on a second stream into alternating buffers */
     gboolean dryRun;         /* plan only: no device is touched, buffers get placeholder addresses, dR_apply refuses */
     size_t dryRunCursor;
 };
