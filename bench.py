@@ -314,7 +314,7 @@ def cpu_baseline(net, budget_s=20.0, steps=3):
     from oracle import build_oracle
     build_oracle.build_restatement()
     use_ref = oracle.ref_available()
-    cores = os.cpu_count() or 1
+    cores = oracle.set_threads()
     layers = _ref_vgg_layers()
     sample, frac, what = choose_cpu_sample(oracle, layers, use_ref, steps + 1, budget_s)
     t0 = time.time()
@@ -336,7 +336,7 @@ def run_reference(args):
     from oracle import build_oracle
     build_oracle.build_restatement()
     use_ref = oracle.ref_available()
-    cores = os.cpu_count() or 1
+    cores = oracle.set_threads()
     layers = _ref_vgg_layers()
     sample, frac, what = choose_cpu_sample(oracle, layers, use_ref, args.steps + args.warmup + 1, 170.0)
     for _ in range(args.warmup):

@@ -40,6 +40,17 @@ def _c(a):
     return None if a is None else np.ascontiguousarray(a, dtype=np.float32)
 
 
+def set_threads(n=None):
+    """OpenMP thread count of the oracle libraries (default: all host cores).  Launchers such as torchrun
+    export OMP_NUM_THREADS=1, which would silently make the CPU baseline single-threaded."""
+    n = int(n or os.cpu_count() or 1)
+    try:
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(n)
+    except OSError:
+        pass
+    return n
+
+
 def restate_lib():
     global _restate
     if _restate is None:
