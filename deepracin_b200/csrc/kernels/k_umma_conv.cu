@@ -340,7 +340,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                         float4 v;
                         v.x = __uint_as_float(r[j + 0]); v.y = __uint_as_float(r[j + 1]);
                         v.z = __uint_as_float(r[j + 2]); v.w = __uint_as_float(r[j + 3]);
-                        if (p.bias) {
+                        if (p.bias && col + j < p.Cout) {
                             const float4 b = __ldg(reinterpret_cast<const float4 *>(p.bias + col + j));
                             v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
                         }
@@ -551,12 +551,12 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                         float4 v;
                         v.x = __uint_as_float(r[j + 0]); v.y = __uint_as_float(r[j + 1]);
                         v.z = __uint_as_float(r[j + 2]); v.w = __uint_as_float(r[j + 3]);
-                        if (p.bias) {
+                        if (p.bias && col + j < p.Cout) {
                             const float4 b = __ldg(reinterpret_cast<const float4 *>(p.bias + col + j));
                             v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
                         }
                         v.x = drk_act(v.x, p.act); v.y = drk_act(v.y, p.act); v.z = drk_act(v.z, p.act); v.w = drk_act(v.w, p.act);
-                        *reinterpret_cast<float4 *>(dst + c0 + j) = v;
+                        if (col + j < p.Cout) *reinterpret_cast<float4 *>(dst + c0 + j) = v;
                     }
                 }
             }
@@ -836,7 +836,7 @@ extern "C" int dRk_tensor_conv_supported(int W, int H, int Cin, int Cout, int kw
     if (W <= 0 || H <= 0) return 0;
     if (!((kw == 1 && kh == 1) || (kw == 3 && kh == 3))) return 0;
     if (Cin % BK != 0) return 0;
-    if (Cout % 64 != 0) return 0;
+    if (Cout % 4 != 0 || Cout < 64) return 0;          /* rows past Cout are TMA zero fill; the epilogues mask them */
     return 1;
 }
 
@@ -856,20 +856,18 @@ static double swap_fill(int W, int H)
 
 static int pick_bn(int Cout, long long m_tiles, int sms)
 {
-    /* largest N tile that divides Cout, unless a smaller one fills the SMs noticeably better */
-    int best = 0;
+    /* N tile: fewest waves of tiles over the SMs, weighting a tile by its width plus a fixed part (pipeline fill, epilogue tail);
+       a tile wider than what is left of Cout wastes the difference */
+    int best = 64;
     double best_cost = 1e30;
     const int cand[3] = {256, 128, 64};
     for (int i = 0; i < 3; i++) {
         const int bn = cand[i];
-        if (Cout % bn) continue;
-        const long long tiles = m_tiles * (Cout / bn);
+        const long long tiles = m_tiles * ((Cout + bn - 1) / bn);
         const long long waves = (tiles + sms - 1) / sms;
-        /* per-tile cost: main loop ~ bn, plus a fixed part (pipeline fill, epilogue tail) */
         const double cost = (double)waves * (bn + 48.0);
         if (cost < best_cost * 0.97) { best_cost = cost; best = bn; }
     }
-    if (!best) best = Cout % 64 == 0 ? 64 : 32;
     return best;
 }
 
@@ -970,8 +968,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     }
     if (r != CUDA_SUCCESS) { fprintf(stderr, "tensor conv plan: activation tensor map rejected (%d)\n", (int)r); free(pl); return NULL; }
     pl->BN = pl->swap ? BM : pick_bn(Cout, p.m_tiles, sms);
-    if (pl->BN == 32) { free(pl); return NULL; }
-    p.n_tiles = pl->swap ? (Cout + BM - 1) / BM : Cout / pl->BN;
+    p.n_tiles = pl->swap ? (Cout + BM - 1) / BM : (Cout + pl->BN - 1) / pl->BN;
     {
         const cuuint64_t K = (cuuint64_t)p.taps * Cin;
         const cuuint64_t dims[2] = {K, (cuuint64_t)Cout};

@@ -167,3 +167,30 @@ def test_overlapped_feeding_gives_the_same_results_in_order():
     for a, b in zip(outs[False], outs[True]):
         assert np.array_equal(a, b)
     assert not np.array_equal(outs[True][0], outs[True][1])
+
+
+def test_full_size_vgg16_fp32_matches_reference_kernels_and_tf32_agrees(tmp_path):
+    """VGG-16 at its real size (224x224, 13 conv + 3 FC): the FP32 path against the CPU oracle running the same
+    saved model (the reference's own kernels where the reference-built library is present), and the TF32
+    tensor-core path against the FP32 path: logits within the TF32 bound, same top-1."""
+    imgs = nets.synthetic_images("vgg_full", 2, 224)
+    res = {}
+    for math in ("fp32", "tf32"):
+        with dr.Environment() as env:
+            g = env.create_graph("HWC")
+            g.batch = 2
+            g.math = math
+            x, out = nets.vgg16(g, size=224, softmax=False)
+            dr.mark_as_output(out)
+            if math == "fp32":
+                dr.save_graph(g, str(tmp_path))
+            dr.prepare(g)
+            dr.feed_data(x, imgs)
+            res[math] = dr.apply(g)[0].reshape(2, 1000)
+            assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    onodes = ograph.parse_graph(str(tmp_path / "dr_graph_export"))
+    ref = ograph.run_graph(onodes, [np.ascontiguousarray(imgs[:1].transpose(0, 3, 1, 2))], leg="ref").reshape(1, 1000)
+    assert np.all(np.isfinite(ref))
+    assert rel_err(res["fp32"][:1], ref) <= 5e-4                 # 16 layers, each within 1e-4
+    assert rel_err(res["tf32"], res["fp32"]) <= 1e-2             # 13 TF32 layers deep; per layer 3e-3
+    assert np.array_equal(res["tf32"].argmax(1), res["fp32"].argmax(1))

@@ -22,6 +22,9 @@ TENSOR_SHAPES = [
     ("t_odd_13x17", 3, 64, 192, 17, 13, 3),
     ("t_1x1_256_512", 2, 256, 512, 28, 28, 1),
     ("t_1x1_odd", 3, 32, 64, 9, 7, 1),
+    ("t_1x1_1000", 2, 512, 1000, 14, 14, 1),         # Cout not a multiple of the N tile: zero-filled filter rows, masked stores
+    ("t_3x3_cout_72", 2, 32, 72, 28, 28, 3),
+    ("t_3x3_cout_200", 1, 64, 200, 14, 14, 3),
 ]
 
 
