@@ -18,7 +18,6 @@ import os
 import subprocess
 import sys
 import tempfile
-import threading
 import time
 
 import numpy as np
@@ -239,11 +238,8 @@ def run_ours(args):
 
 def per_node_profile(dr, lib, g):
     """One apply with per-kernel events; returns [(kind, ms)] per node."""
-    from deepracin_b200 import Node  # noqa: F401
     res = []
     lib.dR_config(g.ptr, b"", 1, 0, 1, 0, (g.env.model_path).encode())
-    import contextlib
-    import io
     # the C library prints a summary line per apply when profiling; keep stdout clean for the JSON line
     fd = os.dup(1)
     devnull = os.open(os.devnull, os.O_WRONLY)

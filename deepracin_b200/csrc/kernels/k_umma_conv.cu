@@ -928,7 +928,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
         const cuuint32_t box[2] = {BK, BM};
         r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)in, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    } else if (Cout <= BM && swap_fill(W, H) >= 0.8 && !getenv("DRK_NO_SWAP") && !getenv("DRK_NO_HALO")) {
+    } else if (Cout <= BM && swap_fill(W, H) >= 0.8 && !getenv("DRK_NO_SWAP") && !getenv("DRK_NO_HALO")   /* env switches: A/B comparisons of the variants when profiling */) {
         pl->swap = 1;
         p.TW = HALO_TW; p.TH = SWAP_TH; p.S = 1;
         p.tiles_x = (W + HALO_TW - 1) / HALO_TW; p.tiles_y = (H + SWAP_TH - 1) / SWAP_TH;
@@ -952,10 +952,6 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else {
         pick_subtile(W, H, fuse_pool2, &p.TW, &p.TH, &p.S);
-        if (const char *ov = getenv("DRK_TILE")) {          /* experiment hook: "tw,th,s" */
-            int a = 0, b = 0, c = 0;
-            if (!fuse_pool2 && sscanf(ov, "%d,%d,%d", &a, &b, &c) == 3 && a > 0 && b > 0 && c > 0 && (a * b) % 8 == 0 && a * b * c <= BM) { p.TW = a; p.TH = b; p.S = c; }
-        }
         p.tiles_x = (W + p.TW - 1) / p.TW;
         p.tiles_y = (H + p.TH - 1) / p.TH;
         p.total_sub = (long long)n * p.tiles_x * p.tiles_y;

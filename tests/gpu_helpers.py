@@ -42,7 +42,6 @@ def run_graph(build, feeds, batch=None, **opts):
             dr.feed_data(fn, f)
         res = dr.apply(g)
         res = [r.reshape((n, o.out_shape[2], o.out_shape[1], o.out_shape[0])) for r, o in zip(res, outs)]
-        extra = opts.get("_inspect")
         return res
 
 
