@@ -788,6 +788,14 @@ static PFN_encodeTiled get_encode()
     return fn;
 }
 
+#define DRK_MAX_DEVICES 64
+static int current_device()
+{
+    int dev = 0;
+    cudaGetDevice(&dev);
+    return dev >= 0 && dev < DRK_MAX_DEVICES ? dev : 0;
+}
+
 struct dRk_TensorConvPlan {
     CUtensorMap mapA, mapB;
     UmmaParams p;
@@ -874,11 +882,12 @@ static int pick_bn(int Cout, long long m_tiles, int sms)
 template <int BN>
 static int launch_umma_halo(cudaStream_t st, dRk_TensorConvPlan *pl)
 {
-    static bool attr_done = false;
-    if (!attr_done) {
+    static bool attr_done[DRK_MAX_DEVICES];         /* the opt-in shared-memory size is a per-device function attribute */
+    const int dev = current_device();
+    if (!attr_done[dev]) {
         cudaError_t e = cudaFuncSetAttribute(k_umma_conv_halo<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, HaloCfg<BN>::SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        attr_done = true;
+        attr_done[dev] = true;
     }
     k_umma_conv_halo<BN><<<pl->grid, UMMA_THREADS, HaloCfg<BN>::SMEM_BYTES, st>>>(pl->mapA, pl->mapB, pl->p);
     DRK_COUNT_LAUNCH();
@@ -888,11 +897,12 @@ static int launch_umma_halo(cudaStream_t st, dRk_TensorConvPlan *pl)
 template <int BN>
 static int launch_umma(cudaStream_t st, dRk_TensorConvPlan *pl)
 {
-    static bool attr_done = false;
-    if (!attr_done) {
+    static bool attr_done[DRK_MAX_DEVICES];
+    const int dev = current_device();
+    if (!attr_done[dev]) {
         cudaError_t e = cudaFuncSetAttribute(k_umma_conv<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<BN>::SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
-        attr_done = true;
+        attr_done[dev] = true;
     }
     k_umma_conv<BN><<<pl->grid, UMMA_THREADS, Cfg<BN>::SMEM_BYTES, st>>>(pl->mapA, pl->mapB, pl->p);
     DRK_COUNT_LAUNCH();
@@ -985,11 +995,12 @@ extern "C" int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *pl)
     if (!pl) return -1;
     cudaStream_t st = drk_stream(stream);
     if (pl->swap) {
-        static bool attr_done = false;
-        if (!attr_done) {
+        static bool attr_done[DRK_MAX_DEVICES];
+        const int dev = current_device();
+        if (!attr_done[dev]) {
             cudaError_t e = cudaFuncSetAttribute(k_umma_conv_swap, cudaFuncAttributeMaxDynamicSharedMemorySize, SWAP_SMEM);
             if (e != cudaSuccess) return (int)e;
-            attr_done = true;
+            attr_done[dev] = true;
         }
         k_umma_conv_swap<<<pl->grid, UMMA_THREADS, SWAP_SMEM, st>>>(pl->mapA, pl->mapB, pl->p);
         DRK_COUNT_LAUNCH();

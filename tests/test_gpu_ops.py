@@ -274,3 +274,42 @@ def test_profiling_reports_kernel_times(capfd):
     out = capfd.readouterr().out
     assert "GPU Profiling: deepRACIN:conv2d took" in out
     assert "Sum of all kernel run times" in out
+
+
+def test_caller_owned_stream_and_buffers():
+    """dR_setClEnvironment with the caller's CUDA stream, dR_setDataFeedNodeBuffer / dR_setPreexistingOutputBuffer with the
+    caller's device buffers (reference include/deepRACIN.h:72,126,242): nothing is copied, the graph reads and writes them."""
+    import ctypes
+    import torch
+    from ctypes import c_void_p, pointer
+    from deepracin_b200._lib import Shape3, Shape4
+    lib = dr.lib
+    x, wt, b = cases.conv_case("caller_owned", 2, 8, 12, 6, 10, 3)
+    ref = oracle.conv2d(x, wt, b, (1, 1), 1)
+    dev = torch.device("cuda", 0)
+    stream = torch.cuda.Stream(device=dev)
+    xin = torch.from_numpy(x).to(dev)                       # [n, C, H, W]: the reference's interface layout
+    yout = torch.zeros(2, 12, 6, 10, device=dev)
+    g = lib.dR_NewGraph()
+    lib.dR_setBatchSize(g, 2)
+    lib.dR_setClEnvironment(g, None, None, stream.cuda_stream, 0)
+    f = lib.dR_Datafeednode(g, pointer(Shape3(10, 6, 8)))
+    c = lib.dR_Conv2d(g, f, pointer(Shape4(3, 3, 8, 12)), pointer(Shape4(1, 1, 1, 1)), 1, 1)
+    lib.dR_Conv2d_setVariables(c, wt.ctypes.data_as(dr._FP), b.ctypes.data_as(dr._FP))
+    in_ptr, out_ptr = c_void_p(xin.data_ptr()), c_void_p(yout.data_ptr())
+    assert lib.dR_setDataFeedNodeBuffer(g, f, ctypes.byref(in_ptr))
+    assert lib.dR_setPreexistingOutputBuffer(g, c, ctypes.byref(out_ptr))
+    assert lib.dR_prepare(g)
+    torch.cuda.synchronize(dev)
+    assert lib.dR_apply(g)
+    stream.synchronize()
+    assert rel_err(yout.cpu().numpy(), ref) <= TOL_FP32
+    # a new input buffer between applies: only the pointer changes
+    xin2 = torch.from_numpy(np.ascontiguousarray(x[::-1])).to(dev)
+    in_ptr2 = c_void_p(xin2.data_ptr())
+    assert lib.dR_setDataFeedNodeBuffer(g, f, ctypes.byref(in_ptr2))
+    assert lib.dR_apply(g)
+    stream.synchronize()
+    assert rel_err(yout.cpu().numpy(), ref[::-1]) <= TOL_FP32
+    lib.dR_cleanup(g, 0)
+    assert np.array_equal(xin.cpu().numpy(), x)             # caller's buffers survive the cleanup
