@@ -111,8 +111,14 @@ class Environment:
 
     def __exit__(self, type, value, traceback):
         shutil.rmtree(self.tmp_path, ignore_errors=True)
-        for i, graph in enumerate(self.graphs):
-            lib.dR_cleanup(graph.ptr, 1 if i == len(self.graphs) - 1 else 0)
+        # graphs that borrowed the environment's stream go first; the graph that created it tears it down last
+        owner = self.graph_with_cl_context
+        for graph in self.graphs:
+            if graph.id != owner:
+                lib.dR_cleanup(graph.ptr, 0)
+        for graph in self.graphs:
+            if graph.id == owner:
+                lib.dR_cleanup(graph.ptr, 1)
         self.graphs = []
 
     def create_graph(self, interface_layout="HWC"):

@@ -197,6 +197,7 @@ extern "C" gboolean dR_cleanupCL(dR_Graph *net)
 {
     dR_ClConfig *c = net->clConfig;
     if (c->cleanupDone) return TRUE;
+    if (net->config->dryRun) { c->cleanupDone = TRUE; return TRUE; }
     if (c->evStart) { cudaEventDestroy((cudaEvent_t)c->evStart); cudaEventDestroy((cudaEvent_t)c->evStop); c->evStart = c->evStop = NULL; }
     if (c->copyStream) { cudaStreamDestroy((cudaStream_t)c->copyStream); c->copyStream = NULL; }
     if (c->ownsStream && c->clCommandQueue) cudaStreamDestroy(streamOf(net));

@@ -228,6 +228,7 @@ void dR_cleanup(dR_Graph *net, gboolean cleanupcl)
     if (!net->config->silent) g_print("Cleaning up deepRACIN...\n");
     if (net->prepared) { dR_finish(net); dR_cleanupBuffers(net); }
     if (cleanupcl) dR_cleanupCL(net);
+    else if (!net->clConfig->ownsStream) dR_cleanupCL(net);     /* a borrowed stream is never destroyed here; only this graph's events go */
     dR_cleanupNet(net);
 }
 

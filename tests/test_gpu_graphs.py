@@ -25,7 +25,8 @@ def load_kat_images():
 
 
 @pytest.mark.skipif(oracle.staged_squeezenet_dir() is None, reason="pretrained SqueezeNet fixture not staged")
-@pytest.mark.parametrize("opts", [dict(), dict(fuse=False), dict(cuda_graph=True), dict(conv_algo="direct"), dict(autotune=True)])
+@pytest.mark.parametrize("opts", [dict(), dict(fuse=False), dict(cuda_graph=True), dict(conv_algo="direct"), dict(autotune=True),
+                                  dict(math="tf32"), dict(math="tf32", cuda_graph=True), dict(math="tf32", feed_overlap=True)])
 def test_pretrained_squeezenet_known_answers(opts):
     d, imgs = load_kat_images()
     with dr.Environment() as env:
@@ -43,9 +44,11 @@ def test_pretrained_squeezenet_known_answers(opts):
     probs, logits = probs.reshape(2, 1000), logits.reshape(2, 1000)
     assert [int(p.argmax()) for p in probs] == [292, 611]
     assert np.array_equal(probs, probs2.reshape(2, 1000))
+    tf32 = opts.get("math") == "tf32"
     for i, name in enumerate(("tiger", "puzzle")):
-        assert rel_err(logits[i], GOLD["kat_%s_logits" % name]) <= TOL_FP32
-        assert rel_err(probs[i], GOLD["kat_%s_softmax" % name]) <= 5e-4
+        # FP32 kernels: per-layer bound 1e-4; TF32 tensor-core layers: 3e-3 per layer, looser on the softmax
+        assert rel_err(logits[i], GOLD["kat_%s_logits" % name]) <= (1e-2 if tf32 else TOL_FP32)
+        assert rel_err(probs[i], GOLD["kat_%s_softmax" % name]) <= (5e-2 if tf32 else 5e-4)
 
 
 def run_vs_oracle(build, feed_hwc, tmp_path, tol=TOL_FP32, **opts):
