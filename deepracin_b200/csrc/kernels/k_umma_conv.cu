@@ -844,7 +844,7 @@ extern "C" int dRk_tensor_conv_supported(int W, int H, int Cin, int Cout, int kw
     if (W <= 0 || H <= 0) return 0;
     if (!((kw == 1 && kh == 1) || (kw == 3 && kh == 3))) return 0;
     if (Cin % BK != 0) return 0;
-    if (Cout % 4 != 0 || Cout < 64) return 0;          /* rows past Cout are TMA zero fill; the epilogues mask them */
+    if (Cout % 4 != 0 || Cout < 16) return 0;          /* rows past Cout are TMA zero fill; the epilogues mask them */
     return 1;
 }
 

@@ -24,6 +24,10 @@ TENSOR_SHAPES = [
     ("t_1x1_odd", 3, 32, 64, 9, 7, 1),
     ("t_1x1_1000", 2, 512, 1000, 14, 14, 1),         # Cout not a multiple of the N tile: zero-filled filter rows, masked stores
     ("t_3x3_cout_72", 2, 32, 72, 28, 28, 3),
+    ("t_1x1_squeeze_16", 2, 64, 16, 56, 56, 1),      # SqueezeNet squeeze layers: fewer output channels than any N tile
+    ("t_1x1_squeeze_48", 3, 256, 48, 14, 14, 1),
+    ("t_3x3_cout_16", 1, 32, 16, 28, 28, 3),
+    ("t_3x3_cout_48_swap", 1, 64, 48, 28, 32, 3),
     ("t_3x3_cout_200", 1, 64, 200, 14, 14, 3),
 ]
 
