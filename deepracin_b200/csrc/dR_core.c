@@ -222,7 +222,7 @@ gboolean dR_planFusion(dR_Graph *net)
     }
     for (dR_ListElement *e = net->scheduledLayers->first; e; e = e->next) {
         dR_Node *l = (dR_Node *)e->element;
-        l->elided = FALSE; l->act_coffset = 0; l->act_cstride = l->oshape.s2;
+        l->elided = FALSE; l->fusedAway = FALSE; l->act_coffset = 0; l->act_cstride = l->oshape.s2;
     }
     if (!net->config->fuseGraph) return TRUE;
     for (dR_ListElement *e = net->scheduledLayers->first; e; e = e->next) {
@@ -230,7 +230,9 @@ gboolean dR_planFusion(dR_Graph *net)
         if (l->type != tConcat) continue;
         dR_Concat_Data *c = (dR_Concat_Data *)l->layer;
         c->elidedCopy = FALSE;
+        c->fusedGather = FALSE;
         if (c->concatDim != 2) continue;
+        if (dR_concat_planGather(l)) continue;
         gboolean ok = TRUE;
         for (dR_ListElement *p = l->previous_layers->first; p; p = p->next) {
             dR_Node *in = (dR_Node *)p->element;

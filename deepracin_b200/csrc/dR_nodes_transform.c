@@ -191,11 +191,75 @@ gboolean dR_concat_fillBuffers(dR_Graph *net, dR_Node *layer) { return noop(net,
 gboolean dR_concat_cleanupBuffers(dR_Graph *net, dR_Node *layer) { return noop(net, layer); }
 gboolean dR_concat_cleanupLayer(dR_Graph *net, dR_Node *layer) { return freeData(net, layer); }
 
+/* Walks one Concat input back through single-consumer scalar element-wise nodes to a full-frame Slice.
+ * Returns the slice node (ops filled source-to-sink) or NULL if the chain has any other shape. */
+static dR_Node *gatherChain(dR_Node *in, gint ops[4], gfloat scalars[4], gint *nops)
+{
+    gint rev[4]; gfloat rs[4]; gint n = 0;
+    dR_Node *nd = in;
+    while (nd->type == tElemWise1Op) {
+        dR_ElemWise1Op_Data *e = (dR_ElemWise1Op_Data *)nd->layer;
+        if (n == 4 || nd->output || nd->next_layers->length != 1 || e->op > tDivS) return NULL;
+        rev[n] = e->op; rs[n] = e->scalar; n++;
+        nd = dR_firstInput(nd);
+    }
+    if (nd->type != tSlice || nd->output || nd->next_layers->length != 1) return NULL;
+    dR_Slice_Data *sl = (dR_Slice_Data *)nd->layer;
+    if (sl->origin.s0 != 0 || sl->origin.s1 != 0 || sl->oshape.s0 != sl->ishape.s0 || sl->oshape.s1 != sl->ishape.s1) return NULL;
+    for (gint k = 0; k < n; k++) { ops[k] = rev[n - 1 - k]; scalars[k] = rs[n - 1 - k]; }
+    *nops = n;
+    return nd;
+}
+
+gboolean dR_concat_planGather(dR_Node *layer)
+{
+    dR_Concat_Data *d = (dR_Concat_Data *)layer->layer;
+    gint ops[4], nops; gfloat sc[4];
+    if (d->concatDim != 2 || layer->oshape.s2 > DRK_CHANNEL_MAP_MAX) return FALSE;
+    for (gint i = 0; i < d->n; i++)
+        if (!gatherChain(dR_nthInput(layer, i), ops, sc, &nops)) return FALSE;
+    for (gint i = 0; i < d->n; i++) {       /* the chain nodes compute nothing on their own any more */
+        dR_Node *nd = dR_nthInput(layer, i);
+        while (nd->type == tElemWise1Op) { nd->fusedAway = TRUE; nd = dR_firstInput(nd); }
+        nd->fusedAway = TRUE;
+    }
+    d->fusedGather = TRUE;
+    return TRUE;
+}
+
+static gboolean concatGather(dR_Graph *net, dR_Node *layer)
+{
+    dR_Concat_Data *d = (dR_Concat_Data *)layer->layer;
+    drk_ChannelMap m;
+    gint j = 0;
+    memset(&m, 0, sizeof m);
+    for (gint i = 0; i < d->n; i++) {
+        gint ops[4], nops; gfloat sc[4];
+        dR_Node *sl = gatherChain(dR_nthInput(layer, i), ops, sc, &nops);
+        if (!sl) return FALSE;
+        dR_Slice_Data *sd = (dR_Slice_Data *)sl->layer;
+        dR_Node *src = dR_firstInput(sl);
+        for (gint c = 0; c < sd->oshape.s2; c++, j++) {
+            m.src[j] = dR_actPtr(src) + src->act_coffset;
+            m.ld[j] = src->act_cstride;
+            m.ch[j] = sd->origin.s2 + c;
+            m.nops[j] = nops;
+            for (gint k = 0; k < nops; k++) { m.op[j][k] = ops[k]; m.scalar[j][k] = sc[k]; }
+        }
+    }
+    m.cout = j;
+    dR_beginCLKernel(net);
+    net->clConfig->clError = dRk_channel_map(net->clConfig->clCommandQueue, &m, dR_actPtr(layer),
+                                             (size_t)net->config->batchSize * layer->oshape.s0 * layer->oshape.s1);
+    return dR_finishCLKernel(net, "deepRACIN:concatGather");
+}
+
 /* reference src/dR_nodes_transform.c:346-375; nothing to launch when the producers already wrote in place */
 gboolean dR_concat_compute(dR_Graph *net, dR_Node *layer)
 {
     dR_Concat_Data *d = (dR_Concat_Data *)layer->layer;
     if (d->elidedCopy) return TRUE;
+    if (d->fusedGather) return concatGather(net, layer);
     gint off = 0;
     dR_beginCLKernel(net);
     for (gint i = 0; i < d->n; i++) {

@@ -172,6 +172,7 @@ static gboolean launchSchedule(dR_Graph *net)
     }
     for (dR_ListElement *e = net->scheduledLayers->first; e; e = e->next) {
         dR_Node *l = (dR_Node *)e->element;
+        if (l->fusedAway) continue;                 /* evaluated inside a consumer's kernel */
         const gdouble before = net->clConfig->totalKernelGPUTime;
         if (!l->compute(net, l)) { g_print("Execution of layer %d failed \n", l->layerID); return FALSE; }
         if (net->config->profilingGPU) l->lastGpuMs = net->clConfig->totalKernelGPUTime - before;

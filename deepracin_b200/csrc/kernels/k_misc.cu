@@ -288,3 +288,28 @@ extern "C" int dRk_concat_place(dRk_stream s, const float *in, float *out, int n
     if (dim < 0 || dim > 2) return -1;
     return copy_box(s, in, out, n, w, h, c, ldi, 0, 0, 0, w, h, c, W, H, C, dim == 0 ? off : 0, dim == 1 ? off : 0, dim == 2 ? off : 0);
 }
+
+/* ------------------------------------------------ fused channel gather + scalar ops
+ * out[pixel][j] = f_j(src_j[pixel*ld_j + ch_j]) where f_j is a short chain of the scalar element-wise ops,
+ * applied one after the other exactly as the separate kernels would.  One launch replaces the
+ * Slice -> ElemWise1Op ... -> Concat preamble of the reference's example graphs (per-channel mean
+ * subtraction and channel reordering: examples/squeezenet-v1.1/squeezenet_whole/graph.dr:7-41). */
+__global__ void k_channel_map(drk_ChannelMap m, float *__restrict__ out, size_t pixels)
+{
+    const size_t total = pixels * m.cout;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int j = (int)(i % m.cout);
+        const size_t p = i / m.cout;
+        float v = m.src[j][p * m.ld[j] + m.ch[j]];
+        for (int k = 0; k < m.nops[j]; k++) v = ew1(v, m.op[j][k], m.scalar[j][k]);
+        out[i] = v;
+    }
+}
+
+extern "C" int dRk_channel_map(dRk_stream s, const drk_ChannelMap *map, float *out, size_t pixels)
+{
+    if (!map || map->cout < 1 || map->cout > DRK_CHANNEL_MAP_MAX || pixels == 0) return -1;
+    k_channel_map<<<drk_blocks(pixels * map->cout, 256, 148u * 16u), 256, 0, drk_stream(s)>>>(*map, out, pixels);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}

@@ -39,6 +39,7 @@
 
 struct UmmaParams {
     int n, W, H, Cin, Cout;
+    int CinPad;                     /* Cin rounded up to whole 32-channel slabs: the K pitch of one tap in the packed filters */
     int taps, kw, pad;              /* 1 or 9 taps; kw = 1 or 3 */
     int TW, TH, S;                  /* sub-box geometry (3x3); S = 0: flat 1x1 mode */
     int tiles_x, tiles_y;           /* sub-boxes per image */
@@ -230,7 +231,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                                 tma_load_4d(sa + q * sub_bytes, &mapA, ks * BK, txi * p.TW + kx - p.pad, tyi * p.TH + ky - p.pad, img, full_bar(stage));
                             }
                         }
-                        tma_load_2d(sb, &mapB, tap * p.Cin + ks * BK, nt * BN, full_bar(stage));
+                        tma_load_2d(sb, &mapB, tap * p.CinPad + ks * BK, nt * BN, full_bar(stage));
                         issued++;
                         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                     }
@@ -449,7 +450,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                     for (int tap = 0; tap < 9; tap++) {
                         if (!mbar_wait(bempty(bs), bph ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
                         mbar_expect_tx(bfull(bs), C::B_STAGE_BYTES);
-                        tma_load_2d(b_base + bs * C::B_STAGE_BYTES, &mapB, tap * p.Cin + ks * BK, nt * BN, bfull(bs));
+                        tma_load_2d(b_base + bs * C::B_STAGE_BYTES, &mapB, tap * p.CinPad + ks * BK, nt * BN, bfull(bs));
                         b_issued++;
                         if (++bs == C::NB) { bs = 0; bph ^= 1u; }
                     }
@@ -651,7 +652,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                     for (int tap = 0; tap < 9; tap++) {
                         if (!mbar_wait(wempty(ws), wph ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
                         mbar_expect_tx(wfull(ws), SWAP_W_BYTES);
-                        tma_load_2d(w_base + ws * SWAP_W_BYTES, &mapW, tap * p.Cin + ks * BK, nt * BM, wfull(ws));
+                        tma_load_2d(w_base + ws * SWAP_W_BYTES, &mapW, tap * p.CinPad + ks * BK, nt * BM, wfull(ws));
                         w_issued++;
                         if (++ws == SWAP_NW) { ws = 0; wph ^= 1u; }
                     }
@@ -839,11 +840,15 @@ static void pick_subtile(int W, int H, int pool, int *TW, int *TH, int *S)
     }
 }
 
+extern "C" int dRk_tensor_conv_cin_pad(int Cin) { return (Cin + BK - 1) / BK * BK; }
+
 extern "C" int dRk_tensor_conv_supported(int W, int H, int Cin, int Cout, int kw, int kh)
 {
     if (W <= 0 || H <= 0) return 0;
     if (!((kw == 1 && kh == 1) || (kw == 3 && kh == 3))) return 0;
-    if (Cin % BK != 0) return 0;
+    /* channels past Cin inside the last 32-channel slab are TMA zero fill (activations) and zero padding (packed filters);
+       TMA needs the pixel stride Cin*4 to be a multiple of 16 bytes */
+    if (Cin % 4 != 0 || Cin < 8) return 0;
     if (Cout % 4 != 0 || Cout < 16) return 0;          /* rows past Cout are TMA zero fill; the epilogues mask them */
     return 1;
 }
@@ -923,8 +928,9 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     dRk_TensorConvPlan *pl = (dRk_TensorConvPlan *)calloc(1, sizeof(dRk_TensorConvPlan));
     UmmaParams &p = pl->p;
     p.n = n; p.W = W; p.H = H; p.Cin = Cin; p.Cout = Cout;
+    p.CinPad = (Cin + BK - 1) / BK * BK;
     p.taps = kw * kh; p.kw = kw; p.pad = kw / 2;
-    p.kslabs = Cin / BK;
+    p.kslabs = p.CinPad / BK;
     p.bias = bias; p.out = out; p.ldo = ldo; p.coff = coff; p.act = act; p.status = status; p.pool = fuse_pool2 ? 1 : 0;
     p.ksplit = 1; p.kper = p.kslabs; p.split_stride = 0;
     const cuuint32_t ones[4] = {1, 1, 1, 1};
@@ -976,7 +982,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     pl->BN = pl->swap ? BM : pick_bn(Cout, p.m_tiles, sms);
     p.n_tiles = pl->swap ? (Cout + BM - 1) / BM : (Cout + pl->BN - 1) / pl->BN;
     {
-        const cuuint64_t K = (cuuint64_t)p.taps * Cin;
+        const cuuint64_t K = (cuuint64_t)p.taps * p.CinPad;
         const cuuint64_t dims[2] = {K, (cuuint64_t)Cout};
         const cuuint64_t strides[1] = {K * 4};
         const cuuint32_t box[2] = {BK, (cuuint32_t)pl->BN};
@@ -1070,7 +1076,7 @@ extern "C" dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wT
     dRk_TensorFcPlan *fp = (dRk_TensorFcPlan *)calloc(1, sizeof(dRk_TensorFcPlan));
     dRk_TensorConvPlan *pl = &fp->conv;
     UmmaParams &p = pl->p;
-    p.n = n; p.W = 1; p.H = 1; p.Cin = Nin; p.Cout = Nout;
+    p.n = n; p.W = 1; p.H = 1; p.Cin = Nin; p.CinPad = Nin; p.Cout = Nout;
     p.taps = 1; p.kw = 1; p.pad = 0; p.kslabs = Nin / BK;
     p.S = 0; p.TW = BM; p.TH = 1; p.tiles_x = p.tiles_y = 1;
     p.total_sub = n; p.m_tiles = 1; p.n_tiles = Nout / 256;

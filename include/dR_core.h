@@ -31,6 +31,8 @@ gboolean dR_propagateShapesAndSchedule(dR_Graph *net);
 gboolean dR_estimateAndAllocateBuffers(dR_Graph *net);
 gboolean dR_fillBuffers(dR_Graph *net);
 gboolean dR_planFusion(dR_Graph *net);
+/* TRUE if every input of this channel-wise Concat is a Slice -> scalar-op chain that one gather kernel can evaluate */
+gboolean dR_concat_planGather(dR_Node *concat);
 void dR_cleanupBuffers(dR_Graph *net);
 void dR_cleanupNet(dR_Graph *net);
 dR_MemoryHandler *dR_newMemoryHandler(gboolean custom);

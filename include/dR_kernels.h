@@ -95,12 +95,27 @@ int dRk_croporpad(dRk_stream stream, const float *in, float *out, int n, int W, 
 int dRk_concat_place(dRk_stream stream, const float *in, float *out, int n, int w, int h, int c, int dim, int off,
                      int W, int H, int C, int ldi);
 
+/* Fused Slice -> scalar element-wise chain -> Concat along channels: output channel j of every pixel is
+ * source channel ch[j] of src[j] (pixel stride ld[j]) pushed through up to 4 scalar ops (codes of
+ * dRk_elemwise1) in order.  Replaces extractSlice + the scalar kernels + the generated concat kernel
+ * (Kernels/dR_transform.cl:5-25, Kernels/dR_math.cl:176-260, src/dR_nodes_transform.c:468-553) for that pattern. */
+#define DRK_CHANNEL_MAP_MAX 16
+typedef struct {
+    const float *src[DRK_CHANNEL_MAP_MAX];
+    int ld[DRK_CHANNEL_MAP_MAX], ch[DRK_CHANNEL_MAP_MAX], nops[DRK_CHANNEL_MAP_MAX];
+    int op[DRK_CHANNEL_MAP_MAX][4];
+    float scalar[DRK_CHANNEL_MAP_MAX][4];
+    int cout;
+} drk_ChannelMap;
+int dRk_channel_map(dRk_stream stream, const drk_ChannelMap *map, float *out, size_t pixels);
+
 /*
  * Tensor-core convolution / GEMM: tcgen05.mma kind::tf32 with FP32 accumulators in TMEM,
  * operands staged by TMA (cp.async.bulk.tensor) into 128B-swizzled shared memory.
  * The plan object owns the CUtensorMap descriptors for one layer shape + buffer set.
- *   in   : N-HWC, Cin a multiple of 8 (dense, ldi == Cin)
- *   wT   : [Cout][kh*kw*Cin]   (K contiguous), k = (ky*kw + kx)*Cin + c
+ *   in   : N-HWC, dense (ldi == Cin), Cin a multiple of 4 and >= 8
+ *   wT   : [Cout][kh*kw*CinPad] (K contiguous), k = (ky*kw + kx)*CinPad + c, CinPad = Cin rounded up to a multiple
+ *          of 32 (dRk_tensor_conv_cin_pad), the padding filled with zeros
  * Returns NULL if the shape is not supported by the tensor path (caller falls back to FFMA).
  * `status` is a device int the kernel writes a non-zero code to if a bounded wait runs out.
  * fuse_pool2 = 1 (3x3 layers, even W and H): the epilogue stores the maximum over each 2x2 pixel window,
@@ -109,6 +124,7 @@ int dRk_concat_place(dRk_stream stream, const float *in, float *out, int n, int 
 typedef struct dRk_TensorConvPlan dRk_TensorConvPlan;
 /* 1 if the tensor path can evaluate this layer shape (stride 1, 1x1 or 3x3, channel counts it can tile). */
 int dRk_tensor_conv_supported(int W, int H, int Cin, int Cout, int kw, int kh);
+int dRk_tensor_conv_cin_pad(int Cin);
 dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float *wT, const float *bias, float *out,
                                          int n, int W, int H, int Cin, int Cout, int kw, int kh, int act,
                                          int ldo, int coff, int fuse_pool2, int *status);

@@ -16,6 +16,7 @@ struct dR_Concat_Data {
     gint inputSizesInConcatDim[3];
     gint maxInputSizeInConcatDim;
     gboolean elidedCopy;        /* producers write straight into this node's buffer */
+    gboolean fusedGather;       /* inputs are Slice -> scalar-op chains: one gather kernel evaluates them all */
 };
 
 typedef struct dR_CropOrPad_Data dR_CropOrPad_Data;

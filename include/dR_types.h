@@ -129,6 +129,7 @@ struct dR_Node {
                                 writes straight into a Concat consumer's buffer */
     gint act_coffset;        /* channel offset inside that pixel */
     gboolean elided;         /* node produces its result in place of a consumer's buffer / is skipped */
+    gboolean fusedAway;      /* a consumer evaluates this node as part of its own kernel: compute() is not called */
     size_t scratchFloats;    /* per-apply scratch this node needs (shared, graph-owned) */
     gdouble lastGpuMs;       /* per-node kernel time of the last profiled apply */
 };

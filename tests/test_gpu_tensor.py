@@ -27,6 +27,11 @@ TENSOR_SHAPES = [
     ("t_1x1_squeeze_16", 2, 64, 16, 56, 56, 1),      # SqueezeNet squeeze layers: fewer output channels than any N tile
     ("t_1x1_squeeze_48", 3, 256, 48, 14, 14, 1),
     ("t_3x3_cout_16", 1, 32, 16, 28, 28, 3),
+    ("t_3x3_cin_16", 2, 16, 64, 56, 56, 3),          # channel counts that do not fill a 32-channel slab: zero-filled tail
+    ("t_3x3_cin_48", 2, 48, 192, 14, 14, 3),
+    ("t_1x1_cin_16", 2, 16, 64, 56, 56, 1),
+    ("t_3x3_cin_8", 1, 8, 32, 20, 28, 3),
+    ("t_3x3_cin_40_swap", 1, 40, 64, 32, 28, 3),
     ("t_3x3_cout_48_swap", 1, 64, 48, 28, 32, 3),
     ("t_3x3_cout_200", 1, 64, 200, 14, 14, 3),
 ]
