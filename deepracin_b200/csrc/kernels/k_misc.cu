@@ -101,6 +101,39 @@ __global__ void k_pool(const float *__restrict__ in, float *__restrict__ out, in
     }
 }
 
+/* Large windows (global average pooling and the like): a CTA owns one output pixel and 32 float4 channel groups; its 8
+ * rows of threads split the window positions, every step reading 512 contiguous bytes, and combine through shared memory. */
+__global__ void k_pool_bigwindow(const float *__restrict__ in, float *__restrict__ out, int W, int H, int C, int Wo, int Ho,
+                                 int sx, int sy, int stx, int sty, int type, int ldi)
+{
+    __shared__ float4 part[8][32];
+    const int g = blockIdx.x * 32 + threadIdx.x;            /* float4 channel group */
+    const int ox = blockIdx.y % Wo, oy = blockIdx.y / Wo, b = blockIdx.z;
+    const bool gok = g * 4 < C;
+    float4 acc = type == 0 ? make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX) : make_float4(0.f, 0.f, 0.f, 0.f);
+    if (gok) {
+        for (int i = threadIdx.y; i < sx * sy; i += 8) {
+            const int dy = i / sx, dx = i - dy * sx;
+            const int ix = ox * stx + dx, iy = oy * sty + dy;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);         /* reads outside the image are zeros that take part */
+            if (ix < W && iy < H) v = *reinterpret_cast<const float4 *>(in + (((size_t)b * H + iy) * W + ix) * ldi + g * 4);
+            if (type == 0) { acc.x = fmaxf(acc.x, v.x); acc.y = fmaxf(acc.y, v.y); acc.z = fmaxf(acc.z, v.z); acc.w = fmaxf(acc.w, v.w); }
+            else { acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
+        }
+    }
+    part[threadIdx.y][threadIdx.x] = acc;
+    __syncthreads();
+    if (threadIdx.y == 0 && gok) {
+        for (int k = 1; k < 8; k++) {
+            const float4 v = part[k][threadIdx.x];
+            if (type == 0) { acc.x = fmaxf(acc.x, v.x); acc.y = fmaxf(acc.y, v.y); acc.z = fmaxf(acc.z, v.z); acc.w = fmaxf(acc.w, v.w); }
+            else { acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w; }
+        }
+        if (type != 0) { const float inv = 1.0f / (float)(sx * sy); acc.x *= inv; acc.y *= inv; acc.z *= inv; acc.w *= inv; }
+        *reinterpret_cast<float4 *>(out + (((size_t)b * Ho + oy) * Wo + ox) * C + g * 4) = acc;
+    }
+}
+
 extern "C" int dRk_pool(dRk_stream s, const float *in, float *out, int n, int W, int H, int C, int sx, int sy, int sz,
                         int stx, int sty, int stz, int type, int ldi)
 {
@@ -109,6 +142,12 @@ extern "C" int dRk_pool(dRk_stream s, const float *in, float *out, int n, int W,
     const bool vec = sz == 1 && stz == 1 && C % 4 == 0 && ldi % 4 == 0 && ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
     const size_t total = (size_t)n * Ho * Wo * (vec ? Co / 4 : Co);
     const unsigned blocks = drk_blocks(total, 256, 148u * 32u);
+    if (vec && sx * sy >= 64 && (size_t)Wo * Ho <= 65535u && n <= 65535) {
+        dim3 grid((C / 4 + 31) / 32, Wo * Ho, n), block(32, 8);
+        k_pool_bigwindow<<<grid, block, 0, drk_stream(s)>>>(in, out, W, H, C, Wo, Ho, sx, sy, stx, sty, type, ldi);
+        DRK_COUNT_LAUNCH();
+        return DRK_LAUNCH_RESULT();
+    }
     if (vec) k_pool<4><<<blocks, 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, Wo, Ho, Co, sx, sy, sz, stx, sty, stz, type, ldi);
     else k_pool<1><<<blocks, 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, Wo, Ho, Co, sx, sy, sz, stx, sty, stz, type, ldi);
     DRK_COUNT_LAUNCH();
@@ -260,12 +299,35 @@ __global__ void k_copy_box(const float *__restrict__ in, float *__restrict__ out
     }
 }
 
+/* same with four channels per thread when every channel count, offset and stride involved is a multiple of 4 */
+__global__ void k_copy_box4(const float *__restrict__ in, float *__restrict__ out, int n, int W, int H, int C, int ldi,
+                            int ox, int oy, int oz, int w, int h, int c, int DW, int DH, int DC, int dx, int dy, int dz)
+{
+    const int c4 = c / 4;
+    const size_t total = (size_t)n * h * w * c4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const int z = (int)(i % c4) * 4;
+        size_t p = i / c4;
+        const int x = (int)(p % w);
+        size_t q = p / w;
+        const int y = (int)(q % h);
+        const int b = (int)(q / h);
+        const int sx = x + ox, sy = y + oy, sz = z + oz;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (sx >= 0 && sx < W && sy >= 0 && sy < H && sz >= 0 && sz + 3 < C) v = *reinterpret_cast<const float4 *>(in + (((size_t)b * H + sy) * W + sx) * ldi + sz);
+        *reinterpret_cast<float4 *>(out + (((size_t)b * DH + y + dy) * DW + x + dx) * DC + z + dz) = v;
+    }
+}
+
 static int copy_box(dRk_stream s, const float *in, float *out, int n, int W, int H, int C, int ldi, int ox, int oy, int oz,
                     int w, int h, int c, int DW, int DH, int DC, int dx, int dy, int dz)
 {
     if (n <= 0 || w <= 0 || h <= 0 || c <= 0) return -1;
     const size_t total = (size_t)n * h * w * c;
-    k_copy_box<<<drk_blocks(total, 256, 148u * 32u), 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, ldi, ox, oy, oz, w, h, c, DW, DH, DC, dx, dy, dz);
+    const bool vec = c % 4 == 0 && C % 4 == 0 && oz % 4 == 0 && dz % 4 == 0 && ldi % 4 == 0 && DC % 4 == 0 &&
+                     ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
+    if (vec) k_copy_box4<<<drk_blocks(total / 4, 256, 148u * 32u), 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, ldi, ox, oy, oz, w, h, c, DW, DH, DC, dx, dy, dz);
+    else k_copy_box<<<drk_blocks(total, 256, 148u * 32u), 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, ldi, ox, oy, oz, w, h, c, DW, DH, DC, dx, dy, dz);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }

@@ -3,6 +3,7 @@
   python deepracin_b200/layer_bench.py conv CIN COUT HW BATCH [--k 3] [--math tf32|fp32] [--algo auto|direct|winograd|1x1|tensor]
   python deepracin_b200/layer_bench.py fc NIN NOUT BATCH [--math ...]
   python deepracin_b200/layer_bench.py sweep           # the conv-sweep and 1x1/FC configurations of the benchmark spec
+  python deepracin_b200/layer_bench.py membound        # pooling / element-wise / softmax / copies: GB/s of the bytes they must move
 
 Times `--iters` launches with CUDA events on the library's stream after `--warmup` launches and prints
 one JSON line per layer: ms, direct-convolution TFLOP/s (Winograd gets no discount), minimum HBM
@@ -84,6 +85,44 @@ def fc_layer(nin, nout, batch, math="fp32", iters=20, warmup=5):
             "min_bytes": bytes_min, "gbs_at_min_bytes": bytes_min / ms / 1e6, "flop_per_byte": flops / bytes_min}
 
 
+def single_node(build, shape_hwc, batch, bytes_moved, label, iters=20, warmup=5, feeds=1):
+    """Times a graph of one memory-bound node; reports GB/s of the bytes it has to move (in + out)."""
+    r = _rng(label)
+    with dr.Environment() as env:
+        g = env.create_graph("HWC")
+        g.batch = batch
+        fs = [dr.feed_node(g, list(shape_hwc)) for _ in range(feeds)]
+        o = build(fs)
+        dr.mark_as_output(o)
+        dr.lib.dR_setInterfaceLayout(g.ptr, 1)
+        dr.prepare(g)
+        for f in fs:
+            dr.feed_data(f, r.standard_normal((batch,) + tuple(shape_hwc), dtype=np.float32))
+        ms = time_graph(g, iters, warmup)
+    return {"layer": label, "ms": ms, "bytes": bytes_moved, "gbs": bytes_moved / ms / 1e6}
+
+
+def membound(iters, warmup):
+    """Pooling, element-wise, softmax, slice/concat and layout kernels at benchmark-sized tensors (all HBM bound)."""
+    out = []
+    b = 64
+    for hw, c in ((224, 64), (112, 128), (56, 256)):
+        n = b * hw * hw * c * 4
+        out.append(single_node(lambda f: dr.Pooling(f[0], "max", [1, 2, 2, 1], [1, 2, 2, 1]), (hw, hw, c), b, n * 1.25,
+                               "maxpool 2x2/2 %dx%dx%d batch %d" % (hw, hw, c, b), iters, warmup))
+    out.append(single_node(lambda f: dr.Pooling(f[0], "max", [1, 3, 3, 1], [1, 2, 2, 1]), (112, 112, 64), b, b * 112 * 112 * 64 * 4 * 1.25,
+                           "maxpool 3x3/2 112x112x64 batch 64", iters, warmup))
+    out.append(single_node(lambda f: dr.Pooling(f[0], "average", [1, 14, 14, 1], [1, 14, 14, 1]), (14, 14, 1000), b, b * 196 * 1000 * 4.0,
+                           "avgpool 14x14 14x14x1000 batch 64", iters, warmup))
+    n = b * 112 * 112 * 128 * 4
+    out.append(single_node(lambda f: dr.Add_Scalar(f[0], 1.5), (112, 112, 128), b, 2.0 * n, "add scalar 112x112x128 batch 64", iters, warmup))
+    out.append(single_node(lambda f: dr.Add(f[0], f[1]), (112, 112, 128), b, 3.0 * n, "add 112x112x128 batch 64", iters, warmup, feeds=2))
+    out.append(single_node(lambda f: dr.Softmax(f[0]), (1, 1, 1000), b, 2.0 * b * 1000 * 4, "softmax 1000 batch 64", iters, warmup))
+    out.append(single_node(lambda f: dr.Concat([f[0], f[1]], 2), (56, 56, 64), b, 4.0 * b * 56 * 56 * 64 * 4, "concat(z) 2 x 56x56x64 batch 64", iters, warmup, feeds=2))
+    out.append(single_node(lambda f: dr.Slice(f[0], (0, 0, 16), (56, 56, 32)), (56, 56, 64), b, 2.0 * b * 56 * 56 * 32 * 4, "slice 32 of 64 channels 56x56 batch 64", iters, warmup))
+    return out
+
+
 def sweep(iters, warmup):
     out = []
     for cin, hw in ((64, 56), (128, 28), (256, 14)):
@@ -99,7 +138,7 @@ def sweep(iters, warmup):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["conv", "fc", "sweep"])
+    ap.add_argument("what", choices=["conv", "fc", "sweep", "membound"])
     ap.add_argument("dims", nargs="*", type=int)
     ap.add_argument("--k", type=int, default=3)
     ap.add_argument("--math", default="tf32")
@@ -113,6 +152,8 @@ def main():
     elif a.what == "fc":
         nin, nout, batch = a.dims
         res = [fc_layer(nin, nout, batch, a.math, a.iters, a.warmup)]
+    elif a.what == "membound":
+        res = membound(a.iters, a.warmup)
     else:
         res = sweep(a.iters, a.warmup)
     for r in res:
