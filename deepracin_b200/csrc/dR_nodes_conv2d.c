@@ -204,7 +204,7 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
     /* conv -> 2x2/2 max pool with no other reader: the tensor kernel's epilogue stores the pooled tensor
        directly into the pooling node's buffer and the pooling node launches nothing */
     dev(c)->fusedPool = FALSE;
-    if (c->chosenTensor && net->config->fuseGraph && is3x3s1(c) && !layer->output && !layer->elided && layer->next_layers->length == 1 &&
+    if (c->chosenTensor && net->config->fuseGraph && is3x3s1(c) && c->shape.s2 >= 8 && !layer->output && !layer->elided && layer->next_layers->length == 1 &&
         layer->oshape.s0 % 2 == 0 && layer->oshape.s1 % 2 == 0) {
         dR_Node *nx = (dR_Node *)layer->next_layers->first->element;
         if (nx->type == tPooling && nx->previous_layers->length == 1) {

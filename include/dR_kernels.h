@@ -113,9 +113,10 @@ int dRk_channel_map(dRk_stream stream, const drk_ChannelMap *map, float *out, si
  * Tensor-core convolution / GEMM: tcgen05.mma kind::tf32 with FP32 accumulators in TMEM,
  * operands staged by TMA (cp.async.bulk.tensor) into 128B-swizzled shared memory.
  * The plan object owns the CUtensorMap descriptors for one layer shape + buffer set.
- *   in   : N-HWC, dense (ldi == Cin), Cin a multiple of 4 and >= 8
- *   wT   : [Cout][kh*kw*CinPad] (K contiguous), k = (ky*kw + kx)*CinPad + c, CinPad = Cin rounded up to a multiple
- *          of 32 (dRk_tensor_conv_cin_pad), the padding filled with zeros
+ *   in   : N-HWC, dense (ldi == Cin), Cin a multiple of 4 and >= 8; or 3x3 filters with Cin <= 4 and
+ *          16 <= Cout <= 128 (first-layer kernel: the patch operand is gathered by producer warps, no TMA)
+ *   wT   : [Cout][kh*kw*CinPad] (K contiguous), k = (ky*kw + kx)*CinPad + c, CinPad = dRk_tensor_conv_cin_pad(Cin):
+ *          Cin rounded up to a multiple of 32 with the padding filled with zeros, or Cin itself when Cin <= 4
  * Returns NULL if the shape is not supported by the tensor path (caller falls back to FFMA).
  * `status` is a device int the kernel writes a non-zero code to if a bounded wait runs out.
  * fuse_pool2 = 1 (3x3 layers, even W and H): the epilogue stores the maximum over each 2x2 pixel window,

@@ -34,6 +34,11 @@ TENSOR_SHAPES = [
     ("t_3x3_cin_40_swap", 1, 40, 64, 32, 28, 3),
     ("t_3x3_cout_48_swap", 1, 64, 48, 28, 32, 3),
     ("t_3x3_cout_200", 1, 64, 200, 14, 14, 3),
+    ("t_first_rgb", 2, 3, 64, 40, 36, 3),            # few input channels: patch operand gathered by producer warps
+    ("t_first_rgb_224", 1, 3, 64, 224, 224, 3),
+    ("t_first_c1", 3, 1, 32, 17, 13, 3),             # pixel count not a multiple of the 256-pixel tile
+    ("t_first_c4", 2, 4, 128, 20, 24, 3),            # K = 36: two swizzle slabs
+    ("t_first_c2_48", 1, 2, 48, 15, 15, 3),
 ]
 
 
@@ -58,14 +63,14 @@ def test_tensor_conv_matches_oracle(name, n, cin, cout, h, w, k, act, bias):
 
 
 def test_tensor_path_falls_back_where_it_cannot_tile():
-    """3 input channels (first VGG layer), 5x5 filters and strided layers stay on the FP32 kernels."""
+    """Few input channels with more than 128 filters, 5x5 filters and strided layers stay on the FP32 kernels."""
     with dr.Environment() as env:
         g = env.create_graph("CHW")
         g.math = "tf32"
         f = dr.feed_node(g, [3, 16, 16])
         z = np.zeros
-        a = dr.Conv2d(f, [3, 3, 3, 64], [1, 1, 1, 1], "relu", z((3, 3, 3, 64), np.float32), None)
-        b = dr.Conv2d(a, [3, 3, 64, 64], [1, 1, 1, 1], "relu", z((3, 3, 64, 64), np.float32), None)
+        a = dr.Conv2d(f, [3, 3, 3, 192], [1, 1, 1, 1], "relu", z((3, 3, 3, 192), np.float32), None)
+        b = dr.Conv2d(a, [3, 3, 192, 64], [1, 1, 1, 1], "relu", z((3, 3, 192, 64), np.float32), None)
         c = dr.Conv2d(b, [5, 5, 64, 64], [1, 1, 1, 1], "relu", z((5, 5, 64, 64), np.float32), None)
         d = dr.Conv2d(c, [3, 3, 64, 64], [1, 2, 2, 1], "relu", z((3, 3, 64, 64), np.float32), None)
         dr.mark_as_output(d)
