@@ -243,9 +243,9 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
     if (algo == DR_CONV_ONEBYONE) algo = DR_CONV_DIRECT;        /* same [K][Cout] packing */
     if (d->wbuf[algo]) return TRUE;
     size_t n = (size_t)kw * kh * I * O;
-    const gint Ipad = dRk_tensor_conv_cin_pad(I);
     if (algo == DR_CONV_WINOGRAD) n = (size_t)16 * I * O;
-    if (algo == DR_CONV_TENSOR) n = (size_t)kw * kh * Ipad * O;
+    if (algo == DR_CONV_TENSOR) n = dRk_tensor_conv_packed_floats(c->ishape.s0, c->ishape.s1, I, O, kw, kh);
+    if (n == 0) return FALSE;
     gfloat *p = (gfloat *)g_malloc0(n * sizeof(gfloat));
     if (algo == DR_CONV_DIRECT) {
         /* [ (ky*kw+kx)*Cin + i ][ o ] */
@@ -254,11 +254,8 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
                 for (gint t = 0; t < kh * kw; t++)
                     p[((size_t)t * I + i) * O + o] = c->weights[((size_t)i * O + o) * kh * kw + t];
     } else if (algo == DR_CONV_TENSOR) {
-        /* [ o ][ (ky*kw+kx)*CinPad + i ], channels Cin..CinPad-1 stay zero */
-        for (gint i = 0; i < I; i++)
-            for (gint o = 0; o < O; o++)
-                for (gint t = 0; t < kh * kw; t++)
-                    p[(size_t)o * kh * kw * Ipad + (size_t)t * Ipad + i] = c->weights[((size_t)i * O + o) * kh * kw + t];
+        /* K-major rows per output channel; the exact layout belongs to the tensor kernel picked for this shape */
+        if (dRk_tensor_conv_pack_weights(c->weights, p, c->ishape.s0, c->ishape.s1, I, O, kw, kh) != 0) { g_free(p); return FALSE; }
     } else {
         /* U = G g G^T with G = [[1,0,0],[.5,.5,.5],[.5,-.5,.5],[0,0,1]] (reference :1162-1240),
            stored [16][Cin][Cout] so that each of the 16 positions is one K x N matrix */

@@ -682,10 +682,16 @@ struct dRk_TensorConvPlan {
     int halo;           /* 1: k_umma_conv_halo (one haloed A tile per channel slab, reused by all nine taps) */
     int swap;           /* 1: k_umma_conv_swap (channels on M, 256 pixels on N) for Cout <= 128 */
     int first;          /* 1: k_umma_conv_first (Cin <= 4: patches gathered by producer warps, no tensor maps) */
+    int pair;           /* 1: k_umma_conv_pair (Cout <= 64: two output rows stacked on M); mapA = odd input rows, mapA2 = even */
+    CUtensorMap mapA2;
     const float *in, *wT;
     int sms;
 };
 
+double drk_umma_pair_fill(int W, int H);
+void drk_umma_pair_geometry(int W, int H, int *tiles_x, int *tiles_y);
+void drk_umma_pair_boxes(unsigned box_plane[4], unsigned box_w[2]);
+int drk_umma_pair_launch(cudaStream_t st, const CUtensorMap *mapO, const CUtensorMap *mapE, const CUtensorMap *mapW, const UmmaParams *p, int grid);
 int drk_umma_first_supported(int Cin, int Cout, int kw, int kh);
 int drk_umma_first_launch(cudaStream_t st, const float *in, const float *wT, const float *bias, float *out, int n, int W, int H, int Cin,
                           int Cout, int act, int ldi, int ldo, int coff, int *status, int sms);
@@ -753,6 +759,61 @@ static double swap_fill(int W, int H)
     return (double)W * H / (tx * ty * SWAP_N);
 }
 
+/* which kernel evaluates a layer shape; the packed-filter layout depends on it, so packing and planning both ask here.
+ * The environment switches exist for A/B comparisons of the variants when profiling. */
+enum { VAR_NONE = 0, VAR_FLAT, VAR_PLAIN, VAR_HALO, VAR_SWAP, VAR_PAIR, VAR_FIRST };
+static int pick_variant(int W, int H, int Cin, int Cout, int kw, int kh)
+{
+    if (!dRk_tensor_conv_supported(W, H, Cin, Cout, kw, kh)) return VAR_NONE;
+    if (drk_umma_first_supported(Cin, Cout, kw, kh)) return VAR_FIRST;
+    if (kw == 1) return VAR_FLAT;
+    const bool no_halo = getenv("DRK_NO_HALO") != NULL;
+    if (Cout <= 64 && H >= 2 && drk_umma_pair_fill(W, H) >= 0.5 && !getenv("DRK_NO_PAIR") && !no_halo) return VAR_PAIR;
+    if (Cout <= BM && swap_fill(W, H) >= 0.8 && !getenv("DRK_NO_SWAP") && !no_halo) return VAR_SWAP;
+    if (halo_fill(W, H) >= 0.55 && !no_halo) return VAR_HALO;
+    return VAR_PLAIN;
+}
+
+extern "C" size_t dRk_tensor_conv_packed_floats(int W, int H, int Cin, int Cout, int kw, int kh)
+{
+    const int v = pick_variant(W, H, Cin, Cout, kw, kh);
+    if (v == VAR_NONE) return 0;
+    const size_t cp = (size_t)dRk_tensor_conv_cin_pad(Cin);
+    if (v == VAR_PAIR) return (size_t)BM * 12 * cp;
+    return (size_t)Cout * kw * kh * cp;
+}
+
+extern "C" int dRk_tensor_conv_pack_weights(const float *w, float *dst, int W, int H, int Cin, int Cout, int kw, int kh)
+{
+    const int v = pick_variant(W, H, Cin, Cout, kw, kh);
+    if (v == VAR_NONE) return -1;
+    const size_t cp = (size_t)dRk_tensor_conv_cin_pad(Cin);
+    const int taps = kw * kh;
+    memset(dst, 0, dRk_tensor_conv_packed_floats(W, H, Cin, Cout, kw, kh) * sizeof(float));
+    if (v == VAR_PAIR) {
+        /* [128 rows][(i*3 + kx)*CinPad + c]: row r < 64 = channel r with ky = i (upper output row), row 64 + o = channel o with
+           ky = i - 1 (lower output row); i = 0..3 counts the four input rows a pair of output rows reads */
+        for (int r = 0; r < BM; r++) {
+            const int o = r & 63, lower = r >> 6;
+            if (o >= Cout) continue;
+            for (int i = 0; i < 4; i++) {
+                const int ky = i - lower;
+                if (ky < 0 || ky > 2) continue;
+                for (int kx = 0; kx < 3; kx++)
+                    for (int c = 0; c < Cin; c++)
+                        dst[(size_t)r * 12 * cp + (size_t)(i * 3 + kx) * cp + c] = w[((size_t)c * Cout + o) * 9 + ky * 3 + kx];
+            }
+        }
+        return 0;
+    }
+    /* [o][(ky*kw + kx)*CinPad + c], channels Cin..CinPad-1 stay zero */
+    for (int c = 0; c < Cin; c++)
+        for (int o = 0; o < Cout; o++)
+            for (int t = 0; t < taps; t++)
+                dst[(size_t)o * taps * cp + (size_t)t * cp + c] = w[((size_t)c * Cout + o) * taps + t];
+    return 0;
+}
+
 static int pick_bn(int Cout, long long m_tiles, int sms)
 {
     /* N tile: fewest waves of tiles over the SMs, weighting a tile by its width plus a fixed part (pipeline fill, epilogue tail);
@@ -814,7 +875,8 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     dRk_TensorConvPlan *pl = (dRk_TensorConvPlan *)calloc(1, sizeof(dRk_TensorConvPlan));
     UmmaParams &p = pl->p;
     pl->in = in; pl->wT = wT; pl->sms = sms;
-    if (drk_umma_first_supported(Cin, Cout, kw, kh)) {
+    const int variant = pick_variant(W, H, Cin, Cout, kw, kh);
+    if (variant == VAR_FIRST) {
         pl->first = 1;
         p.n = n; p.W = W; p.H = H; p.Cin = Cin; p.Cout = Cout; p.bias = bias; p.out = out; p.ldo = ldo; p.coff = coff; p.act = act; p.status = status;
         return pl;
@@ -836,7 +898,25 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
         const cuuint32_t box[2] = {BK, BM};
         r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)in, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    } else if (Cout <= BM && swap_fill(W, H) >= 0.8 && !getenv("DRK_NO_SWAP") && !getenv("DRK_NO_HALO")   /* env switches: A/B comparisons of the variants when profiling */) {
+    } else if (variant == VAR_PAIR) {
+        pl->pair = 1;
+        p.S = 1;
+        drk_umma_pair_geometry(W, H, &p.tiles_x, &p.tiles_y);
+        p.total_sub = (long long)n * p.tiles_x * p.tiles_y;
+        p.m_tiles = (int)p.total_sub;
+        unsigned bp[4], bw[2];
+        drk_umma_pair_boxes(bp, bw);
+        const cuuint32_t box[4] = {bp[0], bp[1], bp[2], bp[3]};
+        /* input rows split by parity: the even plane starts at row 0, the odd plane at row 1, both step two rows */
+        const cuuint64_t strides[3] = {(cuuint64_t)Cin * 4, (cuuint64_t)2 * W * Cin * 4, (cuuint64_t)H * W * Cin * 4};
+        const cuuint64_t dimsE[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)((H + 1) / 2), (cuuint64_t)n};
+        const cuuint64_t dimsO[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)(H / 2), (cuuint64_t)n};
+        r = enc(&pl->mapA2, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void *)in, dimsE, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r == CUDA_SUCCESS)
+            r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void *)(in + (size_t)W * Cin), dimsO, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    } else if (variant == VAR_SWAP) {
         pl->swap = 1;
         p.TW = HALO_TW; p.TH = SWAP_TH; p.S = 1;
         p.tiles_x = (W + HALO_TW - 1) / HALO_TW; p.tiles_y = (H + SWAP_TH - 1) / SWAP_TH;
@@ -847,7 +927,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
         const cuuint32_t box[4] = {BK, HALO_P, SWAP_TH + 2, 1};
         r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void *)in, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    } else if (halo_fill(W, H) >= 0.55 && !getenv("DRK_NO_HALO")) {
+    } else if (variant == VAR_HALO) {
         pl->halo = 1;
         p.TW = HALO_TW; p.TH = HALO_TH; p.S = 1;
         p.tiles_x = (W + HALO_TW - 1) / HALO_TW; p.tiles_y = (H + HALO_TH - 1) / HALO_TH;
@@ -871,11 +951,11 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     }
     if (r != CUDA_SUCCESS) { fprintf(stderr, "tensor conv plan: activation tensor map rejected (%d)\n", (int)r); free(pl); return NULL; }
-    pl->BN = pl->swap ? BM : pick_bn(Cout, p.m_tiles, sms);
-    p.n_tiles = pl->swap ? (Cout + BM - 1) / BM : (Cout + pl->BN - 1) / pl->BN;
+    pl->BN = (pl->swap || pl->pair) ? BM : pick_bn(Cout, p.m_tiles, sms);
+    p.n_tiles = pl->pair ? 1 : pl->swap ? (Cout + BM - 1) / BM : (Cout + pl->BN - 1) / pl->BN;
     {
-        const cuuint64_t K = (cuuint64_t)p.taps * p.CinPad;
-        const cuuint64_t dims[2] = {K, (cuuint64_t)Cout};
+        const cuuint64_t K = (cuuint64_t)(pl->pair ? 12 : p.taps) * p.CinPad;
+        const cuuint64_t dims[2] = {K, (cuuint64_t)(pl->pair ? BM : Cout)};
         const cuuint64_t strides[1] = {K * 4};
         const cuuint32_t box[2] = {BK, (cuuint32_t)pl->BN};
         r = enc(&pl->mapB, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)wT, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -895,6 +975,7 @@ extern "C" int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *pl)
     if (pl->first)
         return drk_umma_first_launch(st, pl->in, pl->wT, pl->p.bias, pl->p.out, pl->p.n, pl->p.W, pl->p.H, pl->p.Cin, pl->p.Cout, pl->p.act,
                                      pl->p.Cin, pl->p.ldo, pl->p.coff, pl->p.status, pl->sms);
+    if (pl->pair) return drk_umma_pair_launch(st, &pl->mapA, &pl->mapA2, &pl->mapB, &pl->p, pl->grid);
     if (pl->swap) {
         static bool attr_done[DRK_MAX_DEVICES];
         const int dev = current_device();

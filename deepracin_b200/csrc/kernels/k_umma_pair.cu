@@ -1,0 +1,302 @@
+/*
+ * Tensor-core 3x3 stride-1 convolution for layers with at most 64 output channels (VGG conv1_2,
+ * SqueezeNet's 64-channel expand layers) in TF32 mode.  A tcgen05.mma costs the same ~93 ns for any M <= 128
+ * and N <= 256, so the transposed product of k_umma_conv_swap (M = channels, N = 256 pixels) wastes half
+ * of every instruction when Cout <= 64.  Here the two halves of M hold the same channels for two
+ * vertically adjacent output rows:
+ *     rows  0..63  : out[o][2j  ][x]      rows 64..127 : out[o][2j+1][x]
+ * Both rows read input rows 2j-1 .. 2j+2; input row 2j-1+i (i = 0..3) is tap ky = i of the upper output row
+ * and tap ky = i-1 of the lower one.  With the input split by row parity into an even and an odd plane
+ * (two TMA maps over the same N-HWC tensor, row stride doubled), the pixels of input row 2j-1+i for
+ * j = 0..15 are consecutive rows of one plane's haloed block, i.e. one B operand read through a shifted
+ * descriptor start as in the halo kernels, and the filter tile of (i, kx) stacks W[ky=i][kx] over
+ * W[ky=i-1][kx] (zeros where ky falls outside 0..2).  Twelve (i, kx) products per 32-channel slab cover what
+ * takes eighteen in the unpaired kernel: 1.5x fewer MMA instructions per output pixel.
+ * Replaces conv2dwinograd2 (Kernels/dR_winograd2.cl:23-254) for these layers; bound: tensor pipe;
+ * algorithmic FLOPs = 2*9*Cin*Cout*n*H*W.
+ *
+ * A tile is 14 x 32 output pixels (N = 256 columns = 16 row pairs x 16-pixel pitch, 14 valid).  6 warps:
+ * warp 0 TMA producer (two plane blocks per slab through a ring of three slots, twelve filter tiles per slab
+ * through a ring of seven, issued in the order the MMA issuer consumes them),
+ * warp 1 MMA issuer and TMEM owner, warps 2-5 epilogue: quarters 0/1 of TMEM hold the upper rows, 2/3 the
+ * lower rows of the same channels.  The fused 2x2 max pooling needs both: the lower-row warp passes its
+ * horizontal maxima to the upper-row warp of the same channels through a small double-buffered
+ * shared-memory exchange guarded by mbarriers.  Every wait is bounded; on expiry the CTA flags an abort,
+ * reports a code through `status`, drains its in-flight copies, frees TMEM and returns.
+ */
+#include <stdio.h>
+#include "k_common.cuh"
+#include "k_umma.cuh"
+
+#define PAIR_THREADS 192
+#define PAIR_TW 14
+#define PAIR_P 16                                       /* pixel pitch of a block row */
+#define PAIR_TJ 16                                      /* row pairs per tile */
+#define PAIR_N 256
+#define PAIR_PLANE_ROWS ((PAIR_TJ + 1) * PAIR_P)        /* 272 shared-memory rows loaded per plane and slab */
+#define PAIR_PLANE_BYTES (PAIR_PLANE_ROWS * BK * 4)     /* 34816 */
+#define PAIR_PLANE_SLOT (35 * 1024)                     /* 280 rows >= 256 + 16 + 2 */
+#define PAIR_NH 3                                       /* ring of plane slots: odd and even planes of a slab are separate stages */
+#define PAIR_W_BYTES (BM * BK * 4)
+#define PAIR_NW 7
+#define PAIR_X_FLOATS (2 * 7 * 32)                      /* one exchange buffer: 2 pooled rows x 7 pooled pixels x 32 lanes */
+#define PAIR_X_BYTES (2 * 2 * PAIR_X_FLOATS * 4)        /* two warp pairs x two buffers */
+#define PAIR_SMEM (PAIR_NH * PAIR_PLANE_SLOT + PAIR_NW * PAIR_W_BYTES + PAIR_X_BYTES + 1024 + 512)
+
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant__ CUtensorMap mapE, const __grid_constant__ CUtensorMap mapW,
+                 const UmmaParams p)
+{
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t raw = smem_u32(smem_raw);
+    const uint32_t base = (raw + 1023u) & ~1023u;
+    uint8_t *gen = smem_raw + (base - raw);
+    const uint32_t h_base = base, w_base = base + PAIR_NH * PAIR_PLANE_SLOT;
+    const uint32_t x_off = PAIR_NH * PAIR_PLANE_SLOT + PAIR_NW * PAIR_W_BYTES;
+    float *xbuf = reinterpret_cast<float *>(gen + x_off);
+    const uint32_t bars = base + x_off + PAIR_X_BYTES;
+    constexpr int NBARS = 2 * PAIR_NH + 2 * PAIR_NW + 4 + 8;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + x_off + PAIR_X_BYTES + 8 * NBARS);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    auto hfull = [&](int s) { return bars + 8u * s; };
+    auto hempty = [&](int s) { return bars + 8u * (PAIR_NH + s); };
+    auto wfull = [&](int s) { return bars + 8u * (2 * PAIR_NH + s); };
+    auto wempty = [&](int s) { return bars + 8u * (2 * PAIR_NH + PAIR_NW + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + 2 + a); };
+    auto xfull = [&](int pr, int b) { return bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + 4 + pr * 4 + b); };
+    auto xempty = [&](int pr, int b) { return bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + 4 + pr * 4 + 2 + b); };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int total_tiles = p.m_tiles;
+    const int per = p.tiles_x * p.tiles_y;
+    constexpr int TMEM_COLS = 2 * PAIR_N;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < PAIR_NH; s++) { mbar_init(hfull(s), 1); mbar_init(hempty(s), 1); }
+        for (int s = 0; s < PAIR_NW; s++) { mbar_init(wfull(s), 1); mbar_init(wempty(s), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        for (int pr = 0; pr < 2; pr++)
+            for (int b = 0; b < 2; b++) { mbar_init(xfull(pr, b), 1); mbar_init(xempty(pr, b), 1); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&mapO) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&mapE) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&mapW) : "memory");
+            int hs = 0, ws = 0;
+            uint32_t hph = 0, wph = 0;
+            long long h_issued = 0, w_issued = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+                const int img = t / per, rem = t - img * per;
+                const int tyi = rem / p.tiles_x, txi = rem - tyi * p.tiles_x;
+                const int j0 = tyi * PAIR_TJ;
+                /* issue order = the MMA issuer's consumption order: odd plane, its six filter tiles, even plane, its six */
+                for (int ks = 0; ks < p.kslabs && ok; ks++) {
+                    for (int half = 0; half < 2 && ok; half++) {
+                        if (!mbar_wait(hempty(hs), hph ^ 1u, abort_flag, p.status, 5)) { ok = false; break; }
+                        mbar_expect_tx(hfull(hs), PAIR_PLANE_BYTES);
+                        /* odd plane rows j0-1 .. j0+15 (input rows 2j0-1, 2j0+1, ...), even plane rows j0 .. j0+16 */
+                        if (half == 0) tma_load_4d(h_base + hs * PAIR_PLANE_SLOT, &mapO, ks * BK, txi * PAIR_TW - 1, j0 - 1, img, hfull(hs));
+                        else tma_load_4d(h_base + hs * PAIR_PLANE_SLOT, &mapE, ks * BK, txi * PAIR_TW - 1, j0, img, hfull(hs));
+                        h_issued++;
+                        if (++hs == PAIR_NH) { hs = 0; hph ^= 1u; }
+                        for (int q = 0; q < 6; q++) {
+                            const int i = half + 2 * (q / 3), kx = q % 3;           /* input row 2j-1+i: i = 0, 2 live in the odd plane, 1, 3 in the even */
+                            if (!mbar_wait(wempty(ws), wph ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+                            mbar_expect_tx(wfull(ws), PAIR_W_BYTES);
+                            tma_load_2d(w_base + ws * PAIR_W_BYTES, &mapW, (i * 3 + kx) * p.CinPad + ks * BK, 0, wfull(ws));
+                            w_issued++;
+                            if (++ws == PAIR_NW) { ws = 0; wph ^= 1u; }
+                        }
+                    }
+                }
+            }
+            if (!ok) {
+                long long pend = h_issued < PAIR_NH ? h_issued : PAIR_NH;
+                int s = hs; uint32_t ph = hph;
+                for (long long i = 0; i < pend; i++) {
+                    if (--s < 0) { s = PAIR_NH - 1; ph ^= 1u; }
+                    const long long t0 = clock64();
+                    while (!mbar_try(hfull(s), ph) && clock64() - t0 < WAIT_CYCLES) { }
+                }
+                pend = w_issued < PAIR_NW ? w_issued : PAIR_NW;
+                s = ws; ph = wph;
+                for (long long i = 0; i < pend; i++) {
+                    if (--s < 0) { s = PAIR_NW - 1; ph ^= 1u; }
+                    const long long t0 = clock64();
+                    while (!mbar_try(wfull(s), ph) && clock64() - t0 < WAIT_CYCLES) { }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(PAIR_N);
+            int hs = 0, ws = 0;
+            uint32_t hph = 0, wph = 0;
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
+                const int acc = it & 1;
+                const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, p.status, 2)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * PAIR_N);
+                for (int ks = 0; ks < p.kslabs && ok; ks++) {
+                    for (int half = 0; half < 2 && ok; half++) {
+                        if (!mbar_wait(hfull(hs), hph, abort_flag, p.status, 6)) { ok = false; break; }
+                        const uint32_t plane = h_base + hs * PAIR_PLANE_SLOT;
+                        for (int q = 0; q < 6; q++) {
+                            if (!mbar_wait(wfull(ws), wph, abort_flag, p.status, 3)) { ok = false; break; }
+                            tc_fence_after();
+                            /* input row 2j-1+i with i = half + 2*(q/3): the second three products read one block row further down */
+                            const int down = q / 3, kx = q - down * 3;
+                            const uint64_t adesc = make_smem_desc(w_base + ws * PAIR_W_BYTES);
+                            const uint64_t bdesc = make_smem_desc(plane + (uint32_t)((down * PAIR_P + kx) * BK * 4));
+#pragma unroll
+                            for (int j = 0; j < BK / 8; j++)
+                                umma_tf32(d_tmem, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, (ks | half | q | j) ? 1u : 0u);
+                            umma_commit(wempty(ws));
+                            if (++ws == PAIR_NW) { ws = 0; wph ^= 1u; }
+                        }
+                        if (ok) umma_commit(hempty(hs));
+                        if (++hs == PAIR_NH) { hs = 0; hph ^= 1u; }
+                    }
+                }
+                if (ok) umma_commit(tfull_bar(acc));
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const int lower = quarter >> 1;                          /* 0: output rows 2j, 1: rows 2j+1 */
+        const int pr = quarter & 1;                              /* channels pr*32 .. pr*32+31 */
+        const int ch = pr * 32 + lane;
+        const bool chok = ch < p.Cout;
+        const float bv = (p.bias && chok) ? __ldg(p.bias + ch) : 0.0f;
+        const float lo = p.act ? 0.0f : -INFINITY, hi = p.act ? FLT_MAX : INFINITY;
+        float *obase = p.out + p.coff + ch;
+        float *xb = xbuf + pr * 2 * PAIR_X_FLOATS;
+        int it = 0;
+        uint32_t gc = 0;                                         /* chunks exchanged so far (pooled mode) */
+        bool ok = true;
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
+            const int acc = it & 1;
+            const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+            const int img = t / per, rem = t - img * per;
+            const int tyi = rem / p.tiles_x, txi = rem - tyi * p.tiles_x;
+            const int x0 = txi * PAIR_TW;
+            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * PAIR_N);
+#pragma unroll 1
+            for (int c0 = 0; c0 < PAIR_N && ok; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + (uint32_t)c0, r);
+                const int jrow = tyi * PAIR_TJ + (c0 >> 4);          /* this chunk holds row pairs jrow and jrow + 1 */
+                if (p.pool) {
+                    /* pooled row = row pair; horizontal maxima first, then the lower-row warp hands its values to the upper-row warp */
+                    float h[14];
+#pragma unroll
+                    for (int dy = 0; dy < 2; dy++)
+#pragma unroll
+                        for (int px = 0; px < 7; px++)
+                            h[dy * 7 + px] = fmaxf(__uint_as_float(r[dy * 16 + 2 * px]), __uint_as_float(r[dy * 16 + 2 * px + 1]));
+                    const int b = (int)(gc & 1u);
+                    const uint32_t xph = (gc >> 1) & 1u;
+                    float *xs = xb + b * PAIR_X_FLOATS + lane;
+                    if (lower) {
+                        if (!mbar_wait(xempty(pr, b), xph ^ 1u, abort_flag, p.status, 7)) { ok = false; break; }
+#pragma unroll
+                        for (int k = 0; k < 14; k++) xs[k * 32] = h[k];
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(xfull(pr, b));
+                    } else {
+                        if (!mbar_wait(xfull(pr, b), xph, abort_flag, p.status, 8)) { ok = false; break; }
+#pragma unroll
+                        for (int k = 0; k < 14; k++) h[k] = fmaxf(h[k], xs[k * 32]);
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(xempty(pr, b));
+                        if (chok) {
+#pragma unroll
+                            for (int dy = 0; dy < 2; dy++) {
+                                const int yo = jrow + dy;
+                                if (yo >= (p.H >> 1)) break;
+                                float *orow = obase + (((size_t)img * (p.H >> 1) + yo) * (size_t)(p.W >> 1) + (x0 >> 1)) * p.ldo;
+                                const int nx = min(7, (p.W >> 1) - (x0 >> 1));
+#pragma unroll
+                                for (int px = 0; px < 7; px++) {
+                                    if (px < nx) *orow = fminf(fmaxf(h[dy * 7 + px] + bv, lo), hi);
+                                    orow += p.ldo;
+                                }
+                            }
+                        }
+                    }
+                    gc++;
+                } else if (chok) {
+#pragma unroll
+                    for (int dy = 0; dy < 2; dy++) {
+                        const int y = 2 * (jrow + dy) + lower;
+                        if (y >= p.H) break;
+                        float *optr = obase + (((size_t)img * p.H + y) * p.W + x0) * (size_t)p.ldo;
+                        const int nx = min(PAIR_TW, p.W - x0);
+#pragma unroll
+                        for (int dx = 0; dx < PAIR_TW; dx++) {
+                            if (dx < nx) *optr = fminf(fmaxf(__uint_as_float(r[dy * 16 + dx]) + bv, lo), hi);
+                            optr += p.ldo;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar(acc));
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+/* fraction of the MMA columns that produce output pixels for a W x H image (14 x 32 blocks, 16-pixel pitch) */
+double drk_umma_pair_fill(int W, int H)
+{
+    const double tx = (W + PAIR_TW - 1) / PAIR_TW, ty = (H + 2 * PAIR_TJ - 1) / (2 * PAIR_TJ);
+    return (double)W * H / (tx * ty * 2 * PAIR_N);
+}
+
+void drk_umma_pair_geometry(int W, int H, int *tiles_x, int *tiles_y)
+{
+    *tiles_x = (W + PAIR_TW - 1) / PAIR_TW;
+    *tiles_y = (H + 2 * PAIR_TJ - 1) / (2 * PAIR_TJ);
+}
+
+void drk_umma_pair_boxes(unsigned box_plane[4], unsigned box_w[2])
+{
+    box_plane[0] = BK; box_plane[1] = PAIR_P; box_plane[2] = PAIR_TJ + 1; box_plane[3] = 1;
+    box_w[0] = BK; box_w[1] = BM;
+}
+
+int drk_umma_pair_launch(cudaStream_t st, const CUtensorMap *mapO, const CUtensorMap *mapE, const CUtensorMap *mapW, const UmmaParams *p, int grid)
+{
+    static bool attr_done[64];                      /* the opt-in shared-memory size is a per-device function attribute */
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev < 0 || dev >= 64) dev = 0;
+    if (!attr_done[dev]) {
+        cudaError_t e = cudaFuncSetAttribute(k_umma_conv_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        attr_done[dev] = true;
+    }
+    k_umma_conv_pair<<<grid, PAIR_THREADS, PAIR_SMEM, st>>>(*mapO, *mapE, *mapW, *p);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}

@@ -126,6 +126,12 @@ typedef struct dRk_TensorConvPlan dRk_TensorConvPlan;
 /* 1 if the tensor path can evaluate this layer shape (stride 1, 1x1 or 3x3, channel counts it can tile). */
 int dRk_tensor_conv_supported(int W, int H, int Cin, int Cout, int kw, int kh);
 int dRk_tensor_conv_cin_pad(int Cin);
+/* Packing of the reference's [Cin][Cout][kh][kw] filters (include/dR_nodes_conv2d.h:78-80) into the `wT` layout of the
+ * tensor kernel that the planner picks for this layer shape: the rows above, except that layers with Cout <= 64 whose image
+ * tiles well into 14 x 32 blocks use [128][12*CinPad] (two output rows stacked on M, see k_umma_pair.cu).
+ * _packed_floats returns the size of `dst` (0: shape not supported); _pack_weights returns 0 on success. */
+size_t dRk_tensor_conv_packed_floats(int W, int H, int Cin, int Cout, int kw, int kh);
+int dRk_tensor_conv_pack_weights(const float *w, float *dst, int W, int H, int Cin, int Cout, int kw, int kh);
 dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float *wT, const float *bias, float *out,
                                          int n, int W, int H, int Cin, int Cout, int kw, int kh, int act,
                                          int ldo, int coff, int fuse_pool2, int *status);

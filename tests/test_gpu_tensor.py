@@ -34,6 +34,9 @@ TENSOR_SHAPES = [
     ("t_3x3_cin_40_swap", 1, 40, 64, 32, 28, 3),
     ("t_3x3_cout_48_swap", 1, 64, 48, 28, 32, 3),
     ("t_3x3_cout_200", 1, 64, 200, 14, 14, 3),
+    ("t_pair_odd_h", 2, 32, 48, 61, 28, 3),          # Cout <= 64: two output rows per MMA; odd height, idle channel rows
+    ("t_pair_cin16", 1, 16, 64, 56, 56, 3),
+    ("t_pair_cout32", 3, 64, 32, 32, 42, 3),
     ("t_first_rgb", 2, 3, 64, 40, 36, 3),            # few input channels: patch operand gathered by producer warps
     ("t_first_rgb_224", 1, 3, 64, 224, 224, 3),
     ("t_first_c1", 3, 1, 32, 17, 13, 3),             # pixel count not a multiple of the 256-pixel tile
@@ -96,7 +99,7 @@ def test_tf32_network_agrees_with_fp32_on_top1():
     assert rel_err(outs["tf32"], outs["fp32"]) <= 2e-2     # probabilities after 16 TF32 layers
 
 
-@pytest.mark.parametrize("n,cin,cout,h,w", [(1, 64, 64, 56, 56), (2, 128, 256, 28, 28), (3, 256, 512, 14, 14), (2, 32, 64, 12, 20), (1, 64, 64, 224, 224)])
+@pytest.mark.parametrize("n,cin,cout,h,w", [(1, 64, 64, 56, 56), (2, 128, 256, 28, 28), (3, 256, 512, 14, 14), (2, 32, 64, 12, 20), (1, 64, 64, 224, 224), (2, 32, 48, 28, 30), (3, 64, 32, 64, 28)])
 def test_conv_with_fused_maxpool_matches_oracle(n, cin, cout, h, w):
     """conv3x3 + ReLU followed by 2x2/2 max pooling: the tensor kernel's epilogue stores the pooled tensor."""
     x, wt, b = cases.conv_case("fusedpool_%d_%d" % (cin, h), n, cin, cout, h, w, 3, True)
