@@ -15,7 +15,7 @@
 typedef struct {
     cl_mem wbuf[5];                 /* packed weights per dR_ConvAlgo */
     dRk_TensorConvPlan *plan;       /* tensor path: TMA descriptors for this layer's buffers */
-    gboolean fusedPool;             /* the following 2x2/2 max pooling is evaluated in this node's epilogue */
+    gint fusedPool;                 /* 1 / 2: the following 2x2/2 max / average pooling is evaluated in this node's epilogue */
     const float *planSrc;           /* buffers the plan's tensor maps were encoded for */
     float *planDst;
 } dR_ConvDevice;
@@ -203,15 +203,17 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
     c->chosenTensor = c->chosenAlgo == DR_CONV_TENSOR;
     /* conv -> 2x2/2 max pool with no other reader: the tensor kernel's epilogue stores the pooled tensor
        directly into the pooling node's buffer and the pooling node launches nothing */
-    dev(c)->fusedPool = FALSE;
-    if (c->chosenTensor && net->config->fuseGraph && is3x3s1(c) && c->shape.s2 >= 8 && !layer->output && !layer->elided && layer->next_layers->length == 1 &&
+    dev(c)->fusedPool = 0;
+    if (c->chosenTensor && net->config->fuseGraph && is3x3s1(c) && !layer->output && !layer->elided && layer->next_layers->length == 1 &&
         layer->oshape.s0 % 2 == 0 && layer->oshape.s1 % 2 == 0) {
         dR_Node *nx = (dR_Node *)layer->next_layers->first->element;
         if (nx->type == tPooling && nx->previous_layers->length == 1) {
             dR_Pooling_Data *pl = (dR_Pooling_Data *)nx->layer;
-            if (pl->poolingType == tMax && pl->shape.s1 == 2 && pl->shape.s2 == 2 && pl->shape.s3 == 1 &&
-                pl->stride.s1 == 2 && pl->stride.s2 == 2 && pl->stride.s3 == 1) {
-                dev(c)->fusedPool = TRUE;
+            const gint ptype = pl->poolingType == tMax ? 1 : pl->poolingType == tAverage ? 2 : 0;
+            if (ptype && pl->shape.s1 == 2 && pl->shape.s2 == 2 && pl->shape.s3 == 1 &&
+                pl->stride.s1 == 2 && pl->stride.s2 == 2 && pl->stride.s3 == 1 &&
+                dRk_tensor_conv_can_fuse_pool(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3, c->shape.s0, c->shape.s1, ptype)) {
+                dev(c)->fusedPool = ptype;
                 pl->useLMEM = TRUE;                 /* marks "computed by the producer" for dR_pooling_compute */
                 layer->elided = TRUE;
                 layer->act_cstride = layer->oshape.s2;
@@ -311,7 +313,7 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
         if (!d->plan) {
             d->planSrc = src; d->planDst = dst;
             d->plan = dRk_tensor_conv_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR], bias, dst, n, W, H, c->shape.s2, c->shape.s3,
-                                           c->shape.s0, c->shape.s1, act, layer->act_cstride, layer->act_coffset, d->fusedPool ? 1 : 0, (int *)net->statusWord);
+                                           c->shape.s0, c->shape.s1, act, layer->act_cstride, layer->act_coffset, d->fusedPool, (int *)net->statusWord);
             if (!d->plan) { g_print("Conv2d Layer %d: tensor-core plan could not be built\n", layer->layerID); return FALSE; }
         }
         net->clConfig->clError = dRk_tensor_conv_run(s, d->plan);

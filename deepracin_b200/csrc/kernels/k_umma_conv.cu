@@ -693,8 +693,9 @@ void drk_umma_pair_geometry(int W, int H, int *tiles_x, int *tiles_y);
 void drk_umma_pair_boxes(unsigned box_plane[4], unsigned box_w[2]);
 int drk_umma_pair_launch(cudaStream_t st, const CUtensorMap *mapO, const CUtensorMap *mapE, const CUtensorMap *mapW, const UmmaParams *p, int grid);
 int drk_umma_first_supported(int Cin, int Cout, int kw, int kh);
+int drk_umma_first_can_pool(int W, int H, int Cin, int Cout);
 int drk_umma_first_launch(cudaStream_t st, const float *in, const float *wT, const float *bias, float *out, int n, int W, int H, int Cin,
-                          int Cout, int act, int ldi, int ldo, int coff, int *status, int sms);
+                          int Cout, int act, int ldi, int ldo, int coff, int pool, int *status, int sms);
 
 /*
  * Sub-box geometry of a CTA's pixel tile for a W x H image: S boxes of TW x TH pixels, TW*TH a multiple
@@ -772,6 +773,16 @@ static int pick_variant(int W, int H, int Cin, int Cout, int kw, int kh)
     if (Cout <= BM && swap_fill(W, H) >= 0.8 && !getenv("DRK_NO_SWAP") && !no_halo) return VAR_SWAP;
     if (halo_fill(W, H) >= 0.55 && !no_halo) return VAR_HALO;
     return VAR_PLAIN;
+}
+
+/* pool_type: 0 none, 1 max 2x2/2, 2 average 2x2/2 */
+extern "C" int dRk_tensor_conv_can_fuse_pool(int W, int H, int Cin, int Cout, int kw, int kh, int pool_type)
+{
+    if (pool_type == 0) return 1;
+    const int v = pick_variant(W, H, Cin, Cout, kw, kh);
+    if (v == VAR_NONE || v == VAR_FLAT || kw != 3 || (W & 1) || (H & 1)) return 0;
+    if (v == VAR_FIRST) return (pool_type == 1 || pool_type == 2) && drk_umma_first_can_pool(W, H, Cin, Cout);
+    return pool_type == 1;
 }
 
 extern "C" size_t dRk_tensor_conv_packed_floats(int W, int H, int Cin, int Cout, int kw, int kh)
@@ -865,7 +876,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
                                                     int Cin, int Cout, int kw, int kh, int act, int ldo, int coff, int fuse_pool2, int *status)
 {
     if (!dRk_tensor_conv_supported(W, H, Cin, Cout, kw, kh) || n <= 0) return NULL;
-    if (fuse_pool2 && (kw != 3 || (W & 1) || (H & 1) || Cin <= 4)) return NULL;
+    if (!dRk_tensor_conv_can_fuse_pool(W, H, Cin, Cout, kw, kh, fuse_pool2)) return NULL;
     if (ldo % 4 || coff % 4 || ((uintptr_t)out % 16) || ((uintptr_t)in % 16) || ((uintptr_t)wT % 16) || (bias && ((uintptr_t)bias % 16))) return NULL;
     PFN_encodeTiled enc = get_encode();
     if (!enc) return NULL;
@@ -879,6 +890,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     if (variant == VAR_FIRST) {
         pl->first = 1;
         p.n = n; p.W = W; p.H = H; p.Cin = Cin; p.Cout = Cout; p.bias = bias; p.out = out; p.ldo = ldo; p.coff = coff; p.act = act; p.status = status;
+        p.pool = fuse_pool2;
         return pl;
     }
     p.n = n; p.W = W; p.H = H; p.Cin = Cin; p.Cout = Cout;
@@ -974,7 +986,7 @@ extern "C" int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *pl)
     cudaStream_t st = drk_stream(stream);
     if (pl->first)
         return drk_umma_first_launch(st, pl->in, pl->wT, pl->p.bias, pl->p.out, pl->p.n, pl->p.W, pl->p.H, pl->p.Cin, pl->p.Cout, pl->p.act,
-                                     pl->p.Cin, pl->p.ldo, pl->p.coff, pl->p.status, pl->sms);
+                                     pl->p.Cin, pl->p.ldo, pl->p.coff, pl->p.pool, pl->p.status, pl->sms);
     if (pl->pair) return drk_umma_pair_launch(st, &pl->mapA, &pl->mapA2, &pl->mapB, &pl->p, pl->grid);
     if (pl->swap) {
         static bool attr_done[DRK_MAX_DEVICES];

@@ -87,7 +87,7 @@ __device__ __forceinline__ float *store32(float *optr, const uint32_t (&r)[32], 
 template <int CIN, int G>
 __global__ void __launch_bounds__(FIRST_THREADS, 1)
 k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, const float *__restrict__ bias, float *__restrict__ out,
-                  int n, int W, int H, int Cout, int act, int ldi, int ldo, int coff, int *status)
+                  int n, int W, int H, int Cout, int act, int ldi, int ldo, int coff, int pool, int *status)
 {
     using C = FirstCfg<CIN, G>;
     constexpr int TILE_PX = G * FIRST_N;
@@ -107,10 +107,15 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long total_px = (long long)n * H * W;
-    const int total_tiles = (int)((total_px + TILE_PX - 1) / TILE_PX);
+    /* pooled mode (G = 2): a column is position f of the flattened (image, row pair, x) index; group 0 computes the pixel
+       of row 2j, group 1 the pixel below it, and pooled pixel f/2 takes the four values of columns f, f+1 of both groups.
+       The accumulator rows are then ordered so that both groups of a channel sit in one 32-lane quarter of TMEM, 16 lanes
+       apart (row = 32*(ch/16) + 16*group + ch%16): the vertical half of the window is one warp shuffle. */
+    const long long total_f = pool ? total_px / 2 : 0;
+    const int total_tiles = pool ? (int)((total_f + FIRST_N - 1) / FIRST_N) : (int)((total_px + TILE_PX - 1) / TILE_PX);
     /* which 32-lane quarters of TMEM hold output channels: quarter q covers rows 32q..32q+31, row r = group*CP + channel */
     int active_quarters = 0;
-    for (int q = 0; q < 4; q++) active_quarters += ((q * 32) % C::CP) < Cout ? 1 : 0;
+    for (int q = 0; q < 4; q++) active_quarters += ((G == 2 && pool) ? q * 16 : (q * 32) % C::CP) < Cout ? 1 : 0;
     constexpr int TMEM_COLS = 2 * FIRST_N;
 
     if (threadIdx.x == 0) {
@@ -124,12 +129,14 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
         const int chunk_all = i % (C::SLABS * 8), row = i / (C::SLABS * 8);
         const int slab = chunk_all >> 3, chunk = chunk_all & 7;
         const int grp = slab / C::KS, ks = slab - grp * C::KS;
-        const int ch = row - grp * C::CP;
+        int ch;                                                     /* the channel row `row` computes for group `grp`, or -1 */
+        if (G == 2 && pool) ch = ((row >> 4) & 1) == grp ? (row >> 5) * 16 + (row & 15) : -1;
+        else ch = (row >= grp * C::CP && row < (grp + 1) * C::CP) ? row - grp * C::CP : -1;
         uint32_t v[4];
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int k = ks * BK + chunk * 4 + e;
-            v[e] = (ch >= 0 && ch < C::CP && ch < Cout && k < C::K) ? to_tf32(__ldg(wT + (size_t)ch * C::K + k)) : 0u;
+            v[e] = (ch >= 0 && ch < Cout && k < C::K) ? to_tf32(__ldg(wT + (size_t)ch * C::K + k)) : 0u;
         }
         *reinterpret_cast<uint4 *>(gen + slab * (BM * BK * 4) + swz(row, chunk)) = make_uint4(v[0], v[1], v[2], v[3]);
     }
@@ -170,12 +177,46 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
     } else if (warp <= FIRST_EPI_WARPS) {
         const int quarter = warp & 3, half = (warp - 1) >> 2;
         const int row = quarter * 32 + lane;
-        const int grp = row / C::CP, ch = row - grp * C::CP;
-        if (((quarter * 32) % C::CP) < Cout) {
+        const bool pooled = G == 2 && pool;
+        const int grp = pooled ? (lane >> 4) : row / C::CP;
+        const int ch = pooled ? quarter * 16 + (lane & 15) : row - grp * C::CP;
+        if ((pooled ? quarter * 16 : (quarter * 32) % C::CP) < Cout) {
             const bool chok = ch < Cout;
             const float bv = (bias && chok) ? __ldg(bias + ch) : 0.0f;
             const float lo = act ? 0.0f : -INFINITY, hi = act ? FLT_MAX : INFINITY;
             int it = 0;
+            if (pooled) {
+                const float inv = pool == 2 ? 0.25f : 1.0f;
+                for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, it++) {
+                    const int acc = it & 1;
+                    const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
+                    if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, status, 4)) break;
+                    tc_fence_after();
+                    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * FIRST_N + half * (FIRST_N / 2));
+                    const long long f0 = (long long)t * FIRST_N + half * (FIRST_N / 2);
+                    /* pooled pixels are consecutive: (f0 + c0)/2 + k; lanes of group 0 store the even k, group 1 the odd k */
+                    float *optr = out + (size_t)((f0 >> 1) + grp) * ldo + coff + (chok ? ch : 0);
+                    long long left = (total_f >> 1) - (f0 >> 1) - grp;
+#pragma unroll 1
+                    for (int c0 = 0; c0 < FIRST_N / 2; c0 += 32) {
+                        uint32_t r[32];
+                        tmem_ld32(taddr + (uint32_t)c0, r);
+#pragma unroll
+                        for (int k = 0; k < 16; k++) {
+                            const float a = fminf(fmaxf(__uint_as_float(r[2 * k]) + bv, lo), hi), b = fminf(fmaxf(__uint_as_float(r[2 * k + 1]) + bv, lo), hi);
+                            float h = pool == 2 ? a + b : fmaxf(a, b);
+                            const float o = __shfl_xor_sync(0xffffffffu, h, 16);
+                            h = pool == 2 ? (h + o) * inv : fmaxf(h, o);
+                            if ((k & 1) == grp && chok && k < left + grp) optr[(size_t)(k - grp) * ldo] = h;
+                        }
+                        optr += 16 * (size_t)ldo;
+                        left -= 16;
+                    }
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(tempty_bar(acc));
+                }
+            } else
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, it++) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -216,9 +257,21 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
             for (int grp = 0; grp < G; grp++) {
 #pragma unroll
                 for (int k = 0; k < C::KS * BK; k++) v[grp][k] = 0u;
-                const long long g = (long long)t * TILE_PX + grp * FIRST_N + col;
-                if (g < total_px) {
-                    int x, y;
+                long long g;
+                int x, y;
+                bool inside;
+                if (G == 2 && pool) {
+                    const long long f = (long long)t * FIRST_N + col;
+                    inside = f < total_f;
+                    const long long jq = f / W;
+                    x = (int)(f - jq * W);
+                    const int hh = H >> 1;
+                    const long long img = jq / hh;
+                    y = 2 * (int)(jq - img * hh) + grp;
+                    g = (img * H + y) * W + x;
+                } else {
+                    g = (long long)t * TILE_PX + grp * FIRST_N + col;
+                    inside = g < total_px;
                     if (small) {
                         const unsigned gu = (unsigned)g, q = gu / (unsigned)W;
                         x = (int)(gu - q * (unsigned)W);
@@ -228,6 +281,8 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
                         x = (int)(g - q * W);
                         y = (int)(q % H);
                     }
+                }
+                if (inside) {
                     const float *pix = in + (size_t)g * ldi;                 /* the centre pixel */
 #pragma unroll
                     for (int ky = 0; ky < 3; ky++) {
@@ -267,7 +322,7 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
 
 template <int CIN, int G>
 static int launch_first(cudaStream_t st, const float *in, const float *wT, const float *bias, float *out, int n, int W, int H, int Cout,
-                        int act, int ldi, int ldo, int coff, int *status, int sms)
+                        int act, int ldi, int ldo, int coff, int pool, int *status, int sms)
 {
     static bool attr_done[64];                      /* the opt-in shared-memory size is a per-device function attribute */
     int dev = 0;
@@ -278,10 +333,11 @@ static int launch_first(cudaStream_t st, const float *in, const float *wT, const
         if (e != cudaSuccess) return (int)e;
         attr_done[dev] = true;
     }
-    const long long tiles = ((long long)n * H * W + G * FIRST_N - 1) / (G * FIRST_N);
+    if (pool && G != 2) return -1;
+    const long long tiles = pool ? ((long long)n * (H / 2) * W + FIRST_N - 1) / FIRST_N : ((long long)n * H * W + G * FIRST_N - 1) / (G * FIRST_N);
     if (tiles <= 0 || tiles > 0x7fffffffll) return -1;
     const int grid = (int)(tiles < sms ? tiles : sms);
-    k_umma_conv_first<CIN, G><<<grid, FIRST_THREADS, FirstCfg<CIN, G>::SMEM_BYTES, st>>>(in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, status);
+    k_umma_conv_first<CIN, G><<<grid, FIRST_THREADS, FirstCfg<CIN, G>::SMEM_BYTES, st>>>(in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }
@@ -292,19 +348,27 @@ int drk_umma_first_supported(int Cin, int Cout, int kw, int kh)
     return kw == 3 && kh == 3 && Cin >= 1 && Cin <= 4 && Cout >= 16 && Cout <= BM && Cout % 4 == 0;
 }
 
-/* wT: [Cout][9*Cin] with k = (ky*3 + kx)*Cin + c; in: N-HWC with pixel stride ldi */
-int drk_umma_first_launch(cudaStream_t st, const float *in, const float *wT, const float *bias, float *out, int n, int W, int H, int Cin,
-                          int Cout, int act, int ldi, int ldo, int coff, int *status, int sms)
+/* 1 if the 2x2/2 pooling (max or average) that follows the layer can be evaluated in this kernel's epilogue */
+int drk_umma_first_can_pool(int W, int H, int Cin, int Cout)
 {
+    return Cin <= 3 && Cout <= 64 && (W % 2) == 0 && (H % 2) == 0;
+}
+
+/* wT: [Cout][9*Cin] with k = (ky*3 + kx)*Cin + c; in: N-HWC with pixel stride ldi; pool: 0 none, 1 max 2x2/2, 2 average 2x2/2
+ * (`out` is then the (W/2) x (H/2) pooled tensor) */
+int drk_umma_first_launch(cudaStream_t st, const float *in, const float *wT, const float *bias, float *out, int n, int W, int H, int Cin,
+                          int Cout, int act, int ldi, int ldo, int coff, int pool, int *status, int sms)
+{
+    if (pool && !drk_umma_first_can_pool(W, H, Cin, Cout)) return -1;
     const bool two = Cout <= 64;                     /* two pixel groups on the M axis */
     switch (Cin) {
-    case 1: return two ? launch_first<1, 2>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, status, sms)
-                       : launch_first<1, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, status, sms);
-    case 2: return two ? launch_first<2, 2>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, status, sms)
-                       : launch_first<2, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, status, sms);
-    case 3: return two ? launch_first<3, 2>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, status, sms)
-                       : launch_first<3, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, status, sms);
-    case 4: return launch_first<4, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, status, sms);
+    case 1: return two ? launch_first<1, 2>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms)
+                       : launch_first<1, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms);
+    case 2: return two ? launch_first<2, 2>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms)
+                       : launch_first<2, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms);
+    case 3: return two ? launch_first<3, 2>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms)
+                       : launch_first<3, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms);
+    case 4: return launch_first<4, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms);
     }
     return -1;
 }

@@ -120,12 +120,15 @@ int dRk_channel_map(dRk_stream stream, const drk_ChannelMap *map, float *out, si
  * Returns NULL if the shape is not supported by the tensor path (caller falls back to FFMA).
  * `status` is a device int the kernel writes a non-zero code to if a bounded wait runs out.
  * fuse_pool2 = 1 (3x3 layers, even W and H): the epilogue stores the maximum over each 2x2 pixel window,
- * i.e. `out` is the (W/2) x (H/2) result of the 2x2/2 max-pooling node that follows the convolution.
+ * i.e. `out` is the (W/2) x (H/2) result of the 2x2/2 max-pooling node that follows the convolution;
+ * fuse_pool2 = 2: the same with the average (first-layer kernel only).  dRk_tensor_conv_can_fuse_pool tells
+ * whether the kernel picked for a shape can do it (pool_type 1 max, 2 average).
  */
 typedef struct dRk_TensorConvPlan dRk_TensorConvPlan;
 /* 1 if the tensor path can evaluate this layer shape (stride 1, 1x1 or 3x3, channel counts it can tile). */
 int dRk_tensor_conv_supported(int W, int H, int Cin, int Cout, int kw, int kh);
 int dRk_tensor_conv_cin_pad(int Cin);
+int dRk_tensor_conv_can_fuse_pool(int W, int H, int Cin, int Cout, int kw, int kh, int pool_type);
 /* Packing of the reference's [Cin][Cout][kh][kw] filters (include/dR_nodes_conv2d.h:78-80) into the `wT` layout of the
  * tensor kernel that the planner picks for this layer shape: the rows above, except that layers with Cout <= 64 whose image
  * tiles well into 14 x 32 blocks use [128][12*CinPad] (two output rows stacked on M, see k_umma_pair.cu).

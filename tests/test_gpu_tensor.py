@@ -124,6 +124,35 @@ def test_conv_with_fused_maxpool_matches_oracle(n, cin, cout, h, w):
     assert np.array_equal(res[True], res[False])        # same accumulators, max commutes with bias + ReLU
 
 
+@pytest.mark.parametrize("kind", ["max", "average"])
+@pytest.mark.parametrize("n,cin,cout,h,w,act", [(2, 3, 64, 20, 24, 1), (1, 3, 64, 224, 224, 1), (3, 1, 32, 6, 10, 0), (2, 2, 48, 18, 14, 1)])
+def test_first_layer_with_fused_pool_matches_oracle(kind, n, cin, cout, h, w, act):
+    """Few-channel first layer followed by 2x2/2 max or average pooling (SqueezeNet reference graph: conv1 -> average pool):
+    the two rows of a window sit in different TMEM lane quarters and meet through the shared-memory exchange."""
+    x, wt, b = cases.conv_case("firstpool_%d_%d_%s" % (cin, h, kind), n, cin, cout, h, w, 3, True)
+    ref = oracle.pool(oracle.conv2d(x, wt, b, (1, 1), act), (2, 2, 1), (2, 2, 1), 0 if kind == "max" else 1)
+    res, launches = {}, {}
+    for fuse in (True, False):
+        with dr.Environment() as env:
+            g = env.create_graph("CHW")
+            g.batch = n
+            g.math = "tf32"
+            g.fuse = fuse
+            f = dr.feed_node(g, [cin, h, w])
+            c = conv_build(wt, b, 1, act)(g, [f])
+            o = dr.Pooling(c, kind, [1, 2, 2, 1], [1, 2, 2, 1])
+            dr.mark_as_output(o)
+            dr.prepare(g)
+            assert dr.lib.dR_getConvAlgo(c.ptr) == 4
+            dr.feed_data(f, x)
+            res[fuse] = dr.apply(g)[0].reshape(ref.shape)
+            launches[fuse] = dr.lib.dR_getLaunchCount(g.ptr)
+            assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    assert launches[False] - launches[True] == 1        # the pooling node launches nothing when fused
+    assert rel_err(res[True], ref) <= TOL_TF32
+    assert rel_err(res[True], res[False]) <= 1e-6       # same accumulators; the average sums in a different order
+
+
 @pytest.mark.parametrize("n,c,h,w,nout,act", [(64, 64, 4, 4, 256, 1), (16, 512, 7, 7, 512, 0), (33, 32, 2, 8, 768, 1)])
 def test_tensor_fc_matches_oracle(n, c, h, w, nout, act):
     """TF32 mode, batch >= 16: fully connected layers run as a split-K GEMM on the tensor cores."""
