@@ -101,6 +101,40 @@ __global__ void k_pool(const float *__restrict__ in, float *__restrict__ out, in
     }
 }
 
+/* The common windows (2x2/2, 3x3/2) with compile-time extents: every float4 of the window is requested before the first is
+ * used, and the index arithmetic is 32-bit.  Same semantics as k_pool<4>. */
+template <int SX, int SY, int STX, int STY>
+__global__ void __launch_bounds__(256) k_pool_fixed(const float *__restrict__ in, float *__restrict__ out, unsigned total, int W, int H, int C,
+                                                    int Wo, int Ho, int type, int ldi)
+{
+    const unsigned cg = (unsigned)C / 4u;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const unsigned g = i % cg, p = i / cg;
+        const unsigned x = p % (unsigned)Wo, q = p / (unsigned)Wo;
+        const unsigned y = q % (unsigned)Ho, b = q / (unsigned)Ho;
+        const float *src = in + (((size_t)b * H + y * STY) * W + x * STX) * ldi + g * 4;
+        float4 v[SY][SX];
+#pragma unroll
+        for (int dy = 0; dy < SY; dy++)
+#pragma unroll
+            for (int dx = 0; dx < SX; dx++) {
+                const bool ok = (int)(x * STX) + dx < W && (int)(y * STY) + dy < H;
+                v[dy][dx] = ok ? __ldg(reinterpret_cast<const float4 *>(src + ((size_t)dy * W + dx) * ldi)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+        float4 r = type == 0 ? make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int dy = 0; dy < SY; dy++)
+#pragma unroll
+            for (int dx = 0; dx < SX; dx++) {
+                const float4 t = v[dy][dx];
+                if (type == 0) { r.x = fmaxf(r.x, t.x); r.y = fmaxf(r.y, t.y); r.z = fmaxf(r.z, t.z); r.w = fmaxf(r.w, t.w); }
+                else { r.x += t.x; r.y += t.y; r.z += t.z; r.w += t.w; }
+            }
+        if (type != 0) { const float inv = 1.0f / (float)(SX * SY); r.x *= inv; r.y *= inv; r.z *= inv; r.w *= inv; }
+        *reinterpret_cast<float4 *>(out + (size_t)p * C + g * 4) = r;
+    }
+}
+
 /* Large windows (global average pooling and the like): a CTA owns one output pixel and 32 float4 channel groups; its 8
  * rows of threads split the window positions, every step reading 512 contiguous bytes, and combine through shared memory. */
 __global__ void k_pool_bigwindow(const float *__restrict__ in, float *__restrict__ out, int W, int H, int C, int Wo, int Ho,
@@ -147,6 +181,19 @@ extern "C" int dRk_pool(dRk_stream s, const float *in, float *out, int n, int W,
         k_pool_bigwindow<<<grid, block, 0, drk_stream(s)>>>(in, out, W, H, C, Wo, Ho, sx, sy, stx, sty, type, ldi);
         DRK_COUNT_LAUNCH();
         return DRK_LAUNCH_RESULT();
+    }
+    if (vec && total < 0x7fffffffu && (size_t)n * H * W * ldi < 0x7fffffffffffull) {
+        const unsigned fb = drk_blocks(total, 256, 148u * 64u);
+        if (sx == 2 && sy == 2 && stx == 2 && sty == 2) {
+            k_pool_fixed<2, 2, 2, 2><<<fb, 256, 0, drk_stream(s)>>>(in, out, (unsigned)total, W, H, C, Wo, Ho, type, ldi);
+            DRK_COUNT_LAUNCH();
+            return DRK_LAUNCH_RESULT();
+        }
+        if (sx == 3 && sy == 3 && stx == 2 && sty == 2) {
+            k_pool_fixed<3, 3, 2, 2><<<fb, 256, 0, drk_stream(s)>>>(in, out, (unsigned)total, W, H, C, Wo, Ho, type, ldi);
+            DRK_COUNT_LAUNCH();
+            return DRK_LAUNCH_RESULT();
+        }
     }
     if (vec) k_pool<4><<<blocks, 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, Wo, Ho, Co, sx, sy, sz, stx, sty, stz, type, ldi);
     else k_pool<1><<<blocks, 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, Wo, Ho, Co, sx, sy, sz, stx, sty, stz, type, ldi);
@@ -300,21 +347,20 @@ __global__ void k_copy_box(const float *__restrict__ in, float *__restrict__ out
 }
 
 /* same with four channels per thread when every channel count, offset and stride involved is a multiple of 4 */
-__global__ void k_copy_box4(const float *__restrict__ in, float *__restrict__ out, int n, int W, int H, int C, int ldi,
+__global__ void k_copy_box4(const float *__restrict__ in, float *__restrict__ out, unsigned total, int W, int H, int C, int ldi,
                             int ox, int oy, int oz, int w, int h, int c, int DW, int DH, int DC, int dx, int dy, int dz)
 {
-    const int c4 = c / 4;
-    const size_t total = (size_t)n * h * w * c4;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const unsigned c4 = (unsigned)c / 4u;
+    for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int z = (int)(i % c4) * 4;
-        size_t p = i / c4;
-        const int x = (int)(p % w);
-        size_t q = p / w;
-        const int y = (int)(q % h);
-        const int b = (int)(q / h);
+        const unsigned p = i / c4;
+        const int x = (int)(p % (unsigned)w);
+        const unsigned q = p / (unsigned)w;
+        const int y = (int)(q % (unsigned)h);
+        const int b = (int)(q / (unsigned)h);
         const int sx = x + ox, sy = y + oy, sz = z + oz;
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (sx >= 0 && sx < W && sy >= 0 && sy < H && sz >= 0 && sz + 3 < C) v = *reinterpret_cast<const float4 *>(in + (((size_t)b * H + sy) * W + sx) * ldi + sz);
+        if (sx >= 0 && sx < W && sy >= 0 && sy < H && sz >= 0 && sz + 3 < C) v = __ldg(reinterpret_cast<const float4 *>(in + (((size_t)b * H + sy) * W + sx) * ldi + sz));
         *reinterpret_cast<float4 *>(out + (((size_t)b * DH + y + dy) * DW + x + dx) * DC + z + dz) = v;
     }
 }
@@ -326,7 +372,7 @@ static int copy_box(dRk_stream s, const float *in, float *out, int n, int W, int
     const size_t total = (size_t)n * h * w * c;
     const bool vec = c % 4 == 0 && C % 4 == 0 && oz % 4 == 0 && dz % 4 == 0 && ldi % 4 == 0 && DC % 4 == 0 &&
                      ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
-    if (vec) k_copy_box4<<<drk_blocks(total / 4, 256, 148u * 32u), 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, ldi, ox, oy, oz, w, h, c, DW, DH, DC, dx, dy, dz);
+    if (vec && total / 4 < 0x7fffffffu) k_copy_box4<<<drk_blocks(total / 4, 256, 148u * 64u), 256, 0, drk_stream(s)>>>(in, out, (unsigned)(total / 4), W, H, C, ldi, ox, oy, oz, w, h, c, DW, DH, DC, dx, dy, dz);
     else k_copy_box<<<drk_blocks(total, 256, 148u * 32u), 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, ldi, ox, oy, oz, w, h, c, DW, DH, DC, dx, dy, dz);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
@@ -356,22 +402,23 @@ extern "C" int dRk_concat_place(dRk_stream s, const float *in, float *out, int n
  * applied one after the other exactly as the separate kernels would.  One launch replaces the
  * Slice -> ElemWise1Op ... -> Concat preamble of the reference's example graphs (per-channel mean
  * subtraction and channel reordering: examples/squeezenet-v1.1/squeezenet_whole/graph.dr:7-41). */
-__global__ void k_channel_map(drk_ChannelMap m, float *__restrict__ out, size_t pixels)
+__global__ void k_channel_map(const __grid_constant__ drk_ChannelMap m, float *__restrict__ out, size_t pixels)
 {
-    const size_t total = pixels * m.cout;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
-        const int j = (int)(i % m.cout);
-        const size_t p = i / m.cout;
-        float v = m.src[j][p * m.ld[j] + m.ch[j]];
-        for (int k = 0; k < m.nops[j]; k++) v = ew1(v, m.op[j][k], m.scalar[j][k]);
-        out[i] = v;
+    /* a thread per pixel: no index division, consecutive threads read and write consecutive pixels */
+    for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < pixels; p += (size_t)gridDim.x * blockDim.x) {
+        float *o = out + p * m.cout;
+        for (int j = 0; j < m.cout; j++) {
+            float v = __ldg(m.src[j] + p * m.ld[j] + m.ch[j]);
+            for (int k = 0; k < m.nops[j]; k++) v = ew1(v, m.op[j][k], m.scalar[j][k]);
+            o[j] = v;
+        }
     }
 }
 
 extern "C" int dRk_channel_map(dRk_stream s, const drk_ChannelMap *map, float *out, size_t pixels)
 {
     if (!map || map->cout < 1 || map->cout > DRK_CHANNEL_MAP_MAX || pixels == 0) return -1;
-    k_channel_map<<<drk_blocks(pixels * map->cout, 256, 148u * 16u), 256, 0, drk_stream(s)>>>(*map, out, pixels);
+    k_channel_map<<<drk_blocks(pixels, 256, 148u * 32u), 256, 0, drk_stream(s)>>>(*map, out, pixels);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }
