@@ -209,6 +209,7 @@ def run_ours(args):
                         "peak_source": peak_src}
             roof["conv_aggregate"] = {"tflops": aggregate, "frac": (aggregate / peak) if aggregate else None, "launches": n_conv, "ms": round(conv_ms, 4)}
             roof["ms_by_kind"] = {k: round(sum(t for kk, t in prof if kk == k), 4) for k in sorted(set(k for k, _ in prof))}
+            roof["ms_per_layer"] = [[k, round(t, 4)] for k, t in prof if t > 0]        # launch order; fused / elided nodes launch nothing
             achieved = aggregate
             value = batch * world * args.steps / (ms * 1e-3)
             e2e = batch * world * args.steps / (ms_e2e * 1e-3)
