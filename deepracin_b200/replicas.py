@@ -43,6 +43,9 @@ def init(backend=None, device=None):
     if dist.is_initialized():
         return dist
     if backend == "nccl":
+        # NCCL prints its version banner on stdout at NCCL_DEBUG=VERSION; callers print machine-read lines there
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         torch.cuda.set_device(local if device is None else device)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local if device is None else device))
     else:
