@@ -43,20 +43,56 @@ __global__ void __launch_bounds__(FC_WARPS * 32) k_fc_stream(const float *__rest
         }
         __syncthreads();
         if (colok) {
-            /* warp `warp` takes rows warp, warp+8, ...; four rows in flight per lane */
+            /* warp `warp` takes rows warp, warp+8, ...; D rows in flight per lane.  With four or more batch rows the FMAs
+               of a step take long enough to matter, so the D weight rows of the next step are requested before them. */
             int k = warp;
-            for (; k + 3 * FC_WARPS < kn; k += 4 * FC_WARPS) {
-                float4 w0 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k) * Nout + col));
-                float4 w1 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k + FC_WARPS) * Nout + col));
-                float4 w2 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k + 2 * FC_WARPS) * Nout + col));
-                float4 w3 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k + 3 * FC_WARPS) * Nout + col));
+            if (NB <= 2) {
+                for (; k + 3 * FC_WARPS < kn; k += 4 * FC_WARPS) {
+                    float4 w0 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k) * Nout + col));
+                    float4 w1 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k + FC_WARPS) * Nout + col));
+                    float4 w2 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k + 2 * FC_WARPS) * Nout + col));
+                    float4 w3 = __ldg(reinterpret_cast<const float4 *>(w + (size_t)(k0 + k + 3 * FC_WARPS) * Nout + col));
 #pragma unroll
-                for (int b = 0; b < NB; b++) {
-                    const float x0 = xs[b][k], x1 = xs[b][k + FC_WARPS], x2 = xs[b][k + 2 * FC_WARPS], x3 = xs[b][k + 3 * FC_WARPS];
-                    acc[b].x = fmaf(x0, w0.x, acc[b].x); acc[b].y = fmaf(x0, w0.y, acc[b].y); acc[b].z = fmaf(x0, w0.z, acc[b].z); acc[b].w = fmaf(x0, w0.w, acc[b].w);
-                    acc[b].x = fmaf(x1, w1.x, acc[b].x); acc[b].y = fmaf(x1, w1.y, acc[b].y); acc[b].z = fmaf(x1, w1.z, acc[b].z); acc[b].w = fmaf(x1, w1.w, acc[b].w);
-                    acc[b].x = fmaf(x2, w2.x, acc[b].x); acc[b].y = fmaf(x2, w2.y, acc[b].y); acc[b].z = fmaf(x2, w2.z, acc[b].z); acc[b].w = fmaf(x2, w2.w, acc[b].w);
-                    acc[b].x = fmaf(x3, w3.x, acc[b].x); acc[b].y = fmaf(x3, w3.y, acc[b].y); acc[b].z = fmaf(x3, w3.z, acc[b].z); acc[b].w = fmaf(x3, w3.w, acc[b].w);
+                    for (int b = 0; b < NB; b++) {
+                        const float x0 = xs[b][k], x1 = xs[b][k + FC_WARPS], x2 = xs[b][k + 2 * FC_WARPS], x3 = xs[b][k + 3 * FC_WARPS];
+                        acc[b].x = fmaf(x0, w0.x, acc[b].x); acc[b].y = fmaf(x0, w0.y, acc[b].y); acc[b].z = fmaf(x0, w0.z, acc[b].z); acc[b].w = fmaf(x0, w0.w, acc[b].w);
+                        acc[b].x = fmaf(x1, w1.x, acc[b].x); acc[b].y = fmaf(x1, w1.y, acc[b].y); acc[b].z = fmaf(x1, w1.z, acc[b].z); acc[b].w = fmaf(x1, w1.w, acc[b].w);
+                        acc[b].x = fmaf(x2, w2.x, acc[b].x); acc[b].y = fmaf(x2, w2.y, acc[b].y); acc[b].z = fmaf(x2, w2.z, acc[b].z); acc[b].w = fmaf(x2, w2.w, acc[b].w);
+                        acc[b].x = fmaf(x3, w3.x, acc[b].x); acc[b].y = fmaf(x3, w3.y, acc[b].y); acc[b].z = fmaf(x3, w3.z, acc[b].z); acc[b].w = fmaf(x3, w3.w, acc[b].w);
+                    }
+                }
+            } else {
+                constexpr int D = NB <= 4 ? 8 : 4;
+                float4 wv[D], nv[D];
+                const float *wp = w + (size_t)(k0 + k) * Nout + col;
+                const size_t rs = (size_t)FC_WARPS * Nout;
+                bool have = k + (D - 1) * FC_WARPS < kn;
+                if (have) {
+#pragma unroll
+                    for (int d = 0; d < D; d++) wv[d] = __ldg(reinterpret_cast<const float4 *>(wp + d * rs));
+                }
+                while (have) {
+                    const int kc = k;
+                    k += D * FC_WARPS;
+                    wp += D * rs;
+                    have = k + (D - 1) * FC_WARPS < kn;
+                    if (have) {
+#pragma unroll
+                        for (int d = 0; d < D; d++) nv[d] = __ldg(reinterpret_cast<const float4 *>(wp + d * rs));
+                    }
+#pragma unroll
+                    for (int b = 0; b < NB; b++) {
+#pragma unroll
+                        for (int d = 0; d < D; d++) {
+                            const float x = xs[b][kc + d * FC_WARPS];
+                            acc[b].x = fmaf(x, wv[d].x, acc[b].x); acc[b].y = fmaf(x, wv[d].y, acc[b].y);
+                            acc[b].z = fmaf(x, wv[d].z, acc[b].z); acc[b].w = fmaf(x, wv[d].w, acc[b].w);
+                        }
+                    }
+                    if (have) {
+#pragma unroll
+                        for (int d = 0; d < D; d++) wv[d] = nv[d];
+                    }
                 }
             }
             for (; k < kn; k += FC_WARPS) {

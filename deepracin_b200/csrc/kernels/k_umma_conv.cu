@@ -1036,7 +1036,8 @@ struct dRk_TensorFcPlan {
 
 extern "C" int dRk_tensor_fc_supported(int n, int Nin, int Nout)
 {
-    return n >= 16 && n <= BM && Nin % BK == 0 && Nout % 256 == 0 && Nin >= 8 * BK;
+    /* output columns past Nout inside the last 256-wide tile are TMA zero fill (weights) and masked stores */
+    return n >= 16 && n <= BM && Nin % BK == 0 && Nout % 4 == 0 && Nout >= 64 && Nin >= 8 * BK;
 }
 
 extern "C" size_t dRk_tensor_fc_scratch_floats(int n, int Nin, int Nout)
@@ -1044,7 +1045,7 @@ extern "C" size_t dRk_tensor_fc_scratch_floats(int n, int Nin, int Nout)
     if (!dRk_tensor_fc_supported(n, Nin, Nout)) return 0;
     int dev = 0, sms = 148;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    int ksplit = sms / (Nout / 256);
+    int ksplit = sms / ((Nout + 255) / 256);
     if (ksplit < 1) ksplit = 1;
     const int kslabs = Nin / BK;
     if (ksplit > kslabs / 8) ksplit = kslabs / 8 > 0 ? kslabs / 8 : 1;
@@ -1067,7 +1068,7 @@ extern "C" dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wT
     p.n = n; p.W = 1; p.H = 1; p.Cin = Nin; p.CinPad = Nin; p.Cout = Nout;
     p.taps = 1; p.kw = 1; p.pad = 0; p.kslabs = Nin / BK;
     p.S = 0; p.TW = BM; p.TH = 1; p.tiles_x = p.tiles_y = 1;
-    p.total_sub = n; p.m_tiles = 1; p.n_tiles = Nout / 256;
+    p.total_sub = n; p.m_tiles = 1; p.n_tiles = (Nout + 255) / 256;
     p.bias = NULL; p.out = scratch; p.ldo = Nout; p.coff = 0; p.act = 0; p.pool = 0; p.status = status;
     p.ksplit = sms / p.n_tiles;
     if (p.ksplit < 1) p.ksplit = 1;

@@ -142,7 +142,7 @@ int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *plan);
 void dRk_tensor_conv_free(dRk_TensorConvPlan *plan);
 
 /* Fully connected layer on the tensor cores (TF32 inputs, FP32 accumulate) for batches of 16..128 with
- * Nin % 32 == 0 and Nout % 256 == 0: split-K flat GEMM + the reduce step of dRk_fc_f32.  wT is [Nout][Nin]
+ * Nin % 32 == 0 and Nout % 4 == 0 (>= 64): split-K flat GEMM + the reduce step of dRk_fc_f32.  wT is [Nout][Nin]
  * (K contiguous); scratch holds dRk_tensor_fc_scratch_floats() floats.  Same reference kernels as dRk_fc_f32. */
 typedef struct dRk_TensorFcPlan dRk_TensorFcPlan;
 int dRk_tensor_fc_supported(int n, int Nin, int Nout);

@@ -153,7 +153,7 @@ def test_first_layer_with_fused_pool_matches_oracle(kind, n, cin, cout, h, w, ac
     assert rel_err(res[True], res[False]) <= 1e-6       # same accumulators; the average sums in a different order
 
 
-@pytest.mark.parametrize("n,c,h,w,nout,act", [(64, 64, 4, 4, 256, 1), (16, 512, 7, 7, 512, 0), (33, 32, 2, 8, 768, 1)])
+@pytest.mark.parametrize("n,c,h,w,nout,act", [(64, 64, 4, 4, 256, 1), (16, 512, 7, 7, 512, 0), (33, 32, 2, 8, 768, 1), (64, 256, 2, 2, 1000, 0), (20, 64, 2, 2, 72, 1)])
 def test_tensor_fc_matches_oracle(n, c, h, w, nout, act):
     """TF32 mode, batch >= 16: fully connected layers run as a split-K GEMM on the tensor cores."""
     x, wt, b = cases.fc_case("tfc_%d_%d" % (c * h * w, nout), n, c, h, w, nout, True)
