@@ -37,10 +37,12 @@ template <int BN>
 struct Cfg {
     static constexpr int B_STAGE_BYTES = BN * BK * 4;
     static constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-    static constexpr int STAGES_RAW = (SMEM_BUDGET - 2048) / STAGE_BYTES;
+    static constexpr int STG_PITCH = 36;                            /* floats per staged pixel row: 32 channels + 4 (bank spread, 16-byte aligned) */
+    static constexpr int STG_BYTES = 4 * 32 * STG_PITCH * 4;        /* per epilogue warp 32 pixels x 32 channels, transposed for coalesced stores */
+    static constexpr int STAGES_RAW = (SMEM_BUDGET - 2048 - STG_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + STG_BYTES;
 };
 
 template <int BN>
@@ -194,6 +196,23 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                 }
             }
             float *dst = p.out + (size_t)ksi * p.split_stride + pix * p.ldo + p.coff + nt * BN;
+            /* Not pooled: a lane holds 32 channels of ONE pixel, so storing from there touches 32 cache lines per instruction.
+               Each 32 x 32 chunk goes through a transposing stage in shared memory instead: afterwards lane l stores channels
+               4*(l%8).. of pixels i*4 + l/8 (i = 0..7), i.e. an instruction writes four full 128-byte runs. */
+            float *rowptr[8];
+            uint32_t rowok = 0;
+            if (!p.pool) {
+                const uint32_t vm = __ballot_sync(0xffffffffu, valid);
+                const unsigned long long d64 = (unsigned long long)(uintptr_t)dst;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int src = i * 4 + (lane >> 3);
+                    const uint32_t lo32 = __shfl_sync(0xffffffffu, (uint32_t)d64, src), hi32 = __shfl_sync(0xffffffffu, (uint32_t)(d64 >> 32), src);
+                    rowptr[i] = reinterpret_cast<float *>((uintptr_t)(((unsigned long long)hi32 << 32) | lo32));
+                    rowok |= ((vm >> src) & 1u) << i;
+                }
+            }
+            float *stg = reinterpret_cast<float *>(gen + C::STAGES * C::STAGE_BYTES + 256) + (warp - 2) * 32 * C::STG_PITCH;
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
@@ -202,7 +221,26 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                 uint32_t r[32];
                 tmem_ld32(taddr + (uint32_t)c0, r);
                 const int col = nt * BN + c0;
-                if (p.pool) {
+                if (!p.pool) {
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<uint4 *>(stg + lane * C::STG_PITCH + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                    __syncwarp();
+                    const int cl = (lane & 7) * 4;
+                    if (col + cl < p.Cout) {
+                        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (p.bias) b = __ldg(reinterpret_cast<const float4 *>(p.bias + col + cl));
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            float4 v = *reinterpret_cast<const float4 *>(stg + (i * 4 + (lane >> 3)) * C::STG_PITCH + cl);
+                            v.x = drk_act(v.x + b.x, p.act); v.y = drk_act(v.y + b.y, p.act); v.z = drk_act(v.z + b.z, p.act); v.w = drk_act(v.w + b.w, p.act);
+                            if ((rowok >> i) & 1u) *reinterpret_cast<float4 *>(rowptr[i] + c0 + cl) = v;
+                        }
+                    }
+                    continue;
+                }
+                {
                     /* bias and activation are monotone, so max commutes with them: reduce the raw accumulators */
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
