@@ -300,10 +300,13 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
 template <int BN>
 struct HaloCfg {
     static constexpr int B_STAGE_BYTES = BN * BK * 4;
-    static constexpr int NB_RAW = (SMEM_BUDGET - 2048 - HALO_NA * HALO_A_SLOT) / B_STAGE_BYTES;
+    /* transposing store stage as in Cfg<BN>, where shared memory allows it without giving up a filter stage (BN <= 128) */
+    static constexpr int STG_PITCH = 36;
+    static constexpr int STG_BYTES = BN <= 128 ? 4 * 32 * STG_PITCH * 4 : 0;
+    static constexpr int NB_RAW = (SMEM_BUDGET - 2048 - HALO_NA * HALO_A_SLOT - STG_BYTES) / B_STAGE_BYTES;
     static constexpr int NB = NB_RAW > 10 ? 10 : NB_RAW;
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr int SMEM_BYTES = HALO_NA * HALO_A_SLOT + NB * B_STAGE_BYTES + 1024 + 512;
+    static constexpr int SMEM_BYTES = HALO_NA * HALO_A_SLOT + NB * B_STAGE_BYTES + 1024 + 512 + STG_BYTES;
 };
 
 template <int BN>
@@ -444,6 +447,22 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                 pix = ((size_t)img * p.H + y) * p.W + x;
             }
             float *dst = p.out + pix * p.ldo + p.coff + nt * BN;
+            /* not pooled, BN <= 128: stores go through the transposing stage (see k_umma_conv) */
+            const bool staged = C::STG_BYTES > 0 && !p.pool;
+            float *rowptr[8];
+            uint32_t rowok = 0;
+            if (staged) {
+                const uint32_t vm = __ballot_sync(0xffffffffu, valid);
+                const unsigned long long d64 = (unsigned long long)(uintptr_t)dst;
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const int src = i * 4 + (lane >> 3);
+                    const uint32_t lo32 = __shfl_sync(0xffffffffu, (uint32_t)d64, src), hi32 = __shfl_sync(0xffffffffu, (uint32_t)(d64 >> 32), src);
+                    rowptr[i] = reinterpret_cast<float *>((uintptr_t)(((unsigned long long)hi32 << 32) | lo32));
+                    rowok |= ((vm >> src) & 1u) << i;
+                }
+            }
+            float *stg = reinterpret_cast<float *>(gen + HALO_NA * HALO_A_SLOT + C::NB * C::B_STAGE_BYTES + 512) + (warp - 2) * 32 * C::STG_PITCH;
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
@@ -452,6 +471,25 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                 uint32_t r[32];
                 tmem_ld32(taddr + (uint32_t)c0, r);
                 const int col = nt * BN + c0;
+                if (staged) {
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 32; j += 4)
+                        *reinterpret_cast<uint4 *>(stg + lane * C::STG_PITCH + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+                    __syncwarp();
+                    const int cl = (lane & 7) * 4;
+                    if (col + cl < p.Cout) {
+                        float4 b = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (p.bias) b = __ldg(reinterpret_cast<const float4 *>(p.bias + col + cl));
+#pragma unroll
+                        for (int i = 0; i < 8; i++) {
+                            float4 v = *reinterpret_cast<const float4 *>(stg + (i * 4 + (lane >> 3)) * C::STG_PITCH + cl);
+                            v.x = drk_act(v.x + b.x, p.act); v.y = drk_act(v.y + b.y, p.act); v.z = drk_act(v.z + b.z, p.act); v.w = drk_act(v.w + b.w, p.act);
+                            if ((rowok >> i) & 1u) *reinterpret_cast<float4 *>(rowptr[i] + c0 + cl) = v;
+                        }
+                    }
+                    continue;
+                }
                 if (p.pool) {
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
