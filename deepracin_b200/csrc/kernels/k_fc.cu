@@ -25,6 +25,8 @@ __global__ void __launch_bounds__(FC_WARPS * 32) k_fc_stream(const float *__rest
 {
     __shared__ float xs[NB][FC_KSTAGE];
     __shared__ float4 red[FC_WARPS][32];
+    drk_dep_trigger();
+    drk_dep_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int col = blockIdx.x * FC_COLS + lane * 4;
     const int kbeg = blockIdx.y * kchunk;
@@ -127,6 +129,8 @@ __global__ void __launch_bounds__(FC_WARPS * 32) k_fc_stream(const float *__rest
 __global__ void k_fc_reduce(const float *__restrict__ partial, const float *__restrict__ bias, float *__restrict__ out,
                             int total, int Nout, int splits, int act)
 {
+    drk_dep_trigger();
+    drk_dep_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
     float s = 0.f;
@@ -137,7 +141,7 @@ __global__ void k_fc_reduce(const float *__restrict__ partial, const float *__re
 
 int drk_fc_reduce_launch(cudaStream_t st, const float *partial, const float *bias, float *out, int total, int Nout, int splits, int act)
 {
-    k_fc_reduce<<<(total + 255) / 256, 256, 0, st>>>(partial, bias, out, total, Nout, splits, act);
+    drk_launch_dep(k_fc_reduce, dim3((total + 255) / 256), dim3(256), 0, st, partial, bias, out, total, Nout, splits, act);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }
@@ -180,11 +184,11 @@ extern "C" int dRk_fc_f32(dRk_stream stream, const float *in, const float *w, co
     int rc;
     if (n <= FC_MAXB && Nout % 4 == 0 && ((uintptr_t)w % 16) == 0 && ((uintptr_t)scratch % 16) == 0) {
         dim3 grid((Nout + FC_COLS - 1) / FC_COLS, splits);
-        if (n <= 1) k_fc_stream<1><<<grid, FC_WARPS * 32, 0, st>>>(in, w, scratch, n, Nin, Nout, kchunk);
-        else if (n <= 2) k_fc_stream<2><<<grid, FC_WARPS * 32, 0, st>>>(in, w, scratch, n, Nin, Nout, kchunk);
-        else if (n <= 4) k_fc_stream<4><<<grid, FC_WARPS * 32, 0, st>>>(in, w, scratch, n, Nin, Nout, kchunk);
-        else if (n <= 8) k_fc_stream<8><<<grid, FC_WARPS * 32, 0, st>>>(in, w, scratch, n, Nin, Nout, kchunk);
-        else k_fc_stream<16><<<grid, FC_WARPS * 32, 0, st>>>(in, w, scratch, n, Nin, Nout, kchunk);
+        if (n <= 1) drk_launch_dep(k_fc_stream<1>, grid, dim3(FC_WARPS * 32), 0, st, in, w, scratch, n, Nin, Nout, kchunk);
+        else if (n <= 2) drk_launch_dep(k_fc_stream<2>, grid, dim3(FC_WARPS * 32), 0, st, in, w, scratch, n, Nin, Nout, kchunk);
+        else if (n <= 4) drk_launch_dep(k_fc_stream<4>, grid, dim3(FC_WARPS * 32), 0, st, in, w, scratch, n, Nin, Nout, kchunk);
+        else if (n <= 8) drk_launch_dep(k_fc_stream<8>, grid, dim3(FC_WARPS * 32), 0, st, in, w, scratch, n, Nin, Nout, kchunk);
+        else drk_launch_dep(k_fc_stream<16>, grid, dim3(FC_WARPS * 32), 0, st, in, w, scratch, n, Nin, Nout, kchunk);
         DRK_COUNT_LAUNCH();
         rc = DRK_LAUNCH_RESULT();
     } else {
@@ -201,7 +205,7 @@ extern "C" int dRk_fc_f32(dRk_stream stream, const float *in, const float *w, co
     }
     if (rc != 0) return rc;
     const int total = n * Nout;
-    k_fc_reduce<<<(total + 255) / 256, 256, 0, st>>>(scratch, bias, out, total, Nout, splits, act);
+    drk_launch_dep(k_fc_reduce, dim3((total + 255) / 256), dim3(256), 0, st, scratch, bias, out, total, Nout, splits, act);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }

@@ -3,6 +3,7 @@
  * softmax, element-wise math, slice / crop-or-pad / concat placement.  All are HBM-bound
  * streaming kernels over N-HWC activations with 128-bit accesses where alignment allows.
  */
+#include <stdlib.h>
 #include "k_common.cuh"
 
 thread_local long g_dRk_launches = 0;
@@ -14,6 +15,8 @@ extern "C" void dRk_launch_count_reset(void) { g_dRk_launches = 0; }
  * CHW->HWC is rows=C, cols=H*W, HWC->CHW the reverse. */
 __global__ void k_transpose(const float *__restrict__ src, float *__restrict__ dst, int rows, int cols)
 {
+    drk_dep_trigger();
+    drk_dep_wait();
     __shared__ float tile[32][33];
     const size_t img = (size_t)blockIdx.z * rows * cols;
     const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
@@ -33,7 +36,7 @@ static int transpose_launch(dRk_stream s, const float *src, float *dst, int n, i
     if (n <= 0 || rows <= 0 || cols <= 0) return -1;
     dim3 block(32, 8), grid((cols + 31) / 32, (rows + 31) / 32, n);
     if (grid.y > 65535u || grid.z > 65535u) return -2;
-    k_transpose<<<grid, block, 0, drk_stream(s)>>>(src, dst, rows, cols);
+    drk_launch_dep(k_transpose, dim3(grid), dim3(block), 0, drk_stream(s), src, dst, rows, cols);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }
@@ -55,6 +58,8 @@ template <int VEC>
 __global__ void k_pool(const float *__restrict__ in, float *__restrict__ out, int n, int W, int H, int C, int Wo, int Ho, int Co,
                        int sx, int sy, int sz, int stx, int sty, int stz, int type, int ldi)
 {
+    drk_dep_trigger();
+    drk_dep_wait();
     const int cg = Co / VEC;
     const size_t total = (size_t)n * Ho * Wo * cg;
     const float inv = 1.0f / (float)(sx * sy * sz);
@@ -107,6 +112,8 @@ template <int SX, int SY, int STX, int STY>
 __global__ void __launch_bounds__(256) k_pool_fixed(const float *__restrict__ in, float *__restrict__ out, unsigned total, int W, int H, int C,
                                                     int Wo, int Ho, int type, int ldi)
 {
+    drk_dep_trigger();
+    drk_dep_wait();
     const unsigned cg = (unsigned)C / 4u;
     for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const unsigned g = i % cg, p = i / cg;
@@ -140,6 +147,8 @@ __global__ void __launch_bounds__(256) k_pool_fixed(const float *__restrict__ in
 __global__ void k_pool_bigwindow(const float *__restrict__ in, float *__restrict__ out, int W, int H, int C, int Wo, int Ho,
                                  int sx, int sy, int stx, int sty, int type, int ldi)
 {
+    drk_dep_trigger();
+    drk_dep_wait();
     __shared__ float4 part[8][32];
     const int g = blockIdx.x * 32 + threadIdx.x;            /* float4 channel group */
     const int ox = blockIdx.y % Wo, oy = blockIdx.y / Wo, b = blockIdx.z;
@@ -178,25 +187,25 @@ extern "C" int dRk_pool(dRk_stream s, const float *in, float *out, int n, int W,
     const unsigned blocks = drk_blocks(total, 256, 148u * 32u);
     if (vec && sx * sy >= 64 && (size_t)Wo * Ho <= 65535u && n <= 65535) {
         dim3 grid((C / 4 + 31) / 32, Wo * Ho, n), block(32, 8);
-        k_pool_bigwindow<<<grid, block, 0, drk_stream(s)>>>(in, out, W, H, C, Wo, Ho, sx, sy, stx, sty, type, ldi);
+        drk_launch_dep(k_pool_bigwindow, dim3(grid), dim3(block), 0, drk_stream(s), in, out, W, H, C, Wo, Ho, sx, sy, stx, sty, type, ldi);
         DRK_COUNT_LAUNCH();
         return DRK_LAUNCH_RESULT();
     }
     if (vec && total < 0x7fffffffu && (size_t)n * H * W * ldi < 0x7fffffffffffull) {
         const unsigned fb = drk_blocks(total, 256, 148u * 64u);
         if (sx == 2 && sy == 2 && stx == 2 && sty == 2) {
-            k_pool_fixed<2, 2, 2, 2><<<fb, 256, 0, drk_stream(s)>>>(in, out, (unsigned)total, W, H, C, Wo, Ho, type, ldi);
+            drk_launch_dep(k_pool_fixed<2, 2, 2, 2>, dim3(fb), dim3(256), 0, drk_stream(s), in, out, (unsigned)total, W, H, C, Wo, Ho, type, ldi);
             DRK_COUNT_LAUNCH();
             return DRK_LAUNCH_RESULT();
         }
         if (sx == 3 && sy == 3 && stx == 2 && sty == 2) {
-            k_pool_fixed<3, 3, 2, 2><<<fb, 256, 0, drk_stream(s)>>>(in, out, (unsigned)total, W, H, C, Wo, Ho, type, ldi);
+            drk_launch_dep(k_pool_fixed<3, 3, 2, 2>, dim3(fb), dim3(256), 0, drk_stream(s), in, out, (unsigned)total, W, H, C, Wo, Ho, type, ldi);
             DRK_COUNT_LAUNCH();
             return DRK_LAUNCH_RESULT();
         }
     }
-    if (vec) k_pool<4><<<blocks, 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, Wo, Ho, Co, sx, sy, sz, stx, sty, stz, type, ldi);
-    else k_pool<1><<<blocks, 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, Wo, Ho, Co, sx, sy, sz, stx, sty, stz, type, ldi);
+    if (vec) drk_launch_dep(k_pool<4>, dim3(blocks), dim3(256), 0, drk_stream(s), in, out, n, W, H, C, Wo, Ho, Co, sx, sy, sz, stx, sty, stz, type, ldi);
+    else drk_launch_dep(k_pool<1>, dim3(blocks), dim3(256), 0, drk_stream(s), in, out, n, W, H, C, Wo, Ho, Co, sx, sy, sz, stx, sty, stz, type, ldi);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }
@@ -224,6 +233,8 @@ __device__ __forceinline__ float block_reduce(float v, bool is_max, float *red)
 
 __global__ void k_softmax(const float *__restrict__ in, float *__restrict__ out, int len)
 {
+    drk_dep_trigger();
+    drk_dep_wait();
     __shared__ float red[32];
     const float *x = in + (size_t)blockIdx.x * len;
     float *y = out + (size_t)blockIdx.x * len;
@@ -240,7 +251,7 @@ __global__ void k_softmax(const float *__restrict__ in, float *__restrict__ out,
 extern "C" int dRk_softmax(dRk_stream s, const float *in, float *out, int n, int len)
 {
     if (n <= 0 || len <= 0) return -1;
-    k_softmax<<<n, len >= 4096 ? 1024 : 256, 0, drk_stream(s)>>>(in, out, len);
+    drk_launch_dep(k_softmax, dim3(n), dim3(len >= 4096 ? 1024 : 256), 0, drk_stream(s), in, out, len);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }
@@ -276,6 +287,8 @@ __device__ __forceinline__ float ew2(float a, float b, int op)
 
 __global__ void k_elemwise1(const float *__restrict__ in, float *__restrict__ out, size_t len, int op, float s, int vec)
 {
+    drk_dep_trigger();
+    drk_dep_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x, t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t done = 0;
     if (vec) {
@@ -292,6 +305,8 @@ __global__ void k_elemwise1(const float *__restrict__ in, float *__restrict__ ou
 
 __global__ void k_elemwise2(const float *__restrict__ a, const float *__restrict__ b, float *__restrict__ out, size_t len, int op, int vec)
 {
+    drk_dep_trigger();
+    drk_dep_wait();
     const size_t stride = (size_t)gridDim.x * blockDim.x, t0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t done = 0;
     if (vec) {
@@ -310,7 +325,7 @@ extern "C" int dRk_elemwise1(dRk_stream s, const float *in, float *out, size_t l
 {
     if (len == 0 || op < 0 || op > 8) return -1;
     const int vec = ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
-    k_elemwise1<<<drk_blocks(len / 4 + 1, 256, 148u * 16u), 256, 0, drk_stream(s)>>>(in, out, len, op, scalar, vec);
+    drk_launch_dep(k_elemwise1, dim3(drk_blocks(len / 4 + 1, 256, 148u * 16u)), dim3(256), 0, drk_stream(s), in, out, len, op, scalar, vec);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }
@@ -319,7 +334,7 @@ extern "C" int dRk_elemwise2(dRk_stream s, const float *a, const float *b, float
 {
     if (len == 0 || op < 0 || op > 4) return -1;
     const int vec = ((uintptr_t)a % 16 == 0) && ((uintptr_t)b % 16 == 0) && ((uintptr_t)out % 16 == 0);
-    k_elemwise2<<<drk_blocks(len / 4 + 1, 256, 148u * 16u), 256, 0, drk_stream(s)>>>(a, b, out, len, op, vec);
+    drk_launch_dep(k_elemwise2, dim3(drk_blocks(len / 4 + 1, 256, 148u * 16u)), dim3(256), 0, drk_stream(s), a, b, out, len, op, vec);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }
@@ -331,6 +346,8 @@ extern "C" int dRk_elemwise2(dRk_stream s, const float *a, const float *b, float
 __global__ void k_copy_box(const float *__restrict__ in, float *__restrict__ out, int n, int W, int H, int C, int ldi,
                            int ox, int oy, int oz, int w, int h, int c, int DW, int DH, int DC, int dx, int dy, int dz)
 {
+    drk_dep_trigger();
+    drk_dep_wait();
     const size_t total = (size_t)n * h * w * c;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         int z = (int)(i % c);
@@ -350,6 +367,8 @@ __global__ void k_copy_box(const float *__restrict__ in, float *__restrict__ out
 __global__ void k_copy_box4(const float *__restrict__ in, float *__restrict__ out, unsigned total, int W, int H, int C, int ldi,
                             int ox, int oy, int oz, int w, int h, int c, int DW, int DH, int DC, int dx, int dy, int dz)
 {
+    drk_dep_trigger();
+    drk_dep_wait();
     const unsigned c4 = (unsigned)c / 4u;
     for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
         const int z = (int)(i % c4) * 4;
@@ -372,8 +391,8 @@ static int copy_box(dRk_stream s, const float *in, float *out, int n, int W, int
     const size_t total = (size_t)n * h * w * c;
     const bool vec = c % 4 == 0 && C % 4 == 0 && oz % 4 == 0 && dz % 4 == 0 && ldi % 4 == 0 && DC % 4 == 0 &&
                      ((uintptr_t)in % 16 == 0) && ((uintptr_t)out % 16 == 0);
-    if (vec && total / 4 < 0x7fffffffu) k_copy_box4<<<drk_blocks(total / 4, 256, 148u * 64u), 256, 0, drk_stream(s)>>>(in, out, (unsigned)(total / 4), W, H, C, ldi, ox, oy, oz, w, h, c, DW, DH, DC, dx, dy, dz);
-    else k_copy_box<<<drk_blocks(total, 256, 148u * 32u), 256, 0, drk_stream(s)>>>(in, out, n, W, H, C, ldi, ox, oy, oz, w, h, c, DW, DH, DC, dx, dy, dz);
+    if (vec && total / 4 < 0x7fffffffu) drk_launch_dep(k_copy_box4, dim3(drk_blocks(total / 4, 256, 148u * 64u)), dim3(256), 0, drk_stream(s), in, out, (unsigned)(total / 4), W, H, C, ldi, ox, oy, oz, w, h, c, DW, DH, DC, dx, dy, dz);
+    else drk_launch_dep(k_copy_box, dim3(drk_blocks(total, 256, 148u * 32u)), dim3(256), 0, drk_stream(s), in, out, n, W, H, C, ldi, ox, oy, oz, w, h, c, DW, DH, DC, dx, dy, dz);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }
@@ -404,6 +423,8 @@ extern "C" int dRk_concat_place(dRk_stream s, const float *in, float *out, int n
  * subtraction and channel reordering: examples/squeezenet-v1.1/squeezenet_whole/graph.dr:7-41). */
 __global__ void k_channel_map(const __grid_constant__ drk_ChannelMap m, float *__restrict__ out, size_t pixels)
 {
+    drk_dep_trigger();
+    drk_dep_wait();
     /* a thread per pixel: no index division, consecutive threads read and write consecutive pixels */
     for (size_t p = (size_t)blockIdx.x * blockDim.x + threadIdx.x; p < pixels; p += (size_t)gridDim.x * blockDim.x) {
         float *o = out + p * m.cout;
@@ -418,7 +439,14 @@ __global__ void k_channel_map(const __grid_constant__ drk_ChannelMap m, float *_
 extern "C" int dRk_channel_map(dRk_stream s, const drk_ChannelMap *map, float *out, size_t pixels)
 {
     if (!map || map->cout < 1 || map->cout > DRK_CHANNEL_MAP_MAX || pixels == 0) return -1;
-    k_channel_map<<<drk_blocks(pixels, 256, 148u * 32u), 256, 0, drk_stream(s)>>>(*map, out, pixels);
+    drk_launch_dep(k_channel_map, dim3(drk_blocks(pixels, 256, 148u * 32u)), dim3(256), 0, drk_stream(s), *map, out, pixels);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
+}
+
+int drk_dep_launch_enabled()
+{
+    static int on = -1;
+    if (on < 0) on = getenv("DRK_NO_DEP_LAUNCH") ? 0 : 1;
+    return on;
 }

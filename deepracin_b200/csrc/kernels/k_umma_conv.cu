@@ -51,6 +51,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
 {
     using C = Cfg<BN>;
     extern __shared__ uint8_t smem_raw[];
+    drk_dep_trigger();
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                       /* swizzled tiles need 1024-byte alignment */
     uint8_t *gen = smem_raw + (base - raw);
@@ -76,6 +77,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    drk_dep_wait();                 /* set-up above overlaps the previous kernel; its outputs are visible from here on */
 
     if (warp == 0) {
         /* ------------------------------------------------ TMA producer (one lane) */
@@ -315,6 +317,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 {
     using C = HaloCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
+    drk_dep_trigger();
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - raw);
@@ -346,6 +349,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    drk_dep_wait();                 /* set-up above overlaps the previous kernel; its outputs are visible from here on */
 
     if (warp == 0) {
         if (lane == 0) {
@@ -551,6 +555,7 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1)
 k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW, const UmmaParams p)
 {
     extern __shared__ uint8_t smem_raw[];
+    drk_dep_trigger();
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - raw);
@@ -583,6 +588,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    drk_dep_wait();                 /* set-up above overlaps the previous kernel; its outputs are visible from here on */
 
     if (warp == 0) {
         if (lane == 0) {
@@ -928,7 +934,7 @@ static int launch_umma_halo(cudaStream_t st, dRk_TensorConvPlan *pl)
         if (e != cudaSuccess) return (int)e;
         attr_done[dev] = true;
     }
-    k_umma_conv_halo<BN><<<pl->grid, UMMA_THREADS, HaloCfg<BN>::SMEM_BYTES, st>>>(pl->mapA, pl->mapB, pl->p);
+    drk_launch_dep(k_umma_conv_halo<BN>, dim3(pl->grid), dim3(UMMA_THREADS), HaloCfg<BN>::SMEM_BYTES, st, pl->mapA, pl->mapB, pl->p);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }
@@ -943,7 +949,7 @@ static int launch_umma(cudaStream_t st, dRk_TensorConvPlan *pl)
         if (e != cudaSuccess) return (int)e;
         attr_done[dev] = true;
     }
-    k_umma_conv<BN><<<pl->grid, UMMA_THREADS, Cfg<BN>::SMEM_BYTES, st>>>(pl->mapA, pl->mapB, pl->p);
+    drk_launch_dep(k_umma_conv<BN>, dim3(pl->grid), dim3(UMMA_THREADS), Cfg<BN>::SMEM_BYTES, st, pl->mapA, pl->mapB, pl->p);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }
@@ -1072,7 +1078,7 @@ extern "C" int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *pl)
             if (e != cudaSuccess) return (int)e;
             attr_done[dev] = true;
         }
-        k_umma_conv_swap<<<pl->grid, UMMA_THREADS, SWAP_SMEM, st>>>(pl->mapA, pl->mapB, pl->p);
+        drk_launch_dep(k_umma_conv_swap, dim3(pl->grid), dim3(UMMA_THREADS), SWAP_SMEM, st, pl->mapA, pl->mapB, pl->p);
         DRK_COUNT_LAUNCH();
         return DRK_LAUNCH_RESULT();
     }

@@ -92,6 +92,7 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
     using C = FirstCfg<CIN, G>;
     constexpr int TILE_PX = G * FIRST_N;
     extern __shared__ uint8_t smem_raw[];
+    drk_dep_trigger();
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - raw);
@@ -146,6 +147,7 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    drk_dep_wait();                 /* the filter tile and set-up above overlap the previous kernel; its outputs are visible from here on */
 
     if (warp == 0) {
         if (lane == 0) {
@@ -337,7 +339,7 @@ static int launch_first(cudaStream_t st, const float *in, const float *wT, const
     const long long tiles = pool ? ((long long)n * (H / 2) * W + FIRST_N - 1) / FIRST_N : ((long long)n * H * W + G * FIRST_N - 1) / (G * FIRST_N);
     if (tiles <= 0 || tiles > 0x7fffffffll) return -1;
     const int grid = (int)(tiles < sms ? tiles : sms);
-    k_umma_conv_first<CIN, G><<<grid, FIRST_THREADS, FirstCfg<CIN, G>::SMEM_BYTES, st>>>(in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status);
+    drk_launch_dep(k_umma_conv_first<CIN, G>, dim3(grid), dim3(FIRST_THREADS), FirstCfg<CIN, G>::SMEM_BYTES, st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }

@@ -48,6 +48,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
                  const UmmaParams p)
 {
     extern __shared__ uint8_t smem_raw[];
+    drk_dep_trigger();
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - raw);
@@ -86,6 +87,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    drk_dep_wait();                 /* set-up above overlaps the previous kernel; its outputs are visible from here on */
 
     if (warp == 0) {
         if (lane == 0) {
@@ -296,7 +298,7 @@ int drk_umma_pair_launch(cudaStream_t st, const CUtensorMap *mapO, const CUtenso
         if (e != cudaSuccess) return (int)e;
         attr_done[dev] = true;
     }
-    k_umma_conv_pair<<<grid, PAIR_THREADS, PAIR_SMEM, st>>>(*mapO, *mapE, *mapW, *p);
+    drk_launch_dep(k_umma_conv_pair, dim3(grid), dim3(PAIR_THREADS), PAIR_SMEM, st, *mapO, *mapE, *mapW, *p);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }
