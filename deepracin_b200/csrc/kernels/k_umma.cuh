@@ -54,10 +54,9 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity)
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
-/* bounded wait; false = aborted (by this thread's timeout or by another role) */
-static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+/* bounded wait, slow path; false = aborted (by this thread's timeout or by another role) */
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
 {
-    if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     for (;;) {
         for (int i = 0; i < 64; i++)
@@ -69,6 +68,13 @@ static __device__ __noinline__ bool mbar_wait(uint32_t bar, uint32_t parity, vol
             return false;
         }
     }
+}
+/* The first probe is inline: the MMA issuer can only run about two instructions ahead of the tensor pipe, so a function
+ * call between two groups of MMAs (measured: ~45 clocks per group of four) shows up as idle pipe time. */
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+{
+    if (mbar_try(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, code);
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar)
 {
