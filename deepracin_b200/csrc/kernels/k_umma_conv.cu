@@ -531,10 +531,12 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 /*
  * Transposed halo variant for layers with few output channels (Cout <= 128).
  *
- * A tcgen05.mma streams its A operand (128 rows x 32 B) into the tensor core in about the time a
- * 128 x 256 x 8 product takes, so an instruction with N < 256 runs at N/256 of the pipe's rate
- * (measured: ~93 ns per instruction for N = 64, 128 and 256 alike).  With pixels on M and output
- * channels on N a 64-channel layer can therefore use a quarter of the pipe.  This variant computes the
+ * A tcgen05.mma (kind::tf32, M = 128) occupies the tensor pipe for 128 clocks at N = 256, 64 at N = 128 and never
+ * less than ~45 (N <= 64), and the single issuing thread has to get through its barrier probe, descriptors and
+ * commit once per group of four instructions whatever N is: the fewer and wider the instructions, the closer the
+ * kernel runs to the pipe's rate (before the issuer's barrier probe was inlined, issue cost alone made every
+ * instruction take ~166 clocks for N = 64, 128 and 256 alike).  With pixels on M and output channels on N a 64-channel
+ * layer issues four times the instructions of a 256-wide one for the same work.  This variant computes the
  * transposed product instead: M = output channels (the filter tile, rows past Cout are TMA zero fill),
  * N = 256 pixels -- a 14 x 16 pixel block read from its haloed (14+2) x (16+2) input block exactly
  * as in the halo kernel above, now through the B descriptor.  The accumulator is [channel][pixel]:

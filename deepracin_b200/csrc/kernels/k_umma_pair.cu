@@ -1,7 +1,7 @@
 /*
  * Tensor-core 3x3 stride-1 convolution for layers with at most 64 output channels (VGG conv1_2,
- * SqueezeNet's 64-channel expand layers) in TF32 mode.  A tcgen05.mma costs the same ~93 ns for any M <= 128
- * and N <= 256, so the transposed product of k_umma_conv_swap (M = channels, N = 256 pixels) wastes half
+ * SqueezeNet's 64-channel expand layers) in TF32 mode.  A tcgen05.mma with N = 256 occupies the tensor pipe for
+ * 128 clocks whether M is 64 or 128 (microbenchmark), so the transposed product of k_umma_conv_swap (M = channels, N = 256 pixels) wastes half
  * of every instruction when Cout <= 64.  Here the two halves of M hold the same channels for two
  * vertically adjacent output rows:
  *     rows  0..63  : out[o][2j  ][x]      rows 64..127 : out[o][2j+1][x]
