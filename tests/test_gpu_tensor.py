@@ -42,6 +42,9 @@ TENSOR_SHAPES = [
     ("t_first_c1", 3, 1, 32, 17, 13, 3),             # pixel count not a multiple of the 256-pixel tile
     ("t_first_c4", 2, 4, 128, 20, 24, 3),            # K = 36: two swizzle slabs
     ("t_first_c2_48", 1, 2, 48, 15, 15, 3),
+    ("t_first_c4_cout64", 1, 4, 64, 10, 12, 3),      # two K slabs and only two of the four TMEM lane quarters in use
+    ("t_first_c3_cout128", 1, 3, 128, 9, 9, 3),
+    ("t_pair_w15", 2, 24, 40, 34, 15, 3),            # image one pixel wider than a 14-pixel block: a second, nearly empty block column
 ]
 
 
@@ -99,7 +102,7 @@ def test_tf32_network_agrees_with_fp32_on_top1():
     assert rel_err(outs["tf32"], outs["fp32"]) <= 2e-2     # probabilities after 16 TF32 layers
 
 
-@pytest.mark.parametrize("n,cin,cout,h,w", [(1, 64, 64, 56, 56), (2, 128, 256, 28, 28), (3, 256, 512, 14, 14), (2, 32, 64, 12, 20), (1, 64, 64, 224, 224), (2, 32, 48, 28, 30), (3, 64, 32, 64, 28)])
+@pytest.mark.parametrize("n,cin,cout,h,w", [(1, 64, 64, 56, 56), (2, 128, 256, 28, 28), (3, 256, 512, 14, 14), (2, 32, 64, 12, 20), (1, 64, 64, 224, 224), (2, 32, 48, 28, 30), (3, 64, 32, 64, 28), (2, 16, 16, 32, 28), (1, 128, 128, 16, 46)])
 def test_conv_with_fused_maxpool_matches_oracle(n, cin, cout, h, w):
     """conv3x3 + ReLU followed by 2x2/2 max pooling: the tensor kernel's epilogue stores the pooled tensor."""
     x, wt, b = cases.conv_case("fusedpool_%d_%d" % (cin, h), n, cin, cout, h, w, 3, True)
