@@ -16,6 +16,9 @@ typedef struct {
     cl_mem wbuf[5];                 /* packed weights per dR_ConvAlgo */
     dRk_TensorConvPlan *plan;       /* tensor path: TMA descriptors for this layer's buffers */
     gint fusedPool;                 /* 1 / 2: the following 2x2/2 max / average pooling is evaluated in this node's epilogue */
+    dR_Node *mapSrc;                /* few-channel first layer: the Slice/scalar-op/Concat preamble in front of it is evaluated by its gather; */
+    gint mapCh[4];                  /* the convolution then reads this node's tensor through an affine channel map */
+    gfloat mapScale[4], mapShift[4];
     const float *planSrc;           /* buffers the plan's tensor maps were encoded for */
     float *planDst;
 } dR_ConvDevice;
@@ -221,6 +224,23 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
             }
         }
     }
+    /* Slice -> scalar op -> Concat preamble in front of a few-channel tensor layer: read the source through a channel map */
+    dev(c)->mapSrc = NULL;
+    {
+        dR_Node *in = dR_firstInput(layer);
+        dR_Node *src = NULL;
+        if (c->chosenTensor && net->config->fuseGraph && !getenv("DRK_NO_INPUT_MAP") && is3x3s1(c) && c->shape.s2 <= 4 && in->type == tConcat && !in->output &&
+            in->next_layers->length == 1 && dR_concat_gatherAsInputMap(in, &src, dev(c)->mapCh, dev(c)->mapScale, dev(c)->mapShift) &&
+            src->type == tDataFeedNode /* feed buffers are never recycled by the buffer planner, so the source outlives the skipped nodes */) {
+            guint seen = 0;                             /* the kernel wants a permutation of the source's first Cin channels */
+            for (gint j = 0; j < c->shape.s2; j++)
+                if (dev(c)->mapCh[j] < c->shape.s2) seen |= 1u << dev(c)->mapCh[j];
+            if (seen == (1u << c->shape.s2) - 1u) {
+                dev(c)->mapSrc = src;
+                in->fusedAway = TRUE;
+            }
+        }
+    }
     /* scratch for every variant the autotuner may try */
     layer->scratchFloats = 0;
     if (c->chosenAlgo == DR_CONV_WINOGRAD || (net->config->autotune && is3x3s1(c)))
@@ -290,6 +310,7 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
     dR_ConvDevice *d = dev(c);
     dR_Node *in = dR_firstInput(layer);
     const float *src = dR_actPtr(in) + in->act_coffset;
+    if (algo == DR_CONV_TENSOR && d->mapSrc) src = dR_actPtr(d->mapSrc) + d->mapSrc->act_coffset;
     float *dst = dR_actPtr(layer);
     const float *bias = c->useBias ? (const float *)c->biasBuf : NULL;
     const gint n = net->config->batchSize, W = c->ishape.s0, H = c->ishape.s1;
@@ -315,6 +336,10 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
             d->plan = dRk_tensor_conv_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR], bias, dst, n, W, H, c->shape.s2, c->shape.s3,
                                            c->shape.s0, c->shape.s1, act, layer->act_cstride, layer->act_coffset, d->fusedPool, (int *)net->statusWord);
             if (!d->plan) { g_print("Conv2d Layer %d: tensor-core plan could not be built\n", layer->layerID); return FALSE; }
+            if (d->mapSrc && dRk_tensor_conv_set_input_map(d->plan, d->mapSrc->act_cstride, d->mapCh, d->mapScale, d->mapShift) != 0) {
+                g_print("Conv2d Layer %d: input channel map rejected\n", layer->layerID);
+                return FALSE;
+            }
         }
         net->clConfig->clError = dRk_tensor_conv_run(s, d->plan);
         break;
@@ -346,7 +371,7 @@ gboolean dR_conv2d_autotune(dR_Graph *net)
         if (layer->type != tConv2d) continue;
         dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
         if (c->algo != DR_CONV_AUTO || net->config->convAlgo != DR_CONV_AUTO) continue;
-        if (dev(c)->fusedPool) continue;            /* only the tensor kernel can store the pooled tensor */
+        if (dev(c)->fusedPool || dev(c)->mapSrc) continue;     /* only the tensor kernel can store the pooled tensor / read through the channel map */
         gint best = c->chosenAlgo;
         gdouble bestMs = 1e30;
         for (gint algo = DR_CONV_DIRECT; algo <= DR_CONV_TENSOR; algo++) {

@@ -227,6 +227,36 @@ gboolean dR_concat_planGather(dR_Node *layer)
     return TRUE;
 }
 
+/* The gather of a fused Concat as an affine per-channel map of ONE source tensor, if it is that simple: at most four
+ * channels, every chain from the same source, at most one scalar op per chain and that op exact as one FMA
+ * (AddS, SubS, MulS).  A few-channel first convolution can then evaluate it while it reads its input. */
+gboolean dR_concat_gatherAsInputMap(dR_Node *layer, dR_Node **srcOut, gint ch[4], gfloat scale[4], gfloat shift[4])
+{
+    dR_Concat_Data *d = (dR_Concat_Data *)layer->layer;
+    dR_Node *src0 = NULL;
+    gint j = 0;
+    if (layer->type != tConcat || !d->fusedGather || layer->oshape.s2 > 4) return FALSE;
+    for (gint i = 0; i < d->n; i++) {
+        gint ops[4], nops; gfloat sc[4];
+        dR_Node *sl = gatherChain(dR_nthInput(layer, i), ops, sc, &nops);
+        if (!sl || nops > 1) return FALSE;
+        if (nops == 1 && ops[0] != tAddS && ops[0] != tSubS && ops[0] != tMulS) return FALSE;
+        dR_Node *src = dR_firstInput(sl);
+        if (src0 && src != src0) return FALSE;
+        src0 = src;
+        dR_Slice_Data *sd = (dR_Slice_Data *)sl->layer;
+        for (gint c = 0; c < sd->oshape.s2; c++, j++) {
+            if (j >= 4) return FALSE;
+            ch[j] = sd->origin.s2 + c;
+            scale[j] = (nops == 1 && ops[0] == tMulS) ? sc[0] : 1.0f;
+            shift[j] = nops == 0 ? 0.0f : ops[0] == tAddS ? sc[0] : ops[0] == tSubS ? -sc[0] : 0.0f;
+        }
+    }
+    if (!src0 || j != layer->oshape.s2) return FALSE;
+    *srcOut = src0;
+    return TRUE;
+}
+
 static gboolean concatGather(dR_Graph *net, dR_Node *layer)
 {
     dR_Concat_Data *d = (dR_Concat_Data *)layer->layer;

@@ -770,6 +770,9 @@ struct dRk_TensorConvPlan {
     CUtensorMap mapA2;
     const float *in, *wT;
     int sms;
+    int ldi;            /* first-layer kernel: pixel stride of `in` and the optional affine channel map of its gather */
+    int mapped, map_ch[4];
+    float map_scale[4], map_shift[4];
 };
 
 double drk_umma_pair_fill(int W, int H);
@@ -779,7 +782,8 @@ int drk_umma_pair_launch(cudaStream_t st, const CUtensorMap *mapO, const CUtenso
 int drk_umma_first_supported(int Cin, int Cout, int kw, int kh);
 int drk_umma_first_can_pool(int W, int H, int Cin, int Cout);
 int drk_umma_first_launch(cudaStream_t st, const float *in, const float *wT, const float *bias, float *out, int n, int W, int H, int Cin,
-                          int Cout, int act, int ldi, int ldo, int coff, int pool, int *status, int sms);
+                          int Cout, int act, int ldi, int ldo, int coff, int pool, int *status, int sms, const int *map_ch, const float *map_scale,
+                          const float *map_shift);
 
 /*
  * Sub-box geometry of a CTA's pixel tile for a W x H image: S boxes of TW x TH pixels, TW*TH a multiple
@@ -973,6 +977,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     const int variant = pick_variant(W, H, Cin, Cout, kw, kh);
     if (variant == VAR_FIRST) {
         pl->first = 1;
+        pl->ldi = Cin;
         p.n = n; p.W = W; p.H = H; p.Cin = Cin; p.Cout = Cout; p.bias = bias; p.out = out; p.ldo = ldo; p.coff = coff; p.act = act; p.status = status;
         p.pool = fuse_pool2;
         return pl;
@@ -1064,13 +1069,28 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     return pl;
 }
 
+extern "C" int dRk_tensor_conv_set_input_map(dRk_TensorConvPlan *pl, int ldi, const int *ch, const float *scale, const float *shift)
+{
+    if (!pl || !pl->first || !ch || !scale || !shift || ldi < pl->p.Cin) return -1;
+    unsigned seen = 0;
+    for (int c = 0; c < pl->p.Cin; c++) {
+        if (ch[c] < 0 || ch[c] >= pl->p.Cin || (seen >> ch[c]) & 1u) return -1;      /* a permutation of the first Cin source channels */
+        seen |= 1u << ch[c];
+        pl->map_ch[c] = ch[c]; pl->map_scale[c] = scale[c]; pl->map_shift[c] = shift[c];
+    }
+    pl->ldi = ldi;
+    pl->mapped = 1;
+    return 0;
+}
+
 extern "C" int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *pl)
 {
     if (!pl) return -1;
     cudaStream_t st = drk_stream(stream);
     if (pl->first)
         return drk_umma_first_launch(st, pl->in, pl->wT, pl->p.bias, pl->p.out, pl->p.n, pl->p.W, pl->p.H, pl->p.Cin, pl->p.Cout, pl->p.act,
-                                     pl->p.Cin, pl->p.ldo, pl->p.coff, pl->p.pool, pl->p.status, pl->sms);
+                                     pl->ldi, pl->p.ldo, pl->p.coff, pl->p.pool, pl->p.status, pl->sms, pl->mapped ? pl->map_ch : NULL,
+                                     pl->map_scale, pl->map_shift);
     if (pl->pair) return drk_umma_pair_launch(st, &pl->mapA, &pl->mapA2, &pl->mapB, &pl->p, pl->grid);
     if (pl->swap) {
         static bool attr_done[DRK_MAX_DEVICES];

@@ -20,6 +20,7 @@
  * writes a code to `status`, and all roles leave (no asynchronous copies are ever in flight here).
  */
 #include <stdio.h>
+#include <string.h>
 #include "k_common.cuh"
 #include "k_umma.cuh"
 
@@ -43,6 +44,18 @@ struct FirstCfg {
     static constexpr int B_STAGE = SLABS * FIRST_N * BK * 4;
     static constexpr int NB = B_STAGE <= 32 * 1024 ? 3 : 2;
     static constexpr int SMEM_BYTES = A_BYTES + NB * B_STAGE + 1024 + 256;
+};
+
+/* Optional affine channel map applied while gathering: input channel j of the convolution is channel ch[j] of the source
+ * pixel times scale[j] plus shift[j] (zero padding stays zero), ch a permutation of 0..Cin-1.  Evaluates a Slice -> scalar
+ * op -> Concat preamble (mean subtraction, channel reordering) inside the first layer instead of in a kernel of its own.
+ * The gather keeps the source's channel order (compile-time load offsets: run-time offsets made it 1.5x slower) and the
+ * permutation goes into the filter tile's K columns, built once per CTA: inv[c] = the convolution channel that reads
+ * source channel c; scale and shift are stored per source channel. */
+struct FirstInMap {
+    int use;
+    int inv[4];
+    float scale[4], shift[4];
 };
 
 __device__ __forceinline__ uint32_t to_tf32(float v)
@@ -84,10 +97,10 @@ __device__ __forceinline__ float *store32(float *optr, const uint32_t (&r)[32], 
     return optr + 32 * ldo;
 }
 
-template <int CIN, int G>
+template <int CIN, int G, bool MAPPED>
 __global__ void __launch_bounds__(FIRST_THREADS, 1)
 k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, const float *__restrict__ bias, float *__restrict__ out,
-                  int n, int W, int H, int Cout, int act, int ldi, int ldo, int coff, int pool, int *status)
+                  int n, int W, int H, int Cout, int act, int ldi, int ldo, int coff, int pool, int *status, const FirstInMap map)
 {
     using C = FirstCfg<CIN, G>;
     constexpr int TILE_PX = G * FIRST_N;
@@ -137,7 +150,9 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
 #pragma unroll
         for (int e = 0; e < 4; e++) {
             const int k = ks * BK + chunk * 4 + e;
-            v[e] = (ch >= 0 && ch < Cout && k < C::K) ? to_tf32(__ldg(wT + (size_t)ch * C::K + k)) : 0u;
+            int kw = k;                                             /* column of the packed filters this K position multiplies */
+            if (MAPPED && k < C::K) { const int tap = k / CIN; kw = tap * CIN + map.inv[k - tap * CIN]; }
+            v[e] = (ch >= 0 && ch < Cout && k < C::K) ? to_tf32(__ldg(wT + (size_t)ch * C::K + kw)) : 0u;
         }
         *reinterpret_cast<uint4 *>(gen + slab * (BM * BK * 4) + swz(row, chunk)) = make_uint4(v[0], v[1], v[2], v[3]);
     }
@@ -296,7 +311,11 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
                             const bool pok = yok && ix >= 0 && ix < W;
                             const float *p = pix + ((ky - 1) * W + (kx - 1)) * ldi;
 #pragma unroll
-                            for (int c = 0; c < CIN; c++) v[grp][(ky * 3 + kx) * CIN + c] = pok ? __float_as_uint(__ldg(p + c)) : 0u;
+                            for (int c = 0; c < CIN; c++) {
+                                float t = pok ? __ldg(p + c) : 0.0f;
+                                if (MAPPED) t = pok ? fmaf(t, map.scale[c], map.shift[c]) : 0.0f;
+                                v[grp][(ky * 3 + kx) * CIN + c] = __float_as_uint(t);
+                            }
                         }
                     }
                 }
@@ -322,16 +341,16 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
     if (warp == 0) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-template <int CIN, int G>
-static int launch_first(cudaStream_t st, const float *in, const float *wT, const float *bias, float *out, int n, int W, int H, int Cout,
-                        int act, int ldi, int ldo, int coff, int pool, int *status, int sms)
+template <int CIN, int G, bool MAPPED>
+static int launch_first_m(cudaStream_t st, const float *in, const float *wT, const float *bias, float *out, int n, int W, int H, int Cout,
+                        int act, int ldi, int ldo, int coff, int pool, int *status, int sms, const FirstInMap &map)
 {
     static bool attr_done[64];                      /* the opt-in shared-memory size is a per-device function attribute */
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_umma_conv_first<CIN, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, FirstCfg<CIN, G>::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(k_umma_conv_first<CIN, G, MAPPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, FirstCfg<CIN, G>::SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         attr_done[dev] = true;
     }
@@ -339,9 +358,17 @@ static int launch_first(cudaStream_t st, const float *in, const float *wT, const
     const long long tiles = pool ? ((long long)n * (H / 2) * W + FIRST_N - 1) / FIRST_N : ((long long)n * H * W + G * FIRST_N - 1) / (G * FIRST_N);
     if (tiles <= 0 || tiles > 0x7fffffffll) return -1;
     const int grid = (int)(tiles < sms ? tiles : sms);
-    drk_launch_dep(k_umma_conv_first<CIN, G>, dim3(grid), dim3(FIRST_THREADS), FirstCfg<CIN, G>::SMEM_BYTES, st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status);
+    drk_launch_dep(k_umma_conv_first<CIN, G, MAPPED>, dim3(grid), dim3(FIRST_THREADS), FirstCfg<CIN, G>::SMEM_BYTES, st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, map);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
+}
+
+template <int CIN, int G>
+static int launch_first(cudaStream_t st, const float *in, const float *wT, const float *bias, float *out, int n, int W, int H, int Cout,
+                        int act, int ldi, int ldo, int coff, int pool, int *status, int sms, const FirstInMap &map)
+{
+    return map.use ? launch_first_m<CIN, G, true>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms, map)
+                   : launch_first_m<CIN, G, false>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms, map);
 }
 
 /* 1 if this kernel takes the layer shape */
@@ -359,18 +386,29 @@ int drk_umma_first_can_pool(int W, int H, int Cin, int Cout)
 /* wT: [Cout][9*Cin] with k = (ky*3 + kx)*Cin + c; in: N-HWC with pixel stride ldi; pool: 0 none, 1 max 2x2/2, 2 average 2x2/2
  * (`out` is then the (W/2) x (H/2) pooled tensor) */
 int drk_umma_first_launch(cudaStream_t st, const float *in, const float *wT, const float *bias, float *out, int n, int W, int H, int Cin,
-                          int Cout, int act, int ldi, int ldo, int coff, int pool, int *status, int sms)
+                          int Cout, int act, int ldi, int ldo, int coff, int pool, int *status, int sms, const int *map_ch, const float *map_scale,
+                          const float *map_shift)
 {
+    FirstInMap map;
+    memset(&map, 0, sizeof map);
+    if (map_ch) {
+        map.use = 1;
+        for (int j = 0; j < Cin && j < 4; j++) {
+            const int c = map_ch[j];
+            if (c < 0 || c >= Cin) return -1;
+            map.inv[c] = j; map.scale[c] = map_scale[j]; map.shift[c] = map_shift[j];
+        }
+    }
     if (pool && !drk_umma_first_can_pool(W, H, Cin, Cout)) return -1;
     const bool two = Cout <= 64;                     /* two pixel groups on the M axis */
     switch (Cin) {
-    case 1: return two ? launch_first<1, 2>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms)
-                       : launch_first<1, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms);
-    case 2: return two ? launch_first<2, 2>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms)
-                       : launch_first<2, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms);
-    case 3: return two ? launch_first<3, 2>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms)
-                       : launch_first<3, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms);
-    case 4: return launch_first<4, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms);
+    case 1: return two ? launch_first<1, 2>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms, map)
+                       : launch_first<1, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms, map);
+    case 2: return two ? launch_first<2, 2>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms, map)
+                       : launch_first<2, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms, map);
+    case 3: return two ? launch_first<3, 2>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms, map)
+                       : launch_first<3, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms, map);
+    case 4: return launch_first<4, 1>(st, in, wT, bias, out, n, W, H, Cout, act, ldi, ldo, coff, pool, status, sms, map);
     }
     return -1;
 }

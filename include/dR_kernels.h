@@ -138,6 +138,11 @@ int dRk_tensor_conv_pack_weights(const float *w, float *dst, int W, int H, int C
 dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float *wT, const float *bias, float *out,
                                          int n, int W, int H, int Cin, int Cout, int kw, int kh, int act,
                                          int ldo, int coff, int fuse_pool2, int *status);
+/* Few-channel first layers only (Cin <= 4): the convolution then reads channel ch[c] of a source with pixel stride ldi,
+ * times scale[c] plus shift[c], as its input channel c (ch a permutation of 0..Cin-1); `in` of the plan is that source.  Replaces a Slice -> scalar op ->
+ * Concat preamble (examples/squeezenet-v1.1/squeezenet_whole/graph.dr:7-41) in front of the layer.  -1 if the plan is for
+ * another kernel. */
+int dRk_tensor_conv_set_input_map(dRk_TensorConvPlan *plan, int ldi, const int *ch, const float *scale, const float *shift);
 int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *plan);
 void dRk_tensor_conv_free(dRk_TensorConvPlan *plan);
 

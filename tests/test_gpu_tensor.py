@@ -156,6 +156,52 @@ def test_first_layer_with_fused_pool_matches_oracle(kind, n, cin, cout, h, w, ac
     assert rel_err(res[True], res[False]) <= 1e-6       # same accumulators; the average sums in a different order
 
 
+@pytest.mark.parametrize("ops", [("sub", "sub", "sub"), ("add", "mul", None)])
+def test_first_layer_reads_through_preamble_channel_map(ops):
+    """Slice -> scalar op -> Concat in front of a few-channel first layer (mean subtraction + BGR reordering of the reference's
+    example graphs): in TF32 mode the convolution's gather evaluates it and the preamble launches nothing."""
+    n, h, w, cout = 2, 22, 26, 32
+    x, wt, b = cases.conv_case("premap_%s" % ops[1], n, 3, cout, h, w, 3, True)
+    x = x * np.float32(40.0)
+    scal = (np.float32(103.9), np.float32(1.7), np.float32(123.6))
+    order = (2, 0, 1)
+    planes = []
+    for j, c in enumerate(order):
+        v = x[:, c:c + 1]
+        if ops[j] == "sub": v = v - scal[j]
+        elif ops[j] == "add": v = v + scal[j]
+        elif ops[j] == "mul": v = v * scal[j]
+        planes.append(v.astype(np.float32))
+    ref = oracle.conv2d(np.concatenate(planes, axis=1), wt, b, (1, 1), 1)
+    res, launches = {}, {}
+    for fuse in (True, False):
+        with dr.Environment() as env:
+            g = env.create_graph("CHW")
+            g.batch = n
+            g.math = "tf32"
+            g.fuse = fuse
+            f = dr.feed_node(g, [3, h, w])
+            parts = []
+            for j, c in enumerate(order):
+                nd = dr.Slice(f, (c, 0, 0), (1, h, w))
+                if ops[j] == "sub": nd = dr.Sub_Scalar(nd, float(scal[j]))
+                elif ops[j] == "add": nd = dr.Add_Scalar(nd, float(scal[j]))
+                elif ops[j] == "mul": nd = dr.Mul_Scalar(nd, float(scal[j]))
+                parts.append(nd)
+            cat = dr.Concat(parts, 0)
+            o = conv_build(wt, b, 1, 1)(g, [cat])
+            dr.mark_as_output(o)
+            dr.prepare(g)
+            dr.feed_data(f, x)
+            res[fuse] = dr.apply(g)[0].reshape(ref.shape)
+            launches[fuse] = dr.lib.dR_getLaunchCount(g.ptr)
+            assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    assert launches[True] == 3                          # feed layout, convolution, output layout
+    assert rel_err(res[True], ref) <= TOL_TF32
+    assert rel_err(res[False], ref) <= TOL_TF32
+    assert rel_err(res[True], res[False]) <= 1e-6
+
+
 @pytest.mark.parametrize("n,c,h,w,nout,act", [(64, 64, 4, 4, 256, 1), (16, 512, 7, 7, 512, 0), (33, 32, 2, 8, 768, 1), (64, 256, 2, 2, 1000, 0), (20, 64, 2, 2, 72, 1)])
 def test_tensor_fc_matches_oracle(n, c, h, w, nout, act):
     """TF32 mode, batch >= 16: fully connected layers run as a split-K GEMM on the tensor cores."""
