@@ -297,18 +297,19 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
 #define HALO_ROWS ((HALO_TH + 2) * HALO_P)             /* 160 rows loaded per slab */
 #define HALO_A_BYTES (HALO_ROWS * BK * 4)              /* 20480 */
 #define HALO_A_SLOT (21 * 1024)                        /* 168 rows: taps of the two idle tail rows read up to row 161 */
-#define HALO_NA 3
 
 template <int BN>
 struct HaloCfg {
     static constexpr int B_STAGE_BYTES = BN * BK * 4;
-    /* transposing store stage as in Cfg<BN>, where shared memory allows it without giving up a filter stage (BN <= 128) */
+    /* transposing store stage as in Cfg<BN>; with BN = 256 the shared memory for it comes from the third activation slot
+       (two suffice: a slot is consumed over nine taps = ~4600 clocks, far longer than a 20 KB load takes) */
+    static constexpr int NA = BN <= 128 ? 3 : 2;
     static constexpr int STG_PITCH = 36;
-    static constexpr int STG_BYTES = BN <= 128 ? 4 * 32 * STG_PITCH * 4 : 0;
-    static constexpr int NB_RAW = (SMEM_BUDGET - 2048 - HALO_NA * HALO_A_SLOT - STG_BYTES) / B_STAGE_BYTES;
+    static constexpr int STG_BYTES = 4 * 32 * STG_PITCH * 4;
+    static constexpr int NB_RAW = (SMEM_BUDGET - 2048 - NA * HALO_A_SLOT - STG_BYTES) / B_STAGE_BYTES;
     static constexpr int NB = NB_RAW > 10 ? 10 : NB_RAW;
     static constexpr int TMEM_COLS = 2 * BN < 32 ? 32 : 2 * BN;
-    static constexpr int SMEM_BYTES = HALO_NA * HALO_A_SLOT + NB * B_STAGE_BYTES + 1024 + 512 + STG_BYTES;
+    static constexpr int SMEM_BYTES = NA * HALO_A_SLOT + NB * B_STAGE_BYTES + 1024 + 512 + STG_BYTES;
 };
 
 template <int BN>
@@ -321,24 +322,24 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - raw);
-    const uint32_t a_base = base, b_base = base + HALO_NA * HALO_A_SLOT;
+    const uint32_t a_base = base, b_base = base + C::NA * HALO_A_SLOT;
     const uint32_t bars = b_base + C::NB * C::B_STAGE_BYTES;
-    constexpr int NBARS = 2 * HALO_NA + 2 * C::NB + 4;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + HALO_NA * HALO_A_SLOT + C::NB * C::B_STAGE_BYTES + 8 * NBARS);
+    constexpr int NBARS = 2 * C::NA + 2 * C::NB + 4;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + C::NA * HALO_A_SLOT + C::NB * C::B_STAGE_BYTES + 8 * NBARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     auto afull = [&](int s) { return bars + 8u * s; };
-    auto aempty = [&](int s) { return bars + 8u * (HALO_NA + s); };
-    auto bfull = [&](int s) { return bars + 8u * (2 * HALO_NA + s); };
-    auto bempty = [&](int s) { return bars + 8u * (2 * HALO_NA + C::NB + s); };
-    auto tfull_bar = [&](int a) { return bars + 8u * (2 * HALO_NA + 2 * C::NB + a); };
-    auto tempty_bar = [&](int a) { return bars + 8u * (2 * HALO_NA + 2 * C::NB + 2 + a); };
+    auto aempty = [&](int s) { return bars + 8u * (C::NA + s); };
+    auto bfull = [&](int s) { return bars + 8u * (2 * C::NA + s); };
+    auto bempty = [&](int s) { return bars + 8u * (2 * C::NA + C::NB + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * C::NA + 2 * C::NB + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * C::NA + 2 * C::NB + 2 + a); };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles * p.n_tiles;
     const int per = p.tiles_x * p.tiles_y;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < HALO_NA; s++) { mbar_init(afull(s), 1); mbar_init(aempty(s), 1); }
+        for (int s = 0; s < C::NA; s++) { mbar_init(afull(s), 1); mbar_init(aempty(s), 1); }
         for (int s = 0; s < C::NB; s++) { mbar_init(bfull(s), 1); mbar_init(bempty(s), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
         *abort_flag = 0;
@@ -368,7 +369,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                     mbar_expect_tx(afull(as), HALO_A_BYTES);
                     tma_load_4d(a_base + as * HALO_A_SLOT, &mapA, ks * BK, txi * HALO_TW - 1, tyi * HALO_TH - 1, img, afull(as));
                     a_issued++;
-                    if (++as == HALO_NA) { as = 0; aph ^= 1u; }
+                    if (++as == C::NA) { as = 0; aph ^= 1u; }
                     for (int tap = 0; tap < 9; tap++) {
                         if (!mbar_wait(bempty(bs), bph ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
                         mbar_expect_tx(bfull(bs), C::B_STAGE_BYTES);
@@ -379,10 +380,10 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                 }
             }
             if (!ok) {      /* drain what is still in flight (bounded) before the CTA's shared memory is released */
-                long long pend = a_issued < HALO_NA ? a_issued : HALO_NA;
+                long long pend = a_issued < C::NA ? a_issued : C::NA;
                 int s = as; uint32_t ph = aph;
                 for (long long i = 0; i < pend; i++) {
-                    if (--s < 0) { s = HALO_NA - 1; ph ^= 1u; }
+                    if (--s < 0) { s = C::NA - 1; ph ^= 1u; }
                     const long long t0 = clock64();
                     while (!mbar_try(afull(s), ph) && clock64() - t0 < WAIT_CYCLES) { }
                 }
@@ -424,7 +425,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                         if (++bs == C::NB) { bs = 0; bph ^= 1u; }
                     }
                     if (ok) umma_commit(aempty(as));
-                    if (++as == HALO_NA) { as = 0; aph ^= 1u; }
+                    if (++as == C::NA) { as = 0; aph ^= 1u; }
                 }
                 if (ok) umma_commit(tfull_bar(acc));
             }
@@ -466,7 +467,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                     rowok |= ((vm >> src) & 1u) << i;
                 }
             }
-            float *stg = reinterpret_cast<float *>(gen + HALO_NA * HALO_A_SLOT + C::NB * C::B_STAGE_BYTES + 512) + (warp - 2) * 32 * C::STG_PITCH;
+            float *stg = reinterpret_cast<float *>(gen + C::NA * HALO_A_SLOT + C::NB * C::B_STAGE_BYTES + 512) + (warp - 2) * 32 * C::STG_PITCH;
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
