@@ -552,9 +552,11 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 #define SWAP_NH 2
 #define SWAP_W_BYTES (BM * BK * 4)                     /* filter stage: 128 rows x 128 B */
 #define SWAP_NW 9
+#define SWAP_EPI_WARPS 8
+#define SWAP_THREADS ((2 + SWAP_EPI_WARPS) * 32)
 #define SWAP_SMEM (SWAP_NH * SWAP_HALO_SLOT + SWAP_NW * SWAP_W_BYTES + 1024 + 512)
 
-__global__ void __launch_bounds__(UMMA_THREADS, 1)
+__global__ void __launch_bounds__(SWAP_THREADS, 1)
 k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW, const UmmaParams p)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -582,7 +584,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     if (threadIdx.x == 0) {
         for (int s = 0; s < SWAP_NH; s++) { mbar_init(hfull(s), 1); mbar_init(hempty(s), 1); }
         for (int s = 0; s < SWAP_NW; s++) { mbar_init(wfull(s), 1); mbar_init(wempty(s), 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), SWAP_EPI_WARPS); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -672,7 +674,9 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             }
         }
     } else {
-        const int quarter = warp & 3;
+        /* eight epilogue warps: two per 32-lane quarter of TMEM, each taking half of the 256 pixel columns (with four, the
+           224 scalar stores per lane and tile of a layer without pooling outlasted the 72 MMAs of a 64-channel-deep tile) */
+        const int quarter = warp & 3, half = (warp - 2) >> 2;
         int it = 0;
         bool ok = true;
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
@@ -691,7 +695,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * SWAP_N);
 #pragma unroll 1
-            for (int c0 = 0; c0 < SWAP_N; c0 += 32) {
+            for (int c0 = half * (SWAP_N / 2); c0 < (half + 1) * (SWAP_N / 2); c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(taddr + (uint32_t)c0, r);
                 if (!chok) continue;
@@ -1101,7 +1105,7 @@ extern "C" int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *pl)
             if (e != cudaSuccess) return (int)e;
             attr_done[dev] = true;
         }
-        drk_launch_dep(k_umma_conv_swap, dim3(pl->grid), dim3(UMMA_THREADS), SWAP_SMEM, st, pl->mapA, pl->mapB, pl->p);
+        drk_launch_dep(k_umma_conv_swap, dim3(pl->grid), dim3(SWAP_THREADS), SWAP_SMEM, st, pl->mapA, pl->mapB, pl->p);
         DRK_COUNT_LAUNCH();
         return DRK_LAUNCH_RESULT();
     }
