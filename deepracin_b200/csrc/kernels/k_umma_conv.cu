@@ -925,6 +925,7 @@ static int pick_bn(int Cout, long long m_tiles, int sms)
     int best = 64;
     double best_cost = 1e30;
     const int cand[3] = {256, 128, 64};
+    if (getenv("DRK_FORCE_BN")) return atoi(getenv("DRK_FORCE_BN"));    /* A/B comparisons when profiling */
     for (int i = 0; i < 3; i++) {
         const int bn = cand[i];
         const long long tiles = m_tiles * ((Cout + bn - 1) / bn);
