@@ -212,3 +212,46 @@ def test_tensor_fc_matches_oracle(n, c, h, w, nout, act):
     (exact,) = run_graph(lambda g, f: dr.Fully_Connected(f[0], [c * h * w, nout], "relu" if act else "linear", wt, b), [x], math="fp32")
     assert rel_err(exact, ref) <= 1e-4
     assert not np.array_equal(got, exact)       # the two arithmetic classes really are different kernels
+
+
+def _random_shapes(count, seed):
+    r = np.random.Generator(np.random.PCG64(seed))
+    out = []
+    for i in range(count):
+        k = 3 if r.random() < 0.7 else 1
+        cin = int(r.choice([1, 2, 3, 4])) if (k == 3 and r.random() < 0.2) else 4 * int(r.integers(2, 25))
+        cout = 4 * int(r.integers(4, 70))
+        if cin <= 4 and cout > 128:
+            cout = 4 * int(r.integers(4, 33))
+        h, w = int(r.integers(3, 64)), int(r.integers(3, 64))
+        n = int(r.integers(1, 4))
+        pool = bool(k == 3 and r.random() < 0.4)
+        if pool:
+            h += h & 1
+            w += w & 1
+        out.append((i, n, cin, cout, h, w, k, pool))
+    return out
+
+
+@pytest.mark.parametrize("idx,n,cin,cout,h,w,k,pool", _random_shapes(40, 20251))
+def test_random_layer_shapes_match_oracle(idx, n, cin, cout, h, w, k, pool):
+    """Seeded random layer shapes across the boundaries between the tensor kernels (first layer, row pair, transposed, halo,
+    plain, flat 1x1), with and without a following 2x2 max pool, bias + ReLU: every one must match the oracle."""
+    x, wt, b = cases.conv_case("rnd_%d" % idx, n, cin, cout, h, w, k, True)
+    ref = oracle.conv2d(x, wt, b, (1, 1), 1)
+    if pool:
+        ref = oracle.pool(ref, (2, 2, 1), (2, 2, 1), 0)
+    with dr.Environment() as env:
+        g = env.create_graph("CHW")
+        g.batch = n
+        g.math = "tf32"
+        f = dr.feed_node(g, [cin, h, w])
+        o = conv_build(wt, b, 1, 1)(g, [f])
+        if pool:
+            o = dr.Pooling(o, "max", [1, 2, 2, 1], [1, 2, 2, 1])
+        dr.mark_as_output(o)
+        dr.prepare(g)
+        dr.feed_data(f, x)
+        got = dr.apply(g)[0].reshape(ref.shape)
+        assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    assert rel_err(got, ref) <= TOL_TF32
