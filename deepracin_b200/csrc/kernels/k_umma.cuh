@@ -132,6 +132,18 @@ __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr)
     d |= (uint64_t)2 << 61;                         /* SWIZZLE_128B */
     return d;
 }
+/* same with an explicit stride between the 8-row groups: a block whose rows are `pitch` pixels apart can present 8 of
+ * every `pitch` rows to the MMA (sbo = pitch * 128 bytes) -- the swizzle follows the absolute shared-memory address */
+__device__ __forceinline__ uint64_t make_smem_desc_sbo(uint32_t saddr, uint32_t sbo_bytes)
+{
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(sbo_bytes >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
 /* instruction descriptor: D = F32, A = B = TF32, both K-major, M = 128, N = bn */
 __host__ __device__ constexpr uint32_t make_idesc(int bn)
 {

@@ -26,7 +26,7 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void *src, uint32_
 #define SMEM_BYTES ((16 + NST * 32) * 1024 + 2048)
 
 /* V = 0: part 1 (no ring); 1: out-of-line wait; 2: inline first probe; 3: look-ahead probe + deferred commit */
-template <int V, int MM, int BN>
+template <int V, int MM, int BN, int SBO = 1024>
 __global__ void __launch_bounds__(192, 1) k_rate(int groups, const float *src, size_t src_floats, long long *out, int *status)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -78,7 +78,7 @@ __global__ void __launch_bounds__(192, 1) k_rate(int groups, const float *src, s
         bool ok = true;
         const long long t0 = clock64();
         if (V == 0) {
-            const uint64_t bdesc = make_smem_desc(b_base);
+            const uint64_t bdesc = SBO == 1024 ? make_smem_desc(b_base) : make_smem_desc_sbo(b_base, SBO);
             for (int g = 0; g < groups; g++) {
 #pragma unroll
                 for (int j = 0; j < 4; j++) umma_tf32(tmem_base, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, 1u);
@@ -124,14 +124,14 @@ __global__ void __launch_bounds__(192, 1) k_rate(int groups, const float *src, s
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
-template <int V, int MM, int BN>
+template <int V, int MM, int BN, int SBO = 1024>
 static void run(const char *what, const float *src, size_t src_floats, long long *out, int *status)
 {
     const int groups = 4096;
-    cudaFuncSetAttribute(k_rate<V, MM, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaFuncSetAttribute(k_rate<V, MM, BN, SBO>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
     cudaMemset(out, 0, 64);
     cudaMemset(status, 0, 4);
-    for (int rep = 0; rep < 2; rep++) k_rate<V, MM, BN><<<148, 192, SMEM_BYTES, 0>>>(groups, src, src_floats, out, status);
+    for (int rep = 0; rep < 2; rep++) k_rate<V, MM, BN, SBO><<<148, 192, SMEM_BYTES, 0>>>(groups, src, src_floats, out, status);
     const cudaError_t e = cudaDeviceSynchronize();
     long long h = 0;
     int st = 0;
@@ -152,6 +152,9 @@ int main()
     run<0, 128, 128>("back to back", src, src_floats, out, status);
     run<0, 128, 64>("back to back", src, src_floats, out, status);
     run<0, 128, 32>("back to back", src, src_floats, out, status);
+    run<0, 128, 256, 1280>("back to back, B groups of 8 rows 1280 bytes apart", src, src_floats, out, status);
+    run<0, 128, 224, 1280>("back to back, B groups of 8 rows 1280 bytes apart", src, src_floats, out, status);
+    run<0, 128, 224>("back to back", src, src_floats, out, status);
     run<0, 64, 256>("back to back", src, src_floats, out, status);
     run<0, 64, 128>("back to back", src, src_floats, out, status);
     run<1, 128, 256>("ring of 32 KB bulk loads per 4 MMAs, bounded wait as an out-of-line call", src, src_floats, out, status);
