@@ -15,7 +15,8 @@
 #define BK 16
 
 template <int BM, int BN, int TM, int TN, bool CONV>
-__global__ void __launch_bounds__(256) k_gemm_f32(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias,
+/* two CTAs per SM for the 128 x 128 convolution variant (128 registers without spills); the dense variant would spill at that limit */
+__global__ void __launch_bounds__(256, BM == 128 ? (CONV ? 2 : 1) : 3) k_gemm_f32(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias,
                                                   float *__restrict__ C, int M, int N, int K, int lda, int ldb, int ldc, int coff, int act,
                                                   size_t strideA, size_t strideB, size_t strideC, int vecA, int vecB, int vecC, drk_ConvGeom g)
 {
@@ -36,16 +37,18 @@ __global__ void __launch_bounds__(256) k_gemm_f32(const float *__restrict__ A, c
     C += (size_t)blockIdx.z * strideC;
 
     /* per-thread description of the A rows it stages */
-    int a_row[A_UNITS], a_kseg[A_UNITS];
+    /* unit i of a thread is float4 number tid + 256*i of the tile: its row is tid/4 + 64*i and its K segment (tid%4)*4 for
+       every i, so only what is expensive to recompute is kept in registers (two CTAs per SM need <= 128 of them) */
+    const int a_kseg0 = (tid % (BK / 4)) * 4, a_row0 = tid / (BK / 4);
+#define a_kseg(i) a_kseg0
+#define a_row(i) (a_row0 + (i) * (256 / (BK / 4)))
     bool a_ok[A_UNITS];
     size_t a_base[A_UNITS];             /* dense: row offset; conv: image offset */
     int a_iy0[A_UNITS], a_ix0[A_UNITS];
 #pragma unroll
     for (int i = 0; i < A_UNITS; i++) {
         const int u = tid + i * 256;
-        a_row[i] = u / (BK / 4);
-        a_kseg[i] = (u % (BK / 4)) * 4;
-        const int m = m0 + a_row[i];
+        const int m = m0 + a_row(i);
         a_ok[i] = u < A_ACTIVE && m < M;
         a_base[i] = 0; a_iy0[i] = 0; a_ix0[i] = 0;
         if (a_ok[i]) {
@@ -62,13 +65,9 @@ __global__ void __launch_bounds__(256) k_gemm_f32(const float *__restrict__ A, c
             }
         }
     }
-    int b_krow[B_UNITS], b_n[B_UNITS];
-#pragma unroll
-    for (int i = 0; i < B_UNITS; i++) {
-        const int u = tid + i * 256;
-        b_krow[i] = u / (BN / 4);
-        b_n[i] = (u % (BN / 4)) * 4;
-    }
+    const int b_n0 = (tid % (BN / 4)) * 4, b_krow0 = tid / (BN / 4);
+#define b_n(i) b_n0
+#define b_krow(i) (b_krow0 + (i) * (256 / (BN / 4)))
 
     float4 ra[A_UNITS], rb[B_UNITS];
 
@@ -76,7 +75,7 @@ __global__ void __launch_bounds__(256) k_gemm_f32(const float *__restrict__ A, c
 #pragma unroll
         for (int i = 0; i < A_UNITS; i++) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            const int k = k0 + a_kseg[i];
+            const int k = k0 + a_kseg(i);
             if (a_ok[i] && k < K) {
                 if (CONV) {
                     if (vecA) {
@@ -116,7 +115,7 @@ __global__ void __launch_bounds__(256) k_gemm_f32(const float *__restrict__ A, c
 #pragma unroll
         for (int i = 0; i < B_UNITS; i++) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            const int k = k0 + b_krow[i], n = n0 + b_n[i];
+            const int k = k0 + b_krow(i), n = n0 + b_n(i);
             if (tid + i * 256 < B_ACTIVE && k < K && n < N) {
                 const float *p = B + (size_t)k * ldb + n;
                 if (vecB && n + 3 < N) v = *reinterpret_cast<const float4 *>(p);
@@ -134,15 +133,15 @@ __global__ void __launch_bounds__(256) k_gemm_f32(const float *__restrict__ A, c
 #pragma unroll
         for (int i = 0; i < A_UNITS; i++) {
             if (tid + i * 256 < A_ACTIVE) {
-                As[buf][a_kseg[i] + 0][a_row[i]] = ra[i].x;
-                As[buf][a_kseg[i] + 1][a_row[i]] = ra[i].y;
-                As[buf][a_kseg[i] + 2][a_row[i]] = ra[i].z;
-                As[buf][a_kseg[i] + 3][a_row[i]] = ra[i].w;
+                As[buf][a_kseg(i) + 0][a_row(i)] = ra[i].x;
+                As[buf][a_kseg(i) + 1][a_row(i)] = ra[i].y;
+                As[buf][a_kseg(i) + 2][a_row(i)] = ra[i].z;
+                As[buf][a_kseg(i) + 3][a_row(i)] = ra[i].w;
             }
         }
 #pragma unroll
         for (int i = 0; i < B_UNITS; i++)
-            if (tid + i * 256 < B_ACTIVE) *reinterpret_cast<float4 *>(&Bs[buf][b_krow[i]][b_n[i]]) = rb[i];
+            if (tid + i * 256 < B_ACTIVE) *reinterpret_cast<float4 *>(&Bs[buf][b_krow(i)][b_n(i)]) = rb[i];
     };
 
     float acc[TM][TN];
@@ -210,6 +209,11 @@ __global__ void __launch_bounds__(256) k_gemm_f32(const float *__restrict__ A, c
             }
         }
 }
+
+#undef a_kseg
+#undef a_row
+#undef b_n
+#undef b_krow
 
 static bool aligned16(const void *p) { return ((uintptr_t)p % 16) == 0; }
 
