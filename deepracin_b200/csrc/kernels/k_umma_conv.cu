@@ -77,7 +77,6 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    drk_dep_wait();                 /* set-up above overlaps the previous kernel; its outputs are visible from here on */
 
     if (warp == 0) {
         /* ------------------------------------------------ TMA producer (one lane) */
@@ -88,6 +87,23 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
             uint32_t phase = 0;
             long long issued = 0;
             bool ok = true;
+            /* The filters are constants: the first stages' filter tiles are requested before this grid waits for the one
+               before it (programmatic dependent launch), so that only the activation loads remain on the critical path.
+               Only this thread reads memory the previous kernel writes, and every store of this kernel follows, through the
+               barrier chain, from a load issued after the wait. */
+            int pre = 0;
+            if ((int)blockIdx.x < total_tiles) {
+                const int t = blockIdx.x;
+                const int ksi = t % p.ksplit, tt = t / p.ksplit;
+                const int nt = tt % p.n_tiles;
+                const int ks0 = ksi * p.kper, ks1 = min(p.kslabs, ks0 + p.kper);
+                for (int tap = 0; tap < p.taps && pre < C::STAGES; tap++)
+                    for (int ks = ks0; ks < ks1 && pre < C::STAGES; ks++, pre++) {
+                        mbar_expect_tx(full_bar(pre), (uint32_t)p.stage_tx);
+                        tma_load_2d(base + pre * C::STAGE_BYTES + A_STAGE_BYTES, &mapB, tap * p.CinPad + ks * BK, nt * BN, full_bar(pre));
+                    }
+            }
+            drk_dep_wait();
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const int ksi = t % p.ksplit, tt = t / p.ksplit;
                 const int mt = tt / p.n_tiles, nt = tt - mt * p.n_tiles;
@@ -95,9 +111,10 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                 for (int tap = 0; tap < p.taps && ok; tap++) {
                     const int ky = tap / p.kw, kx = tap - ky * p.kw;
                     for (int ks = ks0; ks < ks1; ks++) {
-                        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
+                        const bool armed = issued < pre;            /* this stage's barrier is armed and its filter tile on the way */
+                        if (!armed && !mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
                         const uint32_t sa = base + stage * C::STAGE_BYTES, sb = sa + A_STAGE_BYTES;
-                        mbar_expect_tx(full_bar(stage), (uint32_t)p.stage_tx);
+                        if (!armed) mbar_expect_tx(full_bar(stage), (uint32_t)p.stage_tx);
                         if (p.S == 0) {
                             tma_load_2d(sa, &mapA, ks * BK, mt * BM, full_bar(stage));
                         } else {
@@ -112,7 +129,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                                 tma_load_4d(sa + q * sub_bytes, &mapA, ks * BK, txi * p.TW + kx - p.pad, tyi * p.TH + ky - p.pad, img, full_bar(stage));
                             }
                         }
-                        tma_load_2d(sb, &mapB, tap * p.CinPad + ks * BK, nt * BN, full_bar(stage));
+                        if (!armed) tma_load_2d(sb, &mapB, tap * p.CinPad + ks * BK, nt * BN, full_bar(stage));
                         issued++;
                         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                     }
