@@ -8,7 +8,9 @@
  * per CTA; every tile of pixels then costs ceil(9*Cin/8) tcgen05.mma instructions, so the layer is bound by
  * writing its output: algorithmic bytes = n*H*W*(Cin + Cout)*4.
  * Replaces the reference's Winograd launch for such layers (src/dR_nodes_conv2d.c:36-53 sends every 3x3
- * stride-1 filter to conv2dwinograd2, Kernels/dR_winograd2.cl:23-254).
+ * stride-1 filter to conv2dwinograd2, Kernels/dR_winograd2.cl:23-254).  A 2x2/2 max or average pooling node
+ * behind the layer (src/dR_nodes_pooling.c:138-183) can be evaluated in the epilogue, and a Slice -> scalar op ->
+ * Concat preamble in front of it by the gather (see FirstInMap).
  *
  * Persistent CTAs, 17 warps: warp 0 issues the MMAs and owns TMEM; warps 1-8 are the epilogue (a lane owns an
  * output channel, two warps share each 32-lane quarter of TMEM and split the 256 pixel columns; a store
