@@ -30,6 +30,7 @@ struct UmmaParams {
     int ksplit, kper;               /* split-K (flat GEMM mode): ksplit partial products over kper slabs each */
     long long split_stride;         /* floats between the partial outputs of consecutive K parts */
     int *status;
+    int P, ncols;                   /* transposed kernel: pixel pitch of a block row (16 or 32) and MMA columns per tile = P * TH */
 };
 
 /* ------------------------------------------------------------------ PTX wrappers */

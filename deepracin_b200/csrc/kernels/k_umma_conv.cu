@@ -561,11 +561,8 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
  * each epilogue lane owns one channel, a warp stores 32 consecutive channels of one pixel per
  * instruction, and the fused 2x2 max pooling is a maximum over four registers of the same lane.
  */
-#define SWAP_TH 16
-#define SWAP_N 256
-#define SWAP_HALO_ROWS ((SWAP_TH + 2) * HALO_P)        /* 288 rows loaded per slab */
-#define SWAP_HALO_BYTES (SWAP_HALO_ROWS * BK * 4)      /* 36864 */
-#define SWAP_HALO_SLOT (38 * 1024)                     /* 304 rows >= 256 + 2*16 + 2 */
+#define SWAP_N 256                                     /* most MMA columns per tile; a tile is TH block rows of P pixels, P * TH <= 256 */
+#define SWAP_HALO_SLOT (38 * 1024)                     /* (TH + 2) * P <= 288 rows loaded; taps of idle columns read a few rows further */
 #define SWAP_NH 2
 #define SWAP_W_BYTES (BM * BK * 4)                     /* filter stage: 128 rows x 128 B */
 #define SWAP_NW 9
@@ -597,6 +594,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     const int total_tiles = p.m_tiles * p.n_tiles;
     const int per = p.tiles_x * p.tiles_y;
     constexpr int TMEM_COLS = 2 * SWAP_N;
+    const uint32_t halo_bytes = (uint32_t)((p.TH + 2) * p.P * BK * 4);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SWAP_NH; s++) { mbar_init(hfull(s), 1); mbar_init(hempty(s), 1); }
@@ -626,8 +624,8 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                 const int tyi = rem / p.tiles_x, txi = rem - tyi * p.tiles_x;
                 for (int ks = 0; ks < p.kslabs && ok; ks++) {
                     if (!mbar_wait(hempty(hs), hph ^ 1u, abort_flag, p.status, 5)) { ok = false; break; }
-                    mbar_expect_tx(hfull(hs), SWAP_HALO_BYTES);
-                    tma_load_4d(h_base + hs * SWAP_HALO_SLOT, &mapX, ks * BK, txi * HALO_TW - 1, tyi * SWAP_TH - 1, img, hfull(hs));
+                    mbar_expect_tx(hfull(hs), halo_bytes);
+                    tma_load_4d(h_base + hs * SWAP_HALO_SLOT, &mapX, ks * BK, txi * p.TW - 1, tyi * p.TH - 1, img, hfull(hs));
                     h_issued++;
                     if (++hs == SWAP_NH) { hs = 0; hph ^= 1u; }
                     for (int tap = 0; tap < 9; tap++) {
@@ -658,7 +656,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(SWAP_N);
+            const uint32_t idesc = make_idesc(p.ncols);
             int hs = 0, ws = 0;
             uint32_t hph = 0, wph = 0;
             int it = 0;
@@ -677,7 +675,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                         tc_fence_after();
                         const int ky = tap / 3, kx = tap - ky * 3;
                         const uint64_t adesc = make_smem_desc(w_base + ws * SWAP_W_BYTES);
-                        const uint64_t bdesc = make_smem_desc(sh + (uint32_t)((ky * HALO_P + kx) * BK * 4));
+                        const uint64_t bdesc = make_smem_desc(sh + (uint32_t)((ky * p.P + kx) * BK * 4));
 #pragma unroll
                         for (int j = 0; j < BK / 8; j++)
                             umma_tf32(d_tmem, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, (ks | tap | j) ? 1u : 0u);
@@ -712,12 +710,26 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * SWAP_N);
 #pragma unroll 1
-            for (int c0 = half * (SWAP_N / 2); c0 < (half + 1) * (SWAP_N / 2); c0 += 32) {
+            for (int c0 = half * 32; c0 < p.ncols; c0 += 64) {           /* the two warps of a quarter take alternate 32-column chunks */
                 uint32_t r[32];
                 tmem_ld32(taddr + (uint32_t)c0, r);
                 if (!chok) continue;
-                const int y0 = tyi * SWAP_TH + (c0 >> 4);          /* this chunk holds block rows y0 and y0 + 1 */
-                const int x0 = txi * HALO_TW;
+                const int x0 = txi * p.TW;
+                if (p.P == 32) {
+                    /* 32-pixel pitch (images up to 30 wide, no pooling): the chunk is one block row */
+                    const int y = tyi * p.TH + (c0 >> 5);
+                    if (y < p.H) {
+                        float *optr = obase + (((size_t)img * p.H + y) * p.W + x0) * (size_t)p.ldo;
+                        const int nx = min(p.TW, p.W - x0);
+#pragma unroll
+                        for (int dx = 0; dx < 30; dx++) {
+                            if (dx < nx) *optr = fminf(fmaxf(__uint_as_float(r[dx]) + bv, lo), hi);
+                            optr += p.ldo;
+                        }
+                    }
+                    continue;
+                }
+                const int y0 = tyi * p.TH + (c0 >> 4);             /* 16-pixel pitch: this chunk holds block rows y0 and y0 + 1 */
                 if (p.pool) {
                     const int yo = y0 >> 1;
                     if (yo < (p.H >> 1)) {
@@ -863,11 +875,30 @@ static double halo_fill(int W, int H)
     return (double)W * H / (tx * ty * BM);
 }
 
-/* same for the transposed variant's 14 x 16 blocks (256 MMA columns per block) */
+/* Geometry of the transposed variant: block rows of P = 16 (14 valid) or 32 (up to 30 valid) pixels, TH of them per tile,
+ * N = P * TH <= 256 MMA columns.  Picks the one with the largest share of columns that are output pixels; fused pooling
+ * needs the 16-pixel pitch (both rows of a window in one 32-column chunk) and an even TH.  Returns that share. */
+static double swap_geometry(int W, int H, int pool, int *P, int *TW, int *TH)
+{
+    double best = -1.0;
+    for (int pitch = 16; pitch <= 32; pitch += 16) {
+        if (pitch == 32 && (pool || W > 30)) continue;
+        const int tw = pitch == 16 ? HALO_TW : (W < 30 ? W : 30);
+        for (int th = SWAP_N / pitch; th >= 4; th--) {
+            if ((pitch * th) % 32 || (pitch * th) % 16) continue;       /* whole 32-column epilogue chunks; N a multiple of 16 */
+            if (pool && (th & 1)) continue;
+            if ((th + 2) * pitch > 288) continue;                        /* the haloed block has to fit its shared-memory slot */
+            const double tx = (W + tw - 1) / tw, ty = (H + th - 1) / th;
+            const double fill = (double)W * H / (tx * ty * pitch * th) - (pitch * th < 192 ? 0.15 : 0.0);   /* narrow instructions issue badly */
+            if (fill > best + 1e-9) { best = fill; *P = pitch; *TW = tw; *TH = th; }
+        }
+    }
+    return best;
+}
 static double swap_fill(int W, int H)
 {
-    const double tx = (W + HALO_TW - 1) / HALO_TW, ty = (H + SWAP_TH - 1) / SWAP_TH;
-    return (double)W * H / (tx * ty * SWAP_N);
+    int P, TW, TH;
+    return swap_geometry(W, H, 1, &P, &TW, &TH);
 }
 
 /* which kernel evaluates a layer shape; the packed-filter layout depends on it, so packing and planning both ask here.
@@ -933,6 +964,12 @@ extern "C" int dRk_tensor_conv_pack_weights(const float *w, float *dst, int W, i
             for (int t = 0; t < taps; t++)
                 dst[(size_t)o * taps * cp + (size_t)t * cp + c] = w[((size_t)c * Cout + o) * taps + t];
     return 0;
+}
+
+static int swap_wins_over_halo(int W, int H, int pool)
+{
+    int P, TW, TH;
+    return swap_geometry(W, H, pool ? 1 : 0, &P, &TW, &TH) >= halo_fill(W, H) + 0.08;
 }
 
 static int pick_bn(int Cout, long long m_tiles, int sms)
@@ -1040,15 +1077,19 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
         if (r == CUDA_SUCCESS)
             r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void *)(in + (size_t)W * Cin), dimsO, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    } else if (variant == VAR_SWAP) {
+    } else if (variant == VAR_SWAP || (variant == VAR_HALO && !getenv("DRK_NO_SWAP") && swap_wins_over_halo(W, H, fuse_pool2))) {
+        /* also for more than 128 output channels (several channel blocks per pixel tile) where the transposed kernel's tiles
+           leave fewer MMA columns idle than the halo kernel's 14 x 8 blocks: 28- and 14-pixel images */
         pl->swap = 1;
-        p.TW = HALO_TW; p.TH = SWAP_TH; p.S = 1;
-        p.tiles_x = (W + HALO_TW - 1) / HALO_TW; p.tiles_y = (H + SWAP_TH - 1) / SWAP_TH;
+        p.S = 1;
+        swap_geometry(W, H, fuse_pool2 ? 1 : 0, &p.P, &p.TW, &p.TH);
+        p.ncols = p.P * p.TH;
+        p.tiles_x = (W + p.TW - 1) / p.TW; p.tiles_y = (H + p.TH - 1) / p.TH;
         p.total_sub = (long long)n * p.tiles_x * p.tiles_y;
         p.m_tiles = (int)p.total_sub;
         const cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)n};
         const cuuint64_t strides[3] = {(cuuint64_t)Cin * 4, (cuuint64_t)W * Cin * 4, (cuuint64_t)H * W * Cin * 4};
-        const cuuint32_t box[4] = {BK, HALO_P, SWAP_TH + 2, 1};
+        const cuuint32_t box[4] = {BK, (cuuint32_t)p.P, (cuuint32_t)(p.TH + 2), 1};
         r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void *)in, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     } else if (variant == VAR_HALO) {
