@@ -966,10 +966,25 @@ extern "C" int dRk_tensor_conv_pack_weights(const float *w, float *dst, int W, i
     return 0;
 }
 
-static int swap_wins_over_halo(int W, int H, int pool)
+/* Transposed or halo kernel for a 3x3 layer (their packed filters are the same, so this is decided per plan, with the batch
+ * known).  With at least one tile per SM the transposed kernel is taken unless the halo kernel's 14 x 8 blocks leave fewer
+ * MMA rows idle than its tiles leave columns (at equal fill it measured ~5 % faster; on 28- and 14-pixel images it fills
+ * 0.875 against 0.766).  With fewer tiles than SMs (batch 1) latency counts, not idle columns, and the halo kernel's
+ * smaller tiles spread further: then only layers of at most 128 channels whose image tiles well into 14 x 16 blocks go
+ * to the transposed kernel. */
+static int use_swap_kernel(int variant, int n, int W, int H, int Cout, int pool, int sms)
 {
     int P, TW, TH;
-    return swap_geometry(W, H, pool ? 1 : 0, &P, &TW, &TH) >= halo_fill(W, H) + 0.08;
+    if (getenv("DRK_NO_SWAP")) return 0;
+    const double fill = swap_geometry(W, H, pool ? 1 : 0, &P, &TW, &TH);
+    if (fill <= 0.0) return 0;
+    const long long tiles = (long long)n * ((W + TW - 1) / TW) * ((H + TH - 1) / TH) * ((Cout + BM - 1) / BM);
+    if (tiles >= sms) {
+        const double margin = getenv("DRK_SWAP_MARGIN") ? atof(getenv("DRK_SWAP_MARGIN")) : -0.01;     /* A/B comparisons when profiling */
+        return variant == VAR_SWAP || fill >= halo_fill(W, H) + margin;
+    }
+    const double tx = (W + HALO_TW - 1) / HALO_TW, ty = (H + 15) / 16;
+    return Cout <= BM && (double)W * H / (tx * ty * SWAP_N) >= 0.8;
 }
 
 static int pick_bn(int Cout, long long m_tiles, int sms)
@@ -1077,9 +1092,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
         if (r == CUDA_SUCCESS)
             r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void *)(in + (size_t)W * Cin), dimsO, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    } else if (variant == VAR_SWAP || (variant == VAR_HALO && !getenv("DRK_NO_SWAP") && swap_wins_over_halo(W, H, fuse_pool2))) {
-        /* also for more than 128 output channels (several channel blocks per pixel tile) where the transposed kernel's tiles
-           leave fewer MMA columns idle than the halo kernel's 14 x 8 blocks: 28- and 14-pixel images */
+    } else if ((variant == VAR_SWAP || variant == VAR_HALO) && use_swap_kernel(variant, n, W, H, Cout, fuse_pool2, sms)) {
         pl->swap = 1;
         p.S = 1;
         swap_geometry(W, H, fuse_pool2 ? 1 : 0, &p.P, &p.TW, &p.TH);
@@ -1092,7 +1105,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
         const cuuint32_t box[4] = {BK, (cuuint32_t)p.P, (cuuint32_t)(p.TH + 2), 1};
         r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void *)in, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    } else if (variant == VAR_HALO) {
+    } else if ((variant == VAR_HALO || variant == VAR_SWAP) && halo_fill(W, H) >= 0.55 && !getenv("DRK_NO_HALO")) {
         pl->halo = 1;
         p.TW = HALO_TW; p.TH = HALO_TH; p.S = 1;
         p.tiles_x = (W + HALO_TW - 1) / HALO_TW; p.tiles_y = (H + HALO_TH - 1) / HALO_TH;
