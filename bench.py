@@ -198,14 +198,14 @@ def run_ours(args):
             roof = {"bound": "tensor", "achieved": aggregate, "peak": peak, "unit": "TFLOP/s", "frac": (aggregate / peak) if aggregate else None,
                     "traffic": None, "kernel": "convolution (%d launches, aggregate)" % n_conv, "peak_source": peak_src}
             if args.net == "vgg16" and n_conv == 13 and conv_times[5] > 0:
-                # dominant kernel: the 256/512-channel 3x3 layers (k_umma_conv_halo<256> in TF32 mode); measured live on conv3_2
+                # dominant kernel: the 128..512-channel 3x3 layers (k_umma_conv_swap in TF32 mode); measured live on conv3_2
                 ci, co, hw = VGG_CONVS[5]
                 one = 2.0 * 9 * ci * co * hw * hw * batch / (conv_times[5] * 1e-3) / 1e12
                 roof = {"bound": "tensor", "achieved": one, "peak": peak, "unit": "TFLOP/s", "frac": one / peak,
                         # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this layer at batch 64 (ncu capture, see profiles/)
-                        "traffic": 362.1e6 if (tensor and batch == 64) else None,
+                        "traffic": 369.2e6 if (tensor and batch == 64) else None,
                         "algorithmic_bytes": 4.0 * (batch * hw * hw * (ci + co) + 9 * ci * co),
-                        "kernel": "conv3_2 256->256 @56x56 (%s), %.4f ms per launch" % ("k_umma_conv_halo<256>" if tensor else "FP32 variant chosen at prepare", conv_times[5]),
+                        "kernel": "conv3_2 256->256 @56x56 (%s), %.4f ms per launch" % ("k_umma_conv_swap" if tensor else "FP32 variant chosen at prepare", conv_times[5]),
                         "peak_source": peak_src}
             roof["conv_aggregate"] = {"tflops": aggregate, "frac": (aggregate / peak) if aggregate else None, "launches": n_conv, "ms": round(conv_ms, 4)}
             roof["ms_by_kind"] = {k: round(sum(t for kk, t in prof if kk == k), 4) for k in sorted(set(k for k, _ in prof))}
