@@ -710,25 +710,51 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * SWAP_N);
 #pragma unroll 1
+            if (p.P != 16) {
+                /* 30- or 32-pixel pitch: a block row is one 32-column TMEM load starting at column row * P (the last P - TW columns
+                   of it are idle, a load at pitch 30 also fetches two columns of the next row that are not used); the two warps of a
+                   quarter take alternate rows, or row pairs when the 2x2 pool is fused */
+                const int x0 = txi * p.TW;
+                if (chok) {
+                    if (p.pool) {
+                        for (int u = half; u < (p.TH >> 1); u += 2) {
+                            uint32_t r0[32], r1[32];
+                            tmem_ld32(taddr + (uint32_t)(2 * u * p.P), r0);
+                            tmem_ld32(taddr + (uint32_t)((2 * u + 1) * p.P), r1);
+                            const int yo = ((tyi * p.TH) >> 1) + u;
+                            if (yo >= (p.H >> 1)) break;
+                            float *orow = obase + (((size_t)img * (p.H >> 1) + yo) * (size_t)(p.W >> 1) + (x0 >> 1)) * p.ldo;
+                            const int nx = min(p.TW >> 1, (p.W >> 1) - (x0 >> 1));
+#pragma unroll
+                            for (int px = 0; px < 15; px++) {
+                                const float v = fmaxf(fmaxf(__uint_as_float(r0[2 * px]), __uint_as_float(r0[2 * px + 1])),
+                                                      fmaxf(__uint_as_float(r1[2 * px]), __uint_as_float(r1[2 * px + 1])));
+                                if (px < nx) *orow = fminf(fmaxf(v + bv, lo), hi);
+                                orow += p.ldo;
+                            }
+                        }
+                    } else {
+                        for (int u = half; u < p.TH; u += 2) {
+                            uint32_t r[32];
+                            tmem_ld32(taddr + (uint32_t)(u * p.P), r);
+                            const int y = tyi * p.TH + u;
+                            if (y >= p.H) break;
+                            float *optr = obase + (((size_t)img * p.H + y) * p.W + x0) * (size_t)p.ldo;
+                            const int nx = min(p.TW, p.W - x0);
+#pragma unroll
+                            for (int dx = 0; dx < 30; dx++) {
+                                if (dx < nx) *optr = fminf(fmaxf(__uint_as_float(r[dx]) + bv, lo), hi);
+                                optr += p.ldo;
+                            }
+                        }
+                    }
+                }
+            } else
             for (int c0 = half * 32; c0 < p.ncols; c0 += 64) {           /* the two warps of a quarter take alternate 32-column chunks */
                 uint32_t r[32];
                 tmem_ld32(taddr + (uint32_t)c0, r);
                 if (!chok) continue;
                 const int x0 = txi * p.TW;
-                if (p.P == 32) {
-                    /* 32-pixel pitch (images up to 30 wide, no pooling): the chunk is one block row */
-                    const int y = tyi * p.TH + (c0 >> 5);
-                    if (y < p.H) {
-                        float *optr = obase + (((size_t)img * p.H + y) * p.W + x0) * (size_t)p.ldo;
-                        const int nx = min(p.TW, p.W - x0);
-#pragma unroll
-                        for (int dx = 0; dx < 30; dx++) {
-                            if (dx < nx) *optr = fminf(fmaxf(__uint_as_float(r[dx]) + bv, lo), hi);
-                            optr += p.ldo;
-                        }
-                    }
-                    continue;
-                }
                 const int y0 = tyi * p.TH + (c0 >> 4);             /* 16-pixel pitch: this chunk holds block rows y0 and y0 + 1 */
                 if (p.pool) {
                     const int yo = y0 >> 1;
@@ -875,21 +901,26 @@ static double halo_fill(int W, int H)
     return (double)W * H / (tx * ty * BM);
 }
 
-/* Geometry of the transposed variant: block rows of P = 16 (14 valid) or 32 (up to 30 valid) pixels, TH of them per tile,
- * N = P * TH <= 256 MMA columns.  Picks the one with the largest share of columns that are output pixels; fused pooling
- * needs the 16-pixel pitch (both rows of a window in one 32-column chunk) and an even TH.  Returns that share. */
+/* Geometry of the transposed variant: block rows of P = 16 (14 valid), 30 (28 valid) or 32 (up to 30 valid) pixels, TH of
+ * them per tile, N = P * TH <= 256 MMA columns (the operand is a window of consecutive shared-memory rows, so any pitch
+ * works).  Picks the one with the largest share of columns that are output pixels; fused pooling needs an even TH.
+ * Returns that share. */
 static double swap_geometry(int W, int H, int pool, int *P, int *TW, int *TH)
 {
     double best = -1.0;
-    for (int pitch = 16; pitch <= 32; pitch += 16) {
-        if (pitch == 32 && (pool || W > 30)) continue;
-        const int tw = pitch == 16 ? HALO_TW : (W < 30 ? W : 30);
+    const int pitches[3] = {16, 30, 32};
+    for (int pi = 0; pi < 3; pi++) {
+        const int pitch = pitches[pi];
+        const int tw = pitch == 16 ? HALO_TW : pitch == 30 ? 28 : (W < 30 ? (W & ~1) : 30);
+        if (tw < 2) continue;
         for (int th = SWAP_N / pitch; th >= 4; th--) {
-            if ((pitch * th) % 32 || (pitch * th) % 16) continue;       /* whole 32-column epilogue chunks; N a multiple of 16 */
+            const int ncols = pitch * th;
+            if (ncols % 16) continue;                                    /* N of the MMA */
+            if (pitch == 16 && ncols % 32) continue;                     /* 16-pixel pitch: whole 32-column epilogue chunks */
             if (pool && (th & 1)) continue;
-            if ((th + 2) * pitch > 288) continue;                        /* the haloed block has to fit its shared-memory slot */
+            if (ncols + 2 * pitch + 2 > 304) continue;                   /* the taps of the last columns must stay inside the shared-memory slot */
             const double tx = (W + tw - 1) / tw, ty = (H + th - 1) / th;
-            const double fill = (double)W * H / (tx * ty * pitch * th) - (pitch * th < 192 ? 0.15 : 0.0);   /* narrow instructions issue badly */
+            const double fill = (double)W * H / (tx * ty * ncols) - (ncols < 192 ? 0.15 : 0.0);   /* narrow instructions issue badly */
             if (fill > best + 1e-9) { best = fill; *P = pitch; *TW = tw; *TH = th; }
         }
     }
