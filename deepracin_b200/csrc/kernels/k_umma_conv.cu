@@ -836,8 +836,7 @@ struct dRk_TensorConvPlan {
 };
 
 double drk_umma_pair_fill(int W, int H);
-void drk_umma_pair_geometry(int W, int H, int *tiles_x, int *tiles_y);
-void drk_umma_pair_boxes(unsigned box_plane[4], unsigned box_w[2]);
+double drk_umma_pair_geometry(int W, int H, int *P, int *TW, int *TJ);
 int drk_umma_pair_launch(cudaStream_t st, const CUtensorMap *mapO, const CUtensorMap *mapE, const CUtensorMap *mapW, const UmmaParams *p, int grid);
 int drk_umma_first_supported(int Cin, int Cout, int kw, int kh);
 int drk_umma_first_can_pool(int W, int H, int Cin, int Cout);
@@ -1108,12 +1107,12 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     } else if (variant == VAR_PAIR) {
         pl->pair = 1;
         p.S = 1;
-        drk_umma_pair_geometry(W, H, &p.tiles_x, &p.tiles_y);
+        drk_umma_pair_geometry(W, H, &p.P, &p.TW, &p.TH);          /* TH = row pairs per tile */
+        p.ncols = p.P * p.TH;
+        p.tiles_x = (W + p.TW - 1) / p.TW; p.tiles_y = (H + 2 * p.TH - 1) / (2 * p.TH);
         p.total_sub = (long long)n * p.tiles_x * p.tiles_y;
         p.m_tiles = (int)p.total_sub;
-        unsigned bp[4], bw[2];
-        drk_umma_pair_boxes(bp, bw);
-        const cuuint32_t box[4] = {bp[0], bp[1], bp[2], bp[3]};
+        const cuuint32_t box[4] = {BK, (cuuint32_t)p.P, (cuuint32_t)(p.TH + 1), 1};
         /* input rows split by parity: the even plane starts at row 0, the odd plane at row 1, both step two rows */
         const cuuint64_t strides[3] = {(cuuint64_t)Cin * 4, (cuuint64_t)2 * W * Cin * 4, (cuuint64_t)H * W * Cin * 4};
         const cuuint64_t dimsE[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)((H + 1) / 2), (cuuint64_t)n};

@@ -29,13 +29,11 @@
 #include "k_umma.cuh"
 
 #define PAIR_THREADS 192
-#define PAIR_TW 14
-#define PAIR_P 16                                       /* pixel pitch of a block row */
-#define PAIR_TJ 16                                      /* row pairs per tile */
+/* Two block geometries, chosen per layer (UmmaParams P, TW, TH = row pairs per tile, ncols = P * TH):
+ *   P = 16, 14 valid pixels, 16 row pairs: N = 256, 14 x 32 output pixels per tile (0.875 of the columns are pixels);
+ *   P = 30, 28 valid pixels,  8 row pairs: N = 240, 28 x 16 output pixels per tile (0.933). */
 #define PAIR_N 256
-#define PAIR_PLANE_ROWS ((PAIR_TJ + 1) * PAIR_P)        /* 272 shared-memory rows loaded per plane and slab */
-#define PAIR_PLANE_BYTES (PAIR_PLANE_ROWS * BK * 4)     /* 34816 */
-#define PAIR_PLANE_SLOT (35 * 1024)                     /* 280 rows >= 256 + 16 + 2 */
+#define PAIR_PLANE_SLOT (35 * 1024)                     /* 280 rows: (TH + 1) * P <= 272 loaded, taps of idle columns read a few rows further */
 #define PAIR_NH 3                                       /* ring of plane slots: odd and even planes of a slab are separate stages */
 #define PAIR_W_BYTES (BM * BK * 4)
 #define PAIR_NW 7
@@ -72,6 +70,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
     const int total_tiles = p.m_tiles;
     const int per = p.tiles_x * p.tiles_y;
     constexpr int TMEM_COLS = 2 * PAIR_N;
+    const uint32_t plane_bytes = (uint32_t)((p.TH + 1) * p.P * BK * 4);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < PAIR_NH; s++) { mbar_init(hfull(s), 1); mbar_init(hempty(s), 1); }
@@ -101,15 +100,15 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const int img = t / per, rem = t - img * per;
                 const int tyi = rem / p.tiles_x, txi = rem - tyi * p.tiles_x;
-                const int j0 = tyi * PAIR_TJ;
+                const int j0 = tyi * p.TH;
                 /* issue order = the MMA issuer's consumption order: odd plane, its six filter tiles, even plane, its six */
                 for (int ks = 0; ks < p.kslabs && ok; ks++) {
                     for (int half = 0; half < 2 && ok; half++) {
                         if (!mbar_wait(hempty(hs), hph ^ 1u, abort_flag, p.status, 5)) { ok = false; break; }
-                        mbar_expect_tx(hfull(hs), PAIR_PLANE_BYTES);
+                        mbar_expect_tx(hfull(hs), plane_bytes);
                         /* odd plane rows j0-1 .. j0+15 (input rows 2j0-1, 2j0+1, ...), even plane rows j0 .. j0+16 */
-                        if (half == 0) tma_load_4d(h_base + hs * PAIR_PLANE_SLOT, &mapO, ks * BK, txi * PAIR_TW - 1, j0 - 1, img, hfull(hs));
-                        else tma_load_4d(h_base + hs * PAIR_PLANE_SLOT, &mapE, ks * BK, txi * PAIR_TW - 1, j0, img, hfull(hs));
+                        if (half == 0) tma_load_4d(h_base + hs * PAIR_PLANE_SLOT, &mapO, ks * BK, txi * p.TW - 1, j0 - 1, img, hfull(hs));
+                        else tma_load_4d(h_base + hs * PAIR_PLANE_SLOT, &mapE, ks * BK, txi * p.TW - 1, j0, img, hfull(hs));
                         h_issued++;
                         if (++hs == PAIR_NH) { hs = 0; hph ^= 1u; }
                         for (int q = 0; q < 6; q++) {
@@ -142,7 +141,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc(PAIR_N);
+            const uint32_t idesc = make_idesc(p.ncols);
             int hs = 0, ws = 0;
             uint32_t hph = 0, wph = 0;
             int it = 0;
@@ -163,7 +162,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
                             /* input row 2j-1+i with i = half + 2*(q/3): the second three products read one block row further down */
                             const int down = q / 3, kx = q - down * 3;
                             const uint64_t adesc = make_smem_desc(w_base + ws * PAIR_W_BYTES);
-                            const uint64_t bdesc = make_smem_desc(plane + (uint32_t)((down * PAIR_P + kx) * BK * 4));
+                            const uint64_t bdesc = make_smem_desc(plane + (uint32_t)((down * p.P + kx) * BK * 4));
 #pragma unroll
                             for (int j = 0; j < BK / 8; j++)
                                 umma_tf32(d_tmem, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, (ks | half | q | j) ? 1u : 0u);
@@ -195,15 +194,66 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
             const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
             const int img = t / per, rem = t - img * per;
             const int tyi = rem / p.tiles_x, txi = rem - tyi * p.tiles_x;
-            const int x0 = txi * PAIR_TW;
+            const int x0 = txi * p.TW;
             if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * PAIR_N);
+            if (p.P != 16) {
+                /* 30-pixel pitch: a row pair is one 32-column TMEM load at column j * P (28 pixels of it are output) */
+#pragma unroll 1
+                for (int j = 0; j < p.TH && ok; j++) {
+                    uint32_t r[32];
+                    tmem_ld32(taddr + (uint32_t)(j * p.P), r);
+                    const int jrow = tyi * p.TH + j;
+                    if (p.pool) {
+                        float h[14];
+#pragma unroll
+                        for (int px = 0; px < 14; px++) h[px] = fmaxf(__uint_as_float(r[2 * px]), __uint_as_float(r[2 * px + 1]));
+                        const int b = (int)(gc & 1u);
+                        const uint32_t xph = (gc >> 1) & 1u;
+                        float *xs = xb + b * PAIR_X_FLOATS + lane;
+                        if (lower) {
+                            if (!mbar_wait(xempty(pr, b), xph ^ 1u, abort_flag, p.status, 7)) { ok = false; break; }
+#pragma unroll
+                            for (int k = 0; k < 14; k++) xs[k * 32] = h[k];
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(xfull(pr, b));
+                        } else {
+                            if (!mbar_wait(xfull(pr, b), xph, abort_flag, p.status, 8)) { ok = false; break; }
+#pragma unroll
+                            for (int k = 0; k < 14; k++) h[k] = fmaxf(h[k], xs[k * 32]);
+                            __syncwarp();
+                            if (lane == 0) mbar_arrive(xempty(pr, b));
+                            if (chok && jrow < (p.H >> 1)) {
+                                float *orow = obase + (((size_t)img * (p.H >> 1) + jrow) * (size_t)(p.W >> 1) + (x0 >> 1)) * p.ldo;
+                                const int nx = min(14, (p.W >> 1) - (x0 >> 1));
+#pragma unroll
+                                for (int px = 0; px < 14; px++) {
+                                    if (px < nx) *orow = fminf(fmaxf(h[px] + bv, lo), hi);
+                                    orow += p.ldo;
+                                }
+                            }
+                        }
+                        gc++;
+                    } else if (chok) {
+                        const int y = 2 * jrow + lower;
+                        if (y < p.H) {
+                            float *optr = obase + (((size_t)img * p.H + y) * p.W + x0) * (size_t)p.ldo;
+                            const int nx = min(p.TW, p.W - x0);
+#pragma unroll
+                            for (int dx = 0; dx < 28; dx++) {
+                                if (dx < nx) *optr = fminf(fmaxf(__uint_as_float(r[dx]) + bv, lo), hi);
+                                optr += p.ldo;
+                            }
+                        }
+                    }
+                }
+            } else
 #pragma unroll 1
             for (int c0 = 0; c0 < PAIR_N && ok; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(taddr + (uint32_t)c0, r);
-                const int jrow = tyi * PAIR_TJ + (c0 >> 4);          /* this chunk holds row pairs jrow and jrow + 1 */
+                const int jrow = tyi * p.TH + (c0 >> 4);             /* this chunk holds row pairs jrow and jrow + 1 */
                 if (p.pool) {
                     /* pooled row = row pair; horizontal maxima first, then the lower-row warp hands its values to the upper-row warp */
                     float h[14];
@@ -249,9 +299,9 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
                         const int y = 2 * (jrow + dy) + lower;
                         if (y >= p.H) break;
                         float *optr = obase + (((size_t)img * p.H + y) * p.W + x0) * (size_t)p.ldo;
-                        const int nx = min(PAIR_TW, p.W - x0);
+                        const int nx = min(14, p.W - x0);
 #pragma unroll
-                        for (int dx = 0; dx < PAIR_TW; dx++) {
+                        for (int dx = 0; dx < 14; dx++) {
                             if (dx < nx) *optr = fminf(fmaxf(__uint_as_float(r[dy * 16 + dx]) + bv, lo), hi);
                             optr += p.ldo;
                         }
@@ -268,23 +318,25 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
-/* fraction of the MMA columns that produce output pixels for a W x H image (14 x 32 blocks, 16-pixel pitch) */
+/* Picks the block geometry for a W x H image (see the top of the file): the one with the larger share of MMA columns that
+ * are output pixels.  Returns that share; P, TW, TJ (row pairs per tile) through the pointers. */
+double drk_umma_pair_geometry(int W, int H, int *P, int *TW, int *TJ)
+{
+    const int geo[2][3] = {{16, 14, 16}, {30, 28, 8}};
+    double best = -1.0;
+    for (int g = 0; g < 2; g++) {
+        const int pitch = geo[g][0], tw = geo[g][1], tj = geo[g][2];
+        const double tx = (W + tw - 1) / tw, ty = (H + 2 * tj - 1) / (2 * tj);
+        const double fill = (double)W * H / (tx * ty * 2 * pitch * tj);
+        if (fill > best + 1e-9) { best = fill; *P = pitch; *TW = tw; *TJ = tj; }
+    }
+    return best;
+}
+
 double drk_umma_pair_fill(int W, int H)
 {
-    const double tx = (W + PAIR_TW - 1) / PAIR_TW, ty = (H + 2 * PAIR_TJ - 1) / (2 * PAIR_TJ);
-    return (double)W * H / (tx * ty * 2 * PAIR_N);
-}
-
-void drk_umma_pair_geometry(int W, int H, int *tiles_x, int *tiles_y)
-{
-    *tiles_x = (W + PAIR_TW - 1) / PAIR_TW;
-    *tiles_y = (H + 2 * PAIR_TJ - 1) / (2 * PAIR_TJ);
-}
-
-void drk_umma_pair_boxes(unsigned box_plane[4], unsigned box_w[2])
-{
-    box_plane[0] = BK; box_plane[1] = PAIR_P; box_plane[2] = PAIR_TJ + 1; box_plane[3] = 1;
-    box_w[0] = BK; box_w[1] = BM;
+    int P, TW, TJ;
+    return drk_umma_pair_geometry(W, H, &P, &TW, &TJ);
 }
 
 int drk_umma_pair_launch(cudaStream_t st, const CUtensorMap *mapO, const CUtensorMap *mapE, const CUtensorMap *mapW, const UmmaParams *p, int grid)
