@@ -1065,6 +1065,33 @@ static int launch_umma(cudaStream_t st, dRk_TensorConvPlan *pl)
     return DRK_LAUNCH_RESULT();
 }
 
+/* Which kernel and block geometry the planner takes for a layer, without touching a device (variant: 1 flat 1x1, 2 plain,
+ * 3 halo, 4 transposed, 5 row pair, 6 few-channel first layer; 0 = not a tensor-path shape).  P / TW / TH are the pixel pitch,
+ * valid pixels and rows (row pairs for variant 5) of a block, ncols the MMA's N; zero where the variant has no such notion. */
+extern "C" int dRk_tensor_conv_describe(int n, int W, int H, int Cin, int Cout, int kw, int kh, int fuse_pool2, int sms,
+                                        int *P, int *TW, int *TH, int *ncols)
+{
+    int v = pick_variant(W, H, Cin, Cout, kw, kh);
+    *P = *TW = *TH = *ncols = 0;
+    if (v == VAR_NONE || !dRk_tensor_conv_can_fuse_pool(W, H, Cin, Cout, kw, kh, fuse_pool2)) return 0;
+    if (v == VAR_PAIR) {
+        drk_umma_pair_geometry(W, H, P, TW, TH);
+        *ncols = *P * *TH;
+    } else if (v == VAR_SWAP || v == VAR_HALO) {
+        if (use_swap_kernel(v, n, W, H, Cout, fuse_pool2, sms)) {
+            v = VAR_SWAP;
+            swap_geometry(W, H, fuse_pool2 ? 1 : 0, P, TW, TH);
+            *ncols = *P * *TH;
+        } else if (halo_fill(W, H) >= 0.55 && !getenv("DRK_NO_HALO")) {
+            v = VAR_HALO;
+            *P = HALO_P; *TW = HALO_TW; *TH = HALO_TH; *ncols = 0;
+        } else {
+            v = VAR_PLAIN;
+        }
+    }
+    return v;
+}
+
 extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float *wT, const float *bias, float *out, int n, int W, int H,
                                                     int Cin, int Cout, int kw, int kh, int act, int ldo, int coff, int fuse_pool2, int *status)
 {

@@ -143,6 +143,10 @@ dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float *wT, const
  * Concat preamble (examples/squeezenet-v1.1/squeezenet_whole/graph.dr:7-41) in front of the layer.  -1 if the plan is for
  * another kernel. */
 int dRk_tensor_conv_set_input_map(dRk_TensorConvPlan *plan, int ldi, const int *ch, const float *scale, const float *shift);
+/* Planner introspection, no device needed: the kernel (1 flat 1x1, 2 plain, 3 halo, 4 transposed, 5 row pair, 6 few-channel
+ * first layer; 0 = shape or pooling not supported) and block geometry a plan for this layer on a GPU with `sms` SMs would use. */
+int dRk_tensor_conv_describe(int n, int W, int H, int Cin, int Cout, int kw, int kh, int fuse_pool2, int sms,
+                             int *P, int *TW, int *TH, int *ncols);
 int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *plan);
 void dRk_tensor_conv_free(dRk_TensorConvPlan *plan);
 
