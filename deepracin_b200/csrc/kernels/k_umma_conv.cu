@@ -713,39 +713,40 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             if (p.P != 16) {
                 /* 30- or 32-pixel pitch: a block row is one 32-column TMEM load starting at column row * P (the last P - TW columns
                    of it are idle, a load at pitch 30 also fetches two columns of the next row that are not used); the two warps of a
-                   quarter take alternate rows, or row pairs when the 2x2 pool is fused */
+                   quarter take alternate rows, or row pairs when the 2x2 pool is fused.  The TMEM loads are warp-wide instructions:
+                   every lane executes them, lanes past Cout only skip the stores. */
                 const int x0 = txi * p.TW;
-                if (chok) {
-                    if (p.pool) {
-                        for (int u = half; u < (p.TH >> 1); u += 2) {
-                            uint32_t r0[32], r1[32];
-                            tmem_ld32(taddr + (uint32_t)(2 * u * p.P), r0);
-                            tmem_ld32(taddr + (uint32_t)((2 * u + 1) * p.P), r1);
-                            const int yo = ((tyi * p.TH) >> 1) + u;
-                            if (yo >= (p.H >> 1)) break;
-                            float *orow = obase + (((size_t)img * (p.H >> 1) + yo) * (size_t)(p.W >> 1) + (x0 >> 1)) * p.ldo;
-                            const int nx = min(p.TW >> 1, (p.W >> 1) - (x0 >> 1));
+                if (p.pool) {
+                    for (int u = half; u < (p.TH >> 1); u += 2) {
+                        uint32_t r0[32], r1[32];
+                        tmem_ld32(taddr + (uint32_t)(2 * u * p.P), r0);
+                        tmem_ld32(taddr + (uint32_t)((2 * u + 1) * p.P), r1);
+                        const int yo = ((tyi * p.TH) >> 1) + u;
+                        if (yo >= (p.H >> 1)) break;
+                        if (!chok) continue;
+                        float *orow = obase + (((size_t)img * (p.H >> 1) + yo) * (size_t)(p.W >> 1) + (x0 >> 1)) * p.ldo;
+                        const int nx = min(p.TW >> 1, (p.W >> 1) - (x0 >> 1));
 #pragma unroll
-                            for (int px = 0; px < 15; px++) {
-                                const float v = fmaxf(fmaxf(__uint_as_float(r0[2 * px]), __uint_as_float(r0[2 * px + 1])),
-                                                      fmaxf(__uint_as_float(r1[2 * px]), __uint_as_float(r1[2 * px + 1])));
-                                if (px < nx) *orow = fminf(fmaxf(v + bv, lo), hi);
-                                orow += p.ldo;
-                            }
+                        for (int px = 0; px < 15; px++) {
+                            const float v = fmaxf(fmaxf(__uint_as_float(r0[2 * px]), __uint_as_float(r0[2 * px + 1])),
+                                                  fmaxf(__uint_as_float(r1[2 * px]), __uint_as_float(r1[2 * px + 1])));
+                            if (px < nx) *orow = fminf(fmaxf(v + bv, lo), hi);
+                            orow += p.ldo;
                         }
-                    } else {
-                        for (int u = half; u < p.TH; u += 2) {
-                            uint32_t r[32];
-                            tmem_ld32(taddr + (uint32_t)(u * p.P), r);
-                            const int y = tyi * p.TH + u;
-                            if (y >= p.H) break;
-                            float *optr = obase + (((size_t)img * p.H + y) * p.W + x0) * (size_t)p.ldo;
-                            const int nx = min(p.TW, p.W - x0);
+                    }
+                } else {
+                    for (int u = half; u < p.TH; u += 2) {
+                        uint32_t r[32];
+                        tmem_ld32(taddr + (uint32_t)(u * p.P), r);
+                        const int y = tyi * p.TH + u;
+                        if (y >= p.H) break;
+                        if (!chok) continue;
+                        float *optr = obase + (((size_t)img * p.H + y) * p.W + x0) * (size_t)p.ldo;
+                        const int nx = min(p.TW, p.W - x0);
 #pragma unroll
-                            for (int dx = 0; dx < 30; dx++) {
-                                if (dx < nx) *optr = fminf(fmaxf(__uint_as_float(r[dx]) + bv, lo), hi);
-                                optr += p.ldo;
-                            }
+                        for (int dx = 0; dx < 30; dx++) {
+                            if (dx < nx) *optr = fminf(fmaxf(__uint_as_float(r[dx]) + bv, lo), hi);
+                            optr += p.ldo;
                         }
                     }
                 }
@@ -942,7 +943,8 @@ static int pick_variant(int W, int H, int Cin, int Cout, int kw, int kh)
     const bool no_halo = getenv("DRK_NO_HALO") != NULL;
     if (Cout <= 64 && H >= 2 && drk_umma_pair_fill(W, H) >= 0.5 && !getenv("DRK_NO_PAIR") && !no_halo) return VAR_PAIR;
     if (Cout <= BM && swap_fill(W, H) >= 0.8 && !getenv("DRK_NO_SWAP") && !no_halo) return VAR_SWAP;
-    if (halo_fill(W, H) >= 0.55 && !no_halo) return VAR_HALO;
+    /* halo or transposed kernel: which of the two is settled per plan, when the batch is known (use_swap_kernel) */
+    if ((halo_fill(W, H) >= 0.55 || swap_fill(W, H) >= 0.55) && !no_halo) return VAR_HALO;
     return VAR_PLAIN;
 }
 

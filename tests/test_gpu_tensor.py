@@ -45,6 +45,12 @@ TENSOR_SHAPES = [
     ("t_first_c4_cout64", 1, 4, 64, 10, 12, 3),      # two K slabs and only two of the four TMEM lane quarters in use
     ("t_first_c3_cout128", 1, 3, 128, 9, 9, 3),
     ("t_pair_w15", 2, 24, 40, 34, 15, 3),            # image one pixel wider than a 14-pixel block: a second, nearly empty block column
+    # enough images for a tile per SM: the planner then takes the transposed kernel with the geometry that fills best
+    ("t_swap_p30", 40, 8, 128, 56, 56, 3),           # 28 x 8-pixel tiles at a 30-pixel pitch, N = 240
+    ("t_swap_p16_th14", 40, 8, 256, 28, 28, 3),      # 14 x 14-pixel tiles, N = 224, two channel blocks per pixel tile
+    ("t_swap_14x14", 160, 8, 192, 14, 14, 3),        # one image per tile
+    ("t_swap_odd", 40, 8, 136, 29, 27, 3),           # odd width and height, channel count that does not fill the last block
+    ("t_pair_p30", 6, 16, 64, 56, 56, 3),            # row-pair kernel at the 30-pixel pitch
 ]
 
 
@@ -102,7 +108,8 @@ def test_tf32_network_agrees_with_fp32_on_top1():
     assert rel_err(outs["tf32"], outs["fp32"]) <= 2e-2     # probabilities after 16 TF32 layers
 
 
-@pytest.mark.parametrize("n,cin,cout,h,w", [(1, 64, 64, 56, 56), (2, 128, 256, 28, 28), (3, 256, 512, 14, 14), (2, 32, 64, 12, 20), (1, 64, 64, 224, 224), (2, 32, 48, 28, 30), (3, 64, 32, 64, 28), (2, 16, 16, 32, 28), (1, 128, 128, 16, 46)])
+@pytest.mark.parametrize("n,cin,cout,h,w", [(1, 64, 64, 56, 56), (2, 128, 256, 28, 28), (3, 256, 512, 14, 14), (2, 32, 64, 12, 20), (1, 64, 64, 224, 224), (2, 32, 48, 28, 30), (3, 64, 32, 64, 28), (2, 16, 16, 32, 28), (1, 128, 128, 16, 46),
+                                            (40, 8, 128, 56, 56), (40, 8, 256, 28, 28), (160, 8, 192, 14, 14), (6, 16, 64, 56, 56), (40, 8, 72, 30, 26)])
 def test_conv_with_fused_maxpool_matches_oracle(n, cin, cout, h, w):
     """conv3x3 + ReLU followed by 2x2/2 max pooling: the tensor kernel's epilogue stores the pooled tensor."""
     x, wt, b = cases.conv_case("fusedpool_%d_%d" % (cin, h), n, cin, cout, h, w, 3, True)
