@@ -239,3 +239,36 @@ def test_tensor_planner_picks_the_expected_kernels_and_geometries():
     assert describe(64, 224, 224, 3, 64, 3, 2)[0] == FIRST                           # first layer with the average pool fused
     assert describe(64, 56, 56, 256, 256, 3, 2)[0] == 0                              # average pooling is only fused into the first-layer kernel
     assert describe(2, 20, 20, 64, 64, 5, 0)[0] == 0                                 # 5x5 filters stay on the FP32 kernels
+
+
+def test_tensor_planner_geometries_respect_the_kernels_limits():
+    """Every geometry the planner can hand to the transposed and row-pair kernels stays inside what those kernels were
+    written for: N a multiple of 16 and at most 256, whole 32-column epilogue chunks at the 16-pixel pitch, an even row
+    count under fused pooling, the last column's taps inside the 304-pixel shared-memory slot, valid pixels at most
+    pitch - 2 (the halo columns)."""
+    import ctypes
+    lib = dr.lib
+    lib.dRk_tensor_conv_describe.restype = ctypes.c_int
+    lib.dRk_tensor_conv_describe.argtypes = [ctypes.c_int] * 9 + [ctypes.POINTER(ctypes.c_int)] * 4
+    SWAP, PAIR = 4, 5
+    seen = set()
+    sizes = list(range(2, 66)) + [96, 111, 112, 113, 127, 128, 150, 223, 224, 225, 256, 300]
+    for w in sizes:
+        for h in (2, 3, 7, 8, 13, 14, 15, 16, 27, 28, 29, 30, 31, 32, 56, 57, 112, 224, w):
+            for cout, pool, n in ((64, 0, 64), (64, 1, 64), (128, 0, 64), (136, 1, 64), (512, 0, 64), (256, 0, 1)):
+                if pool and ((w | h) & 1):
+                    continue
+                vals = [ctypes.c_int(0) for _ in range(4)]
+                v = lib.dRk_tensor_conv_describe(n, w, h, 64, cout, 3, 3, pool, 148, *[ctypes.byref(x) for x in vals])
+                P, TW, TH, ncols = (x.value for x in vals)
+                if v == SWAP:
+                    assert P in (16, 30, 32) and 2 <= TW <= P - 2 and TH >= 4, (w, h, cout, pool, P, TW, TH)
+                    assert ncols == P * TH and ncols % 16 == 0 and ncols <= 256
+                    assert P != 16 or ncols % 32 == 0
+                    assert not pool or TH % 2 == 0
+                    assert ncols + 2 * P + 2 <= 304
+                    seen.add((SWAP, P))
+                elif v == PAIR:
+                    assert cout <= 64 and (P, TW, TH) in ((16, 14, 16), (30, 28, 8)) and ncols <= 256
+                    seen.add((PAIR, P))
+    assert {(SWAP, 16), (SWAP, 30), (SWAP, 32), (PAIR, 16), (PAIR, 30)} <= seen
