@@ -1106,6 +1106,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     dRk_TensorConvPlan *pl = (dRk_TensorConvPlan *)calloc(1, sizeof(dRk_TensorConvPlan));
+    if (!pl) return NULL;
     UmmaParams &p = pl->p;
     pl->in = in; pl->wT = wT; pl->sms = sms;
     const int variant = pick_variant(W, H, Cin, Cout, kw, kh);
@@ -1303,6 +1304,7 @@ extern "C" dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wT
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     dRk_TensorFcPlan *fp = (dRk_TensorFcPlan *)calloc(1, sizeof(dRk_TensorFcPlan));
+    if (!fp) return NULL;
     dRk_TensorConvPlan *pl = &fp->conv;
     UmmaParams &p = pl->p;
     p.n = n; p.W = 1; p.H = 1; p.Cin = Nin; p.CinPad = Nin; p.Cout = Nout;
