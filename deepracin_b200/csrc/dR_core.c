@@ -353,10 +353,22 @@ gboolean dR_estimateAndAllocateBuffers(dR_Graph *net)
             l->outputBuf = l->act;
         }
 
-        for (dR_ListElement *p = l->previous_layers->first; p; p = p->next) {
+        /* A Slice that a fused Concat evaluates keeps its source alive: the gather kernel reads the source when the
+           Concat runs, so the source is released by the Concat (below), after the Concat has taken its own buffer. */
+        gboolean deferRelease = l->fusedAway && l->type == tSlice;
+        for (dR_ListElement *p = l->previous_layers->first; p && !deferRelease; p = p->next) {
             dR_Node *prev = (dR_Node *)p->element;
             if (prev->type == tDataFeedNode || prev->output || prev->act == l->act) continue;
             if (--prev->act->numberOfDependencies == 0) dR_list_append(freeList, prev->act);
+        }
+        if (l->type == tConcat && ((dR_Concat_Data *)l->layer)->fusedGather) {
+            dR_Node *srcs[DRK_CHANNEL_MAP_MAX];
+            gint ns = dR_concat_gatherSources(l, srcs, DRK_CHANNEL_MAP_MAX);
+            for (gint i = 0; i < ns; i++) {
+                dR_Node *prev = srcs[i];
+                if (prev->type == tDataFeedNode || prev->output || prev->act == l->act) continue;
+                if (--prev->act->numberOfDependencies == 0) dR_list_append(freeList, prev->act);
+            }
         }
         if (!l->allocateBuffers(net, l)) { g_print("Buffer allocation failed for Layer %d! \n", l->layerID); return FALSE; }
     }

@@ -227,6 +227,20 @@ gboolean dR_concat_planGather(dR_Node *layer)
     return TRUE;
 }
 
+/* The source node of every Slice chain of a fused Concat, one entry per Concat input (a source feeding several
+ * chains appears once per chain, as it does in the Slices' dependency counts).  Returns the number of entries. */
+gint dR_concat_gatherSources(dR_Node *layer, dR_Node **srcs, gint maxSrcs)
+{
+    dR_Concat_Data *d = (dR_Concat_Data *)layer->layer;
+    gint n = 0;
+    for (gint i = 0; i < d->n && n < maxSrcs; i++) {
+        gint ops[4], nops; gfloat sc[4];
+        dR_Node *sl = gatherChain(dR_nthInput(layer, i), ops, sc, &nops);
+        if (sl) srcs[n++] = dR_firstInput(sl);
+    }
+    return n;
+}
+
 /* The gather of a fused Concat as an affine per-channel map of ONE source tensor, if it is that simple: at most four
  * channels, every chain from the same source, at most one scalar op per chain and that op exact as one FMA
  * (AddS, SubS, MulS).  A few-channel first convolution can then evaluate it while it reads its input. */

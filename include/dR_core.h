@@ -33,6 +33,7 @@ gboolean dR_fillBuffers(dR_Graph *net);
 gboolean dR_planFusion(dR_Graph *net);
 /* TRUE if every input of this channel-wise Concat is a Slice -> scalar-op chain that one gather kernel can evaluate */
 gboolean dR_concat_planGather(dR_Node *concat);
+gint dR_concat_gatherSources(dR_Node *concat, dR_Node **srcs, gint maxSrcs);
 gboolean dR_concat_gatherAsInputMap(dR_Node *concat, dR_Node **src, gint ch[4], gfloat scale[4], gfloat shift[4]);
 void dR_cleanupBuffers(dR_Graph *net);
 void dR_cleanupNet(dR_Graph *net);

@@ -197,3 +197,22 @@ def test_full_size_vgg16_fp32_matches_reference_kernels_and_tf32_agrees(tmp_path
     assert rel_err(res["fp32"][:1], ref) <= 5e-4                 # 16 layers, each within 1e-4
     assert rel_err(res["tf32"], res["fp32"]) <= 1e-2             # 13 TF32 layers deep; per layer 3e-3
     assert np.array_equal(res["tf32"].argmax(1), res["fp32"].argmax(1))
+
+
+@pytest.mark.parametrize("fuse", [True, False])
+def test_channel_reorder_in_the_middle_of_a_network(fuse):
+    """conv -> {Slice(ch 2..3), Slice(ch 0..1) - 0.5} -> Concat -> conv: with fusion on the Concat's gather kernel reads the
+    first convolution's output directly, so that buffer must stay alive (and distinct from the Concat's) until then."""
+    x, w1, b1 = cases.conv_case("reorder_c1", 3, 3, 4, 9, 11, 3)
+    _, w2, b2 = cases.conv_case("reorder_c2", 1, 4, 6, 9, 11, 3)
+    a = oracle.conv2d(x, w1, b1, (1, 1), 1)
+    mid = np.concatenate([a[:, 2:4], a[:, 0:2] - np.float32(0.5)], axis=1)
+    ref = oracle.conv2d(mid, w2, b2, (1, 1), 1)
+
+    def build(g, f):
+        c1 = conv_build(w1, b1, 1, 1)(g, f)
+        hi = dr.Slice(c1, (2, 0, 0), (2, 9, 11))
+        lo = dr.Sub_Scalar(dr.Slice(c1, (0, 0, 0), (2, 9, 11)), 0.5)
+        return conv_build(w2, b2, 1, 1)(g, [dr.Concat([hi, lo], 0)])
+    (got,) = run_graph(build, [x], fuse=fuse)
+    assert rel_err(got, ref) <= 2 * TOL_FP32

@@ -272,3 +272,23 @@ def test_tensor_planner_geometries_respect_the_kernels_limits():
                     assert cout <= 64 and (P, TW, TH) in ((16, 14, 16), (30, 28, 8)) and ncols <= 256
                     seen.add((PAIR, P))
     assert {(SWAP, 16), (SWAP, 30), (SWAP, 32), (PAIR, 16), (PAIR, 30)} <= seen
+
+
+def test_fused_concat_gather_keeps_its_source_alive():
+    """A Slice -> Concat channel reorder in the middle of a network is evaluated by the Concat's gather kernel, which reads
+    the Slices' source: the planner must not hand the source's buffer to the Concat (or to anything scheduled in between)."""
+    with dr.Environment() as env:
+        g = env.create_graph("HWC")
+        r = np.random.default_rng(1)
+        x = dr.feed_node(g, [8, 8, 3])
+        c1 = dr.Conv2d(x, [3, 3, 3, 4], [1, 1, 1, 1], "relu", r.standard_normal((3, 3, 3, 4)).astype(np.float32), np.zeros(4, np.float32))
+        s1 = dr.Slice(c1, (0, 0, 2), (8, 8, 2))
+        s0 = dr.Slice(c1, (0, 0, 0), (8, 8, 2))
+        cat = dr.Concat([s1, s0], 2)
+        c2 = dr.Conv2d(cat, [3, 3, 4, 4], [1, 1, 1, 1], "relu", r.standard_normal((3, 3, 4, 4)).astype(np.float32), np.zeros(4, np.float32))
+        dr.mark_as_output(c2)
+        dry_prepare(g)
+        a = {k: dr.lib.dR_getNodeActAddress(v.ptr) for k, v in dict(c1=c1, s1=s1, s0=s0, cat=cat, c2=c2).items()}
+        assert a["cat"] != a["c1"]
+        assert a["s1"] != a["c1"] and a["s0"] != a["c1"]
+        assert a["c2"] != a["cat"]
