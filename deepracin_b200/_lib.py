@@ -78,6 +78,7 @@ _SIGS = {
     "dR_applyTimed": (c_double, [c_void_p, c_int]),
     "dR_getConvAlgo": (c_int, [c_void_p]),
     "dR_getConvTensor": (c_int, [c_void_p]),
+    "dR_getConvTensorKernel": (c_int, [c_void_p, POINTER(c_int)]),
     "dR_getNodeGpuMs": (c_double, [c_void_p]),
     "dR_getLaunchCount": (c_int, [c_void_p]),
     "dR_getDeviceStatus": (c_int, [c_void_p]),

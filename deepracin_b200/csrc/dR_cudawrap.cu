@@ -30,6 +30,7 @@ extern "C" gboolean dR_clInit(dR_Graph *net)
 {
     dR_ClConfig *c = net->clConfig;
     int count = 0;
+    if (net->config->dryRun) return TRUE;       /* planning only: no device is touched */
     if (!check(net, cudaGetDeviceCount(&count), "cudaGetDeviceCount") || count == 0) {
         g_print("dR_initCL: no CUDA device available\n");
         return FALSE;

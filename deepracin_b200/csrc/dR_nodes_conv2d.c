@@ -399,6 +399,15 @@ gboolean dR_conv2d_autotune(dR_Graph *net)
     return TRUE;
 }
 
+gint dR_getConvTensorKernel(dR_Node *node, gint geom[4])
+{
+    geom[0] = geom[1] = geom[2] = geom[3] = 0;
+    if (!node || node->type != tConv2d) return -1;
+    dR_Conv2d_Data *c = (dR_Conv2d_Data *)node->layer;
+    if (!c->chosenTensor || !dev(c)) return 0;
+    return dRk_tensor_conv_plan_describe(dev(c)->plan, &geom[0], &geom[1], &geom[2], &geom[3]);
+}
+
 gboolean dR_conv2d_cleanupBuffers(dR_Graph *net, dR_Node *layer)
 {
     dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;

@@ -1206,6 +1206,19 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     return pl;
 }
 
+/* The kernel and block geometry of a built plan, in the numbering of dRk_tensor_conv_describe. */
+extern "C" int dRk_tensor_conv_plan_describe(const dRk_TensorConvPlan *pl, int *P, int *TW, int *TH, int *ncols)
+{
+    *P = *TW = *TH = *ncols = 0;
+    if (!pl) return VAR_NONE;
+    if (pl->first) return VAR_FIRST;
+    if (pl->p.S == 0) return VAR_FLAT;
+    *TW = pl->p.TW; *TH = pl->p.TH;
+    if (pl->pair || pl->swap) { *P = pl->p.P; *ncols = pl->p.ncols; return pl->pair ? VAR_PAIR : VAR_SWAP; }
+    if (pl->halo) { *P = HALO_P; return VAR_HALO; }
+    return VAR_PLAIN;
+}
+
 extern "C" int dRk_tensor_conv_set_input_map(dRk_TensorConvPlan *pl, int ldi, const int *ch, const float *scale, const float *shift)
 {
     if (!pl || !pl->first || !ch || !scale || !shift || ldi < pl->p.Cin) return -1;

@@ -38,6 +38,9 @@ gdouble dR_applyTimed(dR_Graph *net, gint iterations);
 /* Kernel family / arithmetic a prepared convolution node runs (dR_ConvAlgo, 0/1). */
 gint dR_getConvAlgo(dR_Node *node);
 gint dR_getConvTensor(dR_Node *node);
+/* The tensor-core kernel a convolution node's launches run once it has been applied (numbering and geometry of
+ * dRk_tensor_conv_describe: geom = {pitch, valid pixels per block row, block rows, MMA columns}); 0 if it runs an FP32 kernel. */
+gint dR_getConvTensorKernel(dR_Node *node, gint geom[4]);
 /* Last per-node GPU time in ms (profilingGPU runs), and number of kernels one dR_apply launches. */
 gdouble dR_getNodeGpuMs(dR_Node *node);
 gint dR_getLaunchCount(dR_Graph *net);

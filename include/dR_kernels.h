@@ -147,6 +147,8 @@ int dRk_tensor_conv_set_input_map(dRk_TensorConvPlan *plan, int ldi, const int *
  * first layer; 0 = shape or pooling not supported) and block geometry a plan for this layer on a GPU with `sms` SMs would use. */
 int dRk_tensor_conv_describe(int n, int W, int H, int Cin, int Cout, int kw, int kh, int fuse_pool2, int sms,
                              int *P, int *TW, int *TH, int *ncols);
+/* The same for a plan that was built: what its launches actually run. */
+int dRk_tensor_conv_plan_describe(const dRk_TensorConvPlan *plan, int *P, int *TW, int *TH, int *ncols);
 int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *plan);
 void dRk_tensor_conv_free(dRk_TensorConvPlan *plan);
 

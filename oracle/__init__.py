@@ -81,6 +81,12 @@ def staged_squeezenet_dir():
     return d if os.path.exists(os.path.join(d, "graph.dr")) else None
 
 
+def staged_reference_python_module():
+    """Path of the reference's Python ctypes module template (python/deepracin/__init__.py.in) if it was staged."""
+    p = os.path.join(_HERE, "_ref", "python", "__init__.py.in")
+    return p if os.path.exists(p) else None
+
+
 # --------------------------------------------------------------------------- restatement leg
 def conv2d(x, w, b, stride=(1, 1), act=1):
     x, w, b = _c(x), _c(w), _c(b)

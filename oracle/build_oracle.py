@@ -2,10 +2,13 @@
 
 * ``oracle/libdroracle.so``   : the plain-C restatement (``dr_oracle.c``).
 * ``oracle/_ref/libdrref.so`` : the reference's own kernel sources compiled as C through
-  ``ref_shim/`` -- built only where a reference checkout is present (``DR_REF_DIR`` or the
-  default location); the kernel files are compiled where they lie and are never copied.
+  ``ref_shim/`` -- built only where a reference checkout is present (``DR_REF_DIR``, or a folder
+  named ``reference`` beside this repository); the kernel files are compiled where they lie and
+  are never copied.
 * ``oracle/_ref/squeezenet/`` : the reference's pretrained SqueezeNet model folder and its two
   example images (as raw float32 W x H x 3 arrays), staged for the known-answer test.
+* ``oracle/_ref/python/__init__.py.in`` : the reference's Python ctypes module, staged so that the tests can
+  render it against ``libdeepracin.so`` and drive the library through the reference's own binding.
 
 Run ``python oracle/build_oracle.py``.  Building the checker is not using it.
 """
@@ -15,7 +18,7 @@ import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF_DIR = os.environ.get("DR_REF_DIR", "/root/reference")
+REF_DIR = os.environ.get("DR_REF_DIR") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
 CFLAGS = ["-O3", "-march=native", "-fopenmp", "-fPIC", "-shared", "-fvisibility=hidden"]
 
 
@@ -76,6 +79,10 @@ def stage_reference_fixtures():
                 a.tofile(target)
     except ImportError:
         pass
+    pysrc = os.path.join(REF_DIR, "python", "deepracin", "__init__.py.in")
+    if os.path.exists(pysrc):
+        os.makedirs(os.path.join(HERE, "_ref", "python"), exist_ok=True)
+        shutil.copyfile(pysrc, os.path.join(HERE, "_ref", "python", "__init__.py.in"))
     return dst
 
 
