@@ -286,6 +286,13 @@ static dR_Node *elisionTarget(dR_Node *l)
     return l->elided ? (dR_Node *)l->next_layers->first->element : NULL;
 }
 
+/* A caller-owned output buffer (dR_setPreexistingOutputBuffer) whose layout is the node's own N-HWC layout is written by the
+ * node's kernels directly: no stream buffer, no conversion kernel. */
+static gboolean writesIntoCallersBuffer(dR_Graph *net, dR_Node *l)
+{
+    return l->output && l->outputBuf && l->outputBuf->outputBuf && !l->elided && layoutsCoincide(net, l->oshape);
+}
+
 /*
  * Walks the schedule; every node takes a free stream buffer (or a new one), grows it to
  * its need, and releases the buffers of predecessors whose last consumer it was.  Buffers of
@@ -322,14 +329,14 @@ gboolean dR_estimateAndAllocateBuffers(dR_Graph *net)
         gint req = l->getRequiredOutputBufferSize(l);
         if (target) {
             if (!target->act) {
-                target->act = takeStreamBuffer(all, freeList);
+                target->act = writesIntoCallersBuffer(net, target) ? target->outputBuf : takeStreamBuffer(all, freeList);
                 target->act->numberOfDependencies = target->next_layers->length;
                 gint treq = target->getRequiredOutputBufferSize(target);
                 if (target->act->size < treq) target->act->size = treq;
             }
             l->act = target->act;
         } else if (!l->act) {
-            l->act = takeStreamBuffer(all, freeList);
+            l->act = writesIntoCallersBuffer(net, l) ? l->outputBuf : takeStreamBuffer(all, freeList);
             l->act->numberOfDependencies = l->next_layers->length;
             if (l->act->size < req) l->act->size = req;
         }

@@ -10,6 +10,7 @@
 #include <stdio.h>
 #include "dR_core.h"
 #include "dR_b200.h"
+#include "dR_kernels.h"
 
 static cudaStream_t streamOf(dR_Graph *net) { return (cudaStream_t)net->clConfig->clCommandQueue; }
 
@@ -270,6 +271,22 @@ extern "C" gint dR_getDeviceStatus(dR_Graph *net)
     if (st[0]) dR_zeroBuffer(net, net->statusWord, 4);
     net->deviceStatus = st[0];
     return st[0];
+}
+
+extern "C" gboolean dR_probeBoundedWait(dR_Graph *net, gint limitMicroseconds, gint result[3])
+{
+    result[0] = result[1] = result[2] = -1;
+    if (!net->prepared || net->config->dryRun || !net->statusWord || limitMicroseconds <= 0 || limitMicroseconds > 1000000) return FALSE;
+    if (!bindDevice(net)) return FALSE;
+    int khz = 2000000;                                  /* the limit counts SM clocks: use the device's maximum rate */
+    cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, (int)net->clConfig->clDeviceNumber);
+    cl_mem res = NULL;
+    if (!dR_createFloatBufferL(net, &res, 4)) return FALSE;
+    const int rc = dRk_bounded_wait_probe(net->clConfig->clCommandQueue, (int *)net->statusWord, (long long)limitMicroseconds * (khz / 1000), (int *)res);
+    gboolean ok = check(net, (cudaError_t)rc, "bounded-wait probe") && dR_finish(net);
+    if (ok) dR_downloadArray(net, (gchar *)"", &res, 0, 3 * sizeof(int), result);
+    dR_clMemoryBufferCleanup(net, res);
+    return ok;
 }
 
 /* --------------------------------------------------------------- double-buffered feeding */

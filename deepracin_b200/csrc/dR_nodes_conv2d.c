@@ -21,6 +21,9 @@ typedef struct {
     gfloat mapScale[4], mapShift[4];
     const float *planSrc;           /* buffers the plan's tensor maps were encoded for */
     float *planDst;
+    dRk_TensorConvPlan *planAlt;    /* the plan for the other buffer pair when the input alternates (double-buffered feeding) */
+    const float *planAltSrc;
+    float *planAltDst;
 } dR_ConvDevice;
 
 static dR_ConvDevice *dev(dR_Conv2d_Data *c) { return (dR_ConvDevice *)c->tmaDescs; }
@@ -330,7 +333,14 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
                                                          c->shape.s2, c->shape.s3, act, in->act_cstride, layer->act_cstride, layer->act_coffset);
         break;
     case DR_CONV_TENSOR:
-        if (d->plan && (d->planSrc != src || d->planDst != dst)) { dRk_tensor_conv_free(d->plan); d->plan = NULL; }     /* buffers moved (alternating feed buffers) */
+        if (d->plan && (d->planSrc != src || d->planDst != dst)) {
+            /* buffers moved (alternating feed buffers, a caller's new feed buffer): keep this plan aside and take the one built
+               for these buffers if there is one; a third pair replaces the older of the two */
+            dRk_TensorConvPlan *tp = d->plan; const float *ts = d->planSrc; float *td = d->planDst;
+            d->plan = d->planAlt; d->planSrc = d->planAltSrc; d->planDst = d->planAltDst;
+            d->planAlt = tp; d->planAltSrc = ts; d->planAltDst = td;
+            if (d->plan && (d->planSrc != src || d->planDst != dst)) { dRk_tensor_conv_free(d->plan); d->plan = NULL; }
+        }
         if (!d->plan) {
             d->planSrc = src; d->planDst = dst;
             d->plan = dRk_tensor_conv_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR], bias, dst, n, W, H, c->shape.s2, c->shape.s3,
@@ -416,6 +426,7 @@ gboolean dR_conv2d_cleanupBuffers(dR_Graph *net, dR_Node *layer)
     for (gint a = 0; a < 5; a++) if (d->wbuf[a]) { ret &= dR_clMemoryBufferCleanup(net, d->wbuf[a]); d->wbuf[a] = NULL; }
     if (c->biasBuf) { ret &= dR_clMemoryBufferCleanup(net, c->biasBuf); c->biasBuf = NULL; }
     if (d->plan) { dRk_tensor_conv_free(d->plan); d->plan = NULL; }
+    if (d->planAlt) { dRk_tensor_conv_free(d->planAlt); d->planAlt = NULL; }
     c->weightsBuf = NULL;
     return ret;
 }

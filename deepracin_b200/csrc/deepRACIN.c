@@ -82,8 +82,10 @@ gboolean dR_setDataFeedNodeBuffer(dR_Graph *net, dR_Node *node, cl_mem *buf)
         return FALSE;
     }
     if (net->prepared) {
-        /* same handler, new pointer: allowed between applies */
+        /* same handler, new pointer: allowed between applies.  A captured CUDA graph holds the old address in its
+           kernel arguments and tensor maps, so it is dropped here and captured again by the next dR_apply. */
         node->outputBuf->bufptr = buf;
+        dR_captureDestroy(net);
         return TRUE;
     }
     dR_DataFeedNode_Data *d = (dR_DataFeedNode_Data *)node->layer;
@@ -164,7 +166,19 @@ gboolean dR_prepare(dR_Graph *net)
     return TRUE;
 }
 
-static gboolean launchSchedule(dR_Graph *net)
+/* The device addresses a captured schedule has baked in: every feed and output interface buffer.  A caller may replace
+ * the pointer behind a handler between applies (its own cl_mem variable); a replay must then not use the old capture. */
+static size_t interfaceKey(dR_Graph *net)
+{
+    size_t key = 1469598103934665603ull;
+    for (dR_ListElement *e = net->feed_layers->first; e; e = e->next)
+        key = (key ^ (size_t)*((dR_Node *)e->element)->outputBuf->bufptr) * 1099511628211ull;
+    for (dR_ListElement *e = net->output_layers->first; e; e = e->next)
+        key = (key ^ (size_t)*((dR_Node *)e->element)->outputBuf->bufptr) * 1099511628211ull;
+    return key;
+}
+
+static gboolean launchSchedule(dR_Graph *net, gboolean capturing)
 {
     for (dR_ListElement *e = net->feed_layers->first; e; e = e->next) {
         dR_Node *f = (dR_Node *)e->element;
@@ -182,7 +196,7 @@ static gboolean launchSchedule(dR_Graph *net)
                                                     net->config->batchSize, l->oshape.s0, l->oshape.s1, l->oshape.s2);
             if (!dR_finishCLKernel(net, "deepRACIN:outputLayout")) return FALSE;
         }
-        if (l->layerID == net->debugLayer && net->config->batchSize == 1)
+        if (l->layerID == net->debugLayer && net->config->batchSize == 1 && !capturing)     /* a blocking download would end the capture */
             dR_downloadArray(net, "", l->outputBuf->bufptr, 0, (size_t)l->oshape.s0 * l->oshape.s1 * sizeof(cl_float), net->hostDebugBuffer);
     }
     return TRUE;
@@ -197,15 +211,18 @@ gboolean dR_apply(dR_Graph *net)
     if (net->config->debugInfo) g_print("Applying graph...\n");
     if (net->config->profilingCPU) { t0 = wallMs(); net->config->totalNodeCPUTime = 0.0; }
     if (net->config->useCudaGraph && !net->config->profilingGPU) {
+        const size_t key = interfaceKey(net);
+        if (net->graphExec && net->captureKey != key) dR_captureDestroy(net);
         if (!net->graphExec) {
             if (!dR_captureBegin(net)) return FALSE;
-            gboolean ok = launchSchedule(net);
+            gboolean ok = launchSchedule(net, TRUE);
             if (!dR_captureEnd(net) || !ok) return FALSE;
+            net->captureKey = key;
         }
         if (!dR_captureLaunch(net)) return FALSE;
     } else {
         if (net->config->feedOverlap && !dR_feedOverlapBeforeApply(net)) return FALSE;
-        if (!launchSchedule(net)) return FALSE;
+        if (!launchSchedule(net, FALSE)) return FALSE;
         if (net->config->feedOverlap && !dR_feedOverlapAfterApply(net)) return FALSE;
     }
     if (net->config->profilingGPU) {

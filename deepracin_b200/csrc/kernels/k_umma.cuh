@@ -56,14 +56,14 @@ __device__ __forceinline__ uint32_t mbar_try(uint32_t bar, uint32_t parity)
     return ok;
 }
 /* bounded wait, slow path; false = aborted (by this thread's timeout or by another role) */
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code, long long limit)
 {
     const long long t0 = clock64();
     for (;;) {
         for (int i = 0; i < 64; i++)
             if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
-        if (clock64() - t0 > WAIT_CYCLES) {
+        if (clock64() - t0 > limit) {
             *abort_flag = 1;
             if (status) atomicExch(status, code);
             return false;
@@ -72,10 +72,19 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
 }
 /* The first probe is inline: the MMA issuer can only run about two instructions ahead of the tensor pipe, so a function
  * call between two groups of MMAs (measured: ~45 clocks per group of four) shows up as idle pipe time. */
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
+                                          long long limit = WAIT_CYCLES)
 {
     if (mbar_try(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, status, code);
+    return mbar_wait_slow(bar, parity, abort_flag, status, code, limit);
+}
+/* The same for a whole (converged) warp: every lane waits, and all lanes get the same answer.  A lane whose probe succeeded
+ * just as another role raised the abort flag must not go on alone into warp-wide instructions (tcgen05.ld.sync.aligned,
+ * __syncwarp, shuffles) that the rest of its warp skips. */
+__device__ __forceinline__ bool mbar_wait_warp(uint32_t bar, uint32_t parity, volatile int *abort_flag, int *status, int code,
+                                               long long limit = WAIT_CYCLES)
+{
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, status, code, limit));
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int c0, int c1, uint32_t bar)
 {
@@ -105,6 +114,14 @@ __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint6
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+/* Abort path of an MMA issuer: instructions it issued may still be running when it gives up.  One commit on a barrier of
+ * its own and a bounded wait for it let them finish before the CTA frees its TMEM. */
+__device__ __forceinline__ void umma_drain(uint32_t bar)
+{
+    umma_commit(bar);
+    const long long t0 = clock64();
+    while (!mbar_try(bar, 0) && clock64() - t0 < WAIT_CYCLES) { }
 }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }

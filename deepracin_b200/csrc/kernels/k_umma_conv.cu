@@ -55,13 +55,14 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;                       /* swizzled tiles need 1024-byte alignment */
     uint8_t *gen = smem_raw + (base - raw);
-    const uint32_t bars = base + C::STAGES * C::STAGE_BYTES;            /* full[S], empty[S], tfull[2], tempty[2] */
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 4));
+    const uint32_t bars = base + C::STAGES * C::STAGE_BYTES;            /* full[S], empty[S], tfull[2], tempty[2], drain */
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + C::STAGES * C::STAGE_BYTES + 8 * (2 * C::STAGES + 5));
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (C::STAGES + s); };
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + a); };
     auto tempty_bar = [&](int a) { return bars + 8u * (2 * C::STAGES + 2 + a); };
+    const uint32_t drain_bar = bars + 8u * (2 * C::STAGES + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles * p.n_tiles * p.ksplit;
@@ -69,6 +70,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; s++) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -176,6 +178,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                 }
                 if (ok) umma_commit(tfull_bar(acc));
             }
+            if (!ok) umma_drain(drain_bar);
         }
     } else {
         /* ------------------------------------------------ epilogue warps (TMEM lanes 32*(warp%4) ..) */
@@ -232,7 +235,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                 }
             }
             float *stg = reinterpret_cast<float *>(gen + C::STAGES * C::STAGE_BYTES + 256) + (warp - 2) * 32 * C::STG_PITCH;
-            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+            if (!mbar_wait_warp(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
@@ -341,7 +344,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     uint8_t *gen = smem_raw + (base - raw);
     const uint32_t a_base = base, b_base = base + C::NA * HALO_A_SLOT;
     const uint32_t bars = b_base + C::NB * C::B_STAGE_BYTES;
-    constexpr int NBARS = 2 * C::NA + 2 * C::NB + 4;
+    constexpr int NBARS = 2 * C::NA + 2 * C::NB + 5;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + C::NA * HALO_A_SLOT + C::NB * C::B_STAGE_BYTES + 8 * NBARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     auto afull = [&](int s) { return bars + 8u * s; };
@@ -350,6 +353,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
     auto bempty = [&](int s) { return bars + 8u * (2 * C::NA + C::NB + s); };
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * C::NA + 2 * C::NB + a); };
     auto tempty_bar = [&](int a) { return bars + 8u * (2 * C::NA + 2 * C::NB + 2 + a); };
+    const uint32_t drain_bar = bars + 8u * (2 * C::NA + 2 * C::NB + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles * p.n_tiles;
@@ -359,6 +363,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
         for (int s = 0; s < C::NA; s++) { mbar_init(afull(s), 1); mbar_init(aempty(s), 1); }
         for (int s = 0; s < C::NB; s++) { mbar_init(bfull(s), 1); mbar_init(bempty(s), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
+        mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -446,6 +451,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                 }
                 if (ok) umma_commit(tfull_bar(acc));
             }
+            if (!ok) umma_drain(drain_bar);
         }
     } else {
         const int quarter = warp & 3;
@@ -485,7 +491,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
                 }
             }
             float *stg = reinterpret_cast<float *>(gen + C::NA * HALO_A_SLOT + C::NB * C::B_STAGE_BYTES + 512) + (warp - 2) * 32 * C::STG_PITCH;
-            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+            if (!mbar_wait_warp(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
 #pragma unroll 1
@@ -580,7 +586,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     uint8_t *gen = smem_raw + (base - raw);
     const uint32_t h_base = base, w_base = base + SWAP_NH * SWAP_HALO_SLOT;
     const uint32_t bars = w_base + SWAP_NW * SWAP_W_BYTES;
-    constexpr int NBARS = 2 * SWAP_NH + 2 * SWAP_NW + 4;
+    constexpr int NBARS = 2 * SWAP_NH + 2 * SWAP_NW + 5;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + SWAP_NH * SWAP_HALO_SLOT + SWAP_NW * SWAP_W_BYTES + 8 * NBARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     auto hfull = [&](int s) { return bars + 8u * s; };
@@ -589,6 +595,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     auto wempty = [&](int s) { return bars + 8u * (2 * SWAP_NH + SWAP_NW + s); };
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + a); };
     auto tempty_bar = [&](int a) { return bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + 2 + a); };
+    const uint32_t drain_bar = bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles * p.n_tiles;
@@ -600,6 +607,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         for (int s = 0; s < SWAP_NH; s++) { mbar_init(hfull(s), 1); mbar_init(hempty(s), 1); }
         for (int s = 0; s < SWAP_NW; s++) { mbar_init(wfull(s), 1); mbar_init(wempty(s), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), SWAP_EPI_WARPS); }
+        mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -687,6 +695,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                 }
                 if (ok) umma_commit(tfull_bar(acc));
             }
+            if (!ok) umma_drain(drain_bar);
         }
     } else {
         /* eight epilogue warps: two per 32-lane quarter of TMEM, each taking half of the 256 pixel columns (with four, the
@@ -706,7 +715,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             /* ReLU = clamp to [0, FLT_MAX]; linear = clamp to [-inf, +inf] (a no-op): same two instructions either way */
             const float lo = p.act ? 0.0f : -INFINITY, hi = p.act ? FLT_MAX : INFINITY;
             float *obase = p.out + p.coff + ch;
-            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+            if (!mbar_wait_warp(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * SWAP_N);
 #pragma unroll 1

@@ -113,13 +113,14 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
     uint8_t *gen = smem_raw + (base - raw);
     const uint32_t a_base = base, b_base = base + C::A_BYTES;
     const uint32_t bars = b_base + C::NB * C::B_STAGE;
-    constexpr int NBARS = 2 * C::NB + 4;
+    constexpr int NBARS = 2 * C::NB + 5;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + C::A_BYTES + C::NB * C::B_STAGE + 8 * NBARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     auto bfull = [&](int s) { return bars + 8u * s; };
     auto bempty = [&](int s) { return bars + 8u * (C::NB + s); };
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * C::NB + a); };
     auto tempty_bar = [&](int a) { return bars + 8u * (2 * C::NB + 2 + a); };
+    const uint32_t drain_bar = bars + 8u * (2 * C::NB + 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long total_px = (long long)n * H * W;
@@ -137,6 +138,7 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::NB; s++) { mbar_init(bfull(s), FIRST_PROD_THREADS); mbar_init(bempty(s), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 2 * active_quarters); }
+        mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -172,11 +174,12 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
             int bs = 0;
             uint32_t bph = 0;
             int it = 0;
+            bool ok = true;
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, it++) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, status, 2)) break;
-                if (!mbar_wait(bfull(bs), bph, abort_flag, status, 3)) break;
+                if (!mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, status, 2)) { ok = false; break; }
+                if (!mbar_wait(bfull(bs), bph, abort_flag, status, 3)) { ok = false; break; }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * FIRST_N);
 #pragma unroll
@@ -192,6 +195,7 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
                 umma_commit(tfull_bar(acc));
                 if (++bs == C::NB) { bs = 0; bph ^= 1u; }
             }
+            if (!ok) umma_drain(drain_bar);
         }
     } else if (warp <= FIRST_EPI_WARPS) {
         const int quarter = warp & 3, half = (warp - 1) >> 2;
@@ -209,7 +213,7 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
                 for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, it++) {
                     const int acc = it & 1;
                     const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-                    if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, status, 4)) break;
+                    if (!mbar_wait_warp(tfull_bar(acc), acc_phase, abort_flag, status, 4)) break;
                     tc_fence_after();
                     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * FIRST_N + half * (FIRST_N / 2));
                     const long long f0 = (long long)t * FIRST_N + half * (FIRST_N / 2);
@@ -239,7 +243,7 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
             for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, it++) {
                 const int acc = it & 1;
                 const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
-                if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, status, 4)) break;
+                if (!mbar_wait_warp(tfull_bar(acc), acc_phase, abort_flag, status, 4)) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * FIRST_N + half * (FIRST_N / 2));
                 const long long g0 = (long long)t * TILE_PX + grp * FIRST_N + half * (FIRST_N / 2);

@@ -54,7 +54,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
     const uint32_t x_off = PAIR_NH * PAIR_PLANE_SLOT + PAIR_NW * PAIR_W_BYTES;
     float *xbuf = reinterpret_cast<float *>(gen + x_off);
     const uint32_t bars = base + x_off + PAIR_X_BYTES;
-    constexpr int NBARS = 2 * PAIR_NH + 2 * PAIR_NW + 4 + 8;
+    constexpr int NBARS = 2 * PAIR_NH + 2 * PAIR_NW + 4 + 8 + 1;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + x_off + PAIR_X_BYTES + 8 * NBARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     auto hfull = [&](int s) { return bars + 8u * s; };
@@ -65,6 +65,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
     auto tempty_bar = [&](int a) { return bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + 2 + a); };
     auto xfull = [&](int pr, int b) { return bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + 4 + pr * 4 + b); };
     auto xempty = [&](int pr, int b) { return bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + 4 + pr * 4 + 2 + b); };
+    const uint32_t drain_bar = bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + 4 + 8);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles;
@@ -78,6 +79,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
         for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), 4); }
         for (int pr = 0; pr < 2; pr++)
             for (int b = 0; b < 2; b++) { mbar_init(xfull(pr, b), 1); mbar_init(xempty(pr, b), 1); }
+        mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -175,6 +177,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
                 }
                 if (ok) umma_commit(tfull_bar(acc));
             }
+            if (!ok) umma_drain(drain_bar);
         }
     } else {
         const int quarter = warp & 3;
@@ -195,7 +198,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
             const int img = t / per, rem = t - img * per;
             const int tyi = rem / p.tiles_x, txi = rem - tyi * p.tiles_x;
             const int x0 = txi * p.TW;
-            if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
+            if (!mbar_wait_warp(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * PAIR_N);
             if (p.P != 16) {
@@ -213,13 +216,13 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
                         const uint32_t xph = (gc >> 1) & 1u;
                         float *xs = xb + b * PAIR_X_FLOATS + lane;
                         if (lower) {
-                            if (!mbar_wait(xempty(pr, b), xph ^ 1u, abort_flag, p.status, 7)) { ok = false; break; }
+                            if (!mbar_wait_warp(xempty(pr, b), xph ^ 1u, abort_flag, p.status, 7)) { ok = false; break; }
 #pragma unroll
                             for (int k = 0; k < 14; k++) xs[k * 32] = h[k];
                             __syncwarp();
                             if (lane == 0) mbar_arrive(xfull(pr, b));
                         } else {
-                            if (!mbar_wait(xfull(pr, b), xph, abort_flag, p.status, 8)) { ok = false; break; }
+                            if (!mbar_wait_warp(xfull(pr, b), xph, abort_flag, p.status, 8)) { ok = false; break; }
 #pragma unroll
                             for (int k = 0; k < 14; k++) h[k] = fmaxf(h[k], xs[k * 32]);
                             __syncwarp();
@@ -266,13 +269,13 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
                     const uint32_t xph = (gc >> 1) & 1u;
                     float *xs = xb + b * PAIR_X_FLOATS + lane;
                     if (lower) {
-                        if (!mbar_wait(xempty(pr, b), xph ^ 1u, abort_flag, p.status, 7)) { ok = false; break; }
+                        if (!mbar_wait_warp(xempty(pr, b), xph ^ 1u, abort_flag, p.status, 7)) { ok = false; break; }
 #pragma unroll
                         for (int k = 0; k < 14; k++) xs[k * 32] = h[k];
                         __syncwarp();
                         if (lane == 0) mbar_arrive(xfull(pr, b));
                     } else {
-                        if (!mbar_wait(xfull(pr, b), xph, abort_flag, p.status, 8)) { ok = false; break; }
+                        if (!mbar_wait_warp(xfull(pr, b), xph, abort_flag, p.status, 8)) { ok = false; break; }
 #pragma unroll
                         for (int k = 0; k < 14; k++) h[k] = fmaxf(h[k], xs[k * 32]);
                         __syncwarp();

@@ -46,6 +46,11 @@ gdouble dR_getNodeGpuMs(dR_Node *node);
 gint dR_getLaunchCount(dR_Graph *net);
 /* Non-zero if a kernel reported a device-side status (bounded wait ran out, ...) since the last call. */
 gint dR_getDeviceStatus(dR_Graph *net);
+/* Exercises the failure path of the tensor-core kernels without a failure: a one-CTA kernel waits at most
+ * `limitMicroseconds` (at the GPU's maximum clock) on a barrier nothing arrives at, gives up the way a stuck kernel
+ * would (code 9 in the graph's status word, read by dR_getDeviceStatus) and returns.  result as dRk_bounded_wait_probe.
+ * The graph must be prepared; blocks until the probe has finished. */
+gboolean dR_probeBoundedWait(dR_Graph *net, gint limitMicroseconds, gint result[3]);
 /* Double-buffered feeding: dR_feedDataAsync copies on a second stream into the feed node's other interface
  * buffer while the previous batch is still being computed; the next dR_apply waits for that copy and reads it.
  * Before dR_prepare; not combined with CUDA-graph replay or caller-supplied feed buffers. */

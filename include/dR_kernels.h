@@ -163,6 +163,13 @@ dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wT, const flo
 int dRk_tensor_fc_run(dRk_stream stream, dRk_TensorFcPlan *plan);
 void dRk_tensor_fc_free(dRk_TensorFcPlan *plan);
 
+/* Test support for the bounded waits of the tensor-core kernels (no counterpart in the reference, whose failure path is
+ * the return code of its OpenCL calls, src/dR_clwrap.c:874-883): one CTA waits at most `limit_cycles` SM clocks on a
+ * barrier nothing arrives at, through the kernels' own wait function; it then writes code 9 to `status`, as a kernel
+ * whose wait ran out does, and returns.  result (device int[3]): [0] outcome of that wait (0 = ran out), [1] outcome of
+ * a wait on a barrier that was arrived at (1), [2] how long the first wait took, in units of 1024 clocks. */
+int dRk_bounded_wait_probe(dRk_stream stream, int *status, long long limit_cycles, int *result);
+
 /* Number of kernel launches issued through this ABI by the calling thread since the last reset. */
 long dRk_launch_count(void);
 void dRk_launch_count_reset(void);

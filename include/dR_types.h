@@ -209,6 +209,7 @@ struct dR_Graph {
     cl_mem scratch;          /* shared per-apply scratch (Winograd transform domain, FC partials) */
     size_t scratchFloats;
     void *graphExec;         /* cudaGraphExec_t when useCudaGraph */
+    size_t captureKey;       /* hash of the feed / output buffer addresses the captured graph was recorded with */
     gint deviceStatus;       /* last non-zero status a kernel reported (bounded waits etc.) */
     cl_mem statusWord;       /* device int the tensor-core kernels write error codes to */
 };
