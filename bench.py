@@ -228,7 +228,7 @@ def measure_dropin(ctx, steps, warmup, batch=64, math="tf32"):
     dr, nets, lib = ctx.dr, ctx.nets, ctx.lib
     size = 224
     with dr.Environment(device=ctx.local) as env:
-        g = env.create_graph("CHW")
+        g = env.create_graph("HWC")                 # layout of the Python-side shapes only; the C interface stays [C][H][W]
         g.batch = batch
         g.math = math
         x, out = nets.vgg16(g, size=size)

@@ -196,8 +196,10 @@ def test_vgg16_batch64_every_layer_tf32_against_fp32_and_oracle():
                             ref = oracle.pool(ref, (2, 2, 1), (2, 2, 1), 0)
                         got = path[layer][i:i + 1]
                     assert rel_err(got, ref) <= tol, (layer, i, "fp32" if path is fp else "tf32")
-    # accumulated over the layers before it, each layer still sits inside the per-layer TF32 bound
-    assert max(worst.values()) <= TOL_TF32, worst
+    # accumulated over the layers before it, every layer output still sits inside the per-layer TF32 bound; the softmax
+    # exponentiates the class scores' differences, so the probabilities get the bound the whole-network tests use
+    assert max(v for k, v in worst.items() if k != "prob") <= TOL_TF32, worst
+    assert worst["prob"] <= 2e-2, worst
 
 
 def test_first_layer_at_batch64_against_oracle():
