@@ -31,8 +31,6 @@ def _compile(src, obj, verbose):
     cmd = [NVCC, *ARCH, *COMMON, "-c", src, "-o", obj]
     if src.endswith(".cu"):
         cmd += ["-std=c++17", "-Xptxas", "-v"] if verbose else ["-std=c++17"]
-    else:
-        cmd += ["-x", "c"] if False else []
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))
@@ -64,19 +62,5 @@ def build_library(force=False, verbose=False):
     return OUT
 
 
-def build_microbench():
-    """Standalone measurement programs under csrc/microbench (not part of the library); returns the binaries' paths."""
-    outs = []
-    for src in sorted(glob.glob(os.path.join(CSRC, "microbench", "*.cu"))):
-        exe = src[:-3]
-        r = subprocess.run([NVCC, *ARCH, "-O3", "-std=c++17", "-I", os.path.join(ROOT, "include"), "-o", exe, src], capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError("nvcc failed for %s:\n%s\n%s" % (src, r.stdout, r.stderr))
-        outs.append(exe)
-    return outs
-
-
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
-    if "--microbench" in sys.argv:
-        print("\n".join(build_microbench()))

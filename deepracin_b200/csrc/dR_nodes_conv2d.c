@@ -232,7 +232,7 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
     {
         dR_Node *in = dR_firstInput(layer);
         dR_Node *src = NULL;
-        if (c->chosenTensor && net->config->fuseGraph && !getenv("DRK_NO_INPUT_MAP") && is3x3s1(c) && c->shape.s2 <= 4 && in->type == tConcat && !in->output &&
+        if (c->chosenTensor && net->config->fuseGraph && !dRk_debug_switches()->no_input_map && is3x3s1(c) && c->shape.s2 <= 4 && in->type == tConcat && !in->output &&
             in->next_layers->length == 1 && dR_concat_gatherAsInputMap(in, &src, dev(c)->mapCh, dev(c)->mapScale, dev(c)->mapShift) &&
             src->type == tDataFeedNode /* feed buffers are never recycled by the buffer planner, so the source outlives the skipped nodes */) {
             guint seen = 0;                             /* the kernel wants a permutation of the source's first Cin channels */

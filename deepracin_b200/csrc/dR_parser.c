@@ -61,6 +61,31 @@ static gchar *nextLine(gchar **cursor)
     return p;
 }
 
+/* Floats that variable file `k` of a node must hold, from the node's parameters: Conv2D "act useBias kw kh Cin Cout ..."
+ * (src/dR_nodes_conv2d.c:153-162) has kw*kh*Cin*Cout weights and, with a bias, Cout more; FullyConnected "act useBias Nin
+ * Nout" (src/dR_nodes_fc.c:70-73) has Nin*Nout and Nout.  -1: the node type takes no variables this function knows; -2: the
+ * parameters themselves are unusable (non-positive or overflowing sizes).  setVariables copies exactly this many floats out of
+ * the file's buffer, so a shorter file would be read past its end. */
+static long long expectedVariableFloats(const char *desc, gchar **params, gint numParams, gint k)
+{
+    long long dims[4];
+    gint first, nd;
+    if (strcmp(desc, "Conv2D") == 0) { first = 2; nd = 4; }
+    else if (strcmp(desc, "FullyConnected") == 0) { first = 2; nd = 2; }
+    else return -1;
+    if (numParams < first + nd) return -2;
+    long long prod = 1;
+    for (gint i = 0; i < nd; i++) {
+        dims[i] = atoll(params[first + i]);
+        if (dims[i] <= 0 || dims[i] > 0x7fffffffLL) return -2;
+        prod *= dims[i];
+        if (prod > 0x7fffffffLL) return -2;
+    }
+    if (k == 0) return prod;
+    if (k == 1 && atoi(params[1])) return dims[nd - 1];
+    return -2;                                          /* more variable files than the node has variables */
+}
+
 dR_Node *dR_parseGraph(dR_Graph *net, gchar *path, dR_Node ***outnodes, gint *numnodes, dR_Node ***outfeednodes, gint *numfeednodes)
 {
     if (net->number_of_layers != 0) {
@@ -127,8 +152,14 @@ dR_Node *dR_parseGraph(dR_Graph *net, gchar *path, dR_Node ***outnodes, gint *nu
             size_t vlen = 0;
             variables[numVars] = (gfloat *)dR_file_get_contents(vp, &vlen);
             if (!variables[numVars]) { g_print("Error while opening variable file: %s\n", vp); g_free(vp); goto failvars; }
-            g_free(vp);
             numVars++;
+            const long long want = expectedVariableFloats(desc, params, numParams, numVars - 1);
+            if (want == -2 || (want >= 0 && (long long)vlen != want * (long long)sizeof(gfloat))) {
+                g_print("Parsing Error: variable file %s holds %zu bytes, node %d (%s) needs %lld floats\n", vp, vlen, id, desc, want);
+                g_free(vp);
+                goto failvars;
+            }
+            g_free(vp);
         }
         if (!net->config->silent && net->config->debugInfo)
             g_print("Found %s with id %d, %d params and %d variables\n", desc, id, numParams, numVars);

@@ -444,9 +444,25 @@ extern "C" int dRk_channel_map(dRk_stream s, const drk_ChannelMap *map, float *o
     return DRK_LAUNCH_RESULT();
 }
 
-int drk_dep_launch_enabled()
+/* The library's debug switches: environment variables for A/B timing of kernel variants, read once, the first time any part
+ * of the library asks (results stay within rounding order whatever they are set to):
+ *   DRK_NO_PAIR / DRK_NO_SWAP / DRK_NO_HALO  take the row-pair / transposed / halo tensor kernels out of the planner's choice
+ *                                            (the next of pair -> transposed -> halo -> plain is used)
+ *   DRK_NO_INPUT_MAP                         keep a Slice / scalar-op / Concat preamble as a kernel of its own
+ *   DRK_NO_DEP_LAUNCH                        launch every kernel in plain stream order (no programmatic dependent launch) */
+extern "C" const drk_DebugSwitches *dRk_debug_switches(void)
 {
-    static int on = -1;
-    if (on < 0) on = getenv("DRK_NO_DEP_LAUNCH") ? 0 : 1;
-    return on;
+    static drk_DebugSwitches sw;
+    static int read = 0;
+    if (!read) {
+        sw.no_pair = getenv("DRK_NO_PAIR") != NULL;
+        sw.no_swap = getenv("DRK_NO_SWAP") != NULL;
+        sw.no_halo = getenv("DRK_NO_HALO") != NULL;
+        sw.no_input_map = getenv("DRK_NO_INPUT_MAP") != NULL;
+        sw.no_dep_launch = getenv("DRK_NO_DEP_LAUNCH") != NULL;
+        read = 1;
+    }
+    return &sw;
 }
+
+int drk_dep_launch_enabled() { return !dRk_debug_switches()->no_dep_launch; }

@@ -942,16 +942,17 @@ static double swap_fill(int W, int H)
 }
 
 /* which kernel evaluates a layer shape; the packed-filter layout depends on it, so packing and planning both ask here.
- * The environment switches exist for A/B comparisons of the variants when profiling. */
+ * The debug switches (dRk_debug_switches) exist for A/B comparisons of the variants when profiling. */
 enum { VAR_NONE = 0, VAR_FLAT, VAR_PLAIN, VAR_HALO, VAR_SWAP, VAR_PAIR, VAR_FIRST };
 static int pick_variant(int W, int H, int Cin, int Cout, int kw, int kh)
 {
     if (!dRk_tensor_conv_supported(W, H, Cin, Cout, kw, kh)) return VAR_NONE;
     if (drk_umma_first_supported(Cin, Cout, kw, kh)) return VAR_FIRST;
     if (kw == 1) return VAR_FLAT;
-    const bool no_halo = getenv("DRK_NO_HALO") != NULL;
-    if (Cout <= 64 && H >= 2 && drk_umma_pair_fill(W, H) >= 0.5 && !getenv("DRK_NO_PAIR") && !no_halo) return VAR_PAIR;
-    if (Cout <= BM && swap_fill(W, H) >= 0.8 && !getenv("DRK_NO_SWAP") && !no_halo) return VAR_SWAP;
+    const drk_DebugSwitches *sw = dRk_debug_switches();
+    const bool no_halo = sw->no_halo;
+    if (Cout <= 64 && H >= 2 && drk_umma_pair_fill(W, H) >= 0.5 && !sw->no_pair && !no_halo) return VAR_PAIR;
+    if (Cout <= BM && swap_fill(W, H) >= 0.8 && !sw->no_swap && !no_halo) return VAR_SWAP;
     /* halo or transposed kernel: which of the two is settled per plan, when the batch is known (use_swap_kernel) */
     if ((halo_fill(W, H) >= 0.55 || swap_fill(W, H) >= 0.55) && !no_halo) return VAR_HALO;
     return VAR_PLAIN;
@@ -1016,14 +1017,11 @@ extern "C" int dRk_tensor_conv_pack_weights(const float *w, float *dst, int W, i
 static int use_swap_kernel(int variant, int n, int W, int H, int Cout, int pool, int sms)
 {
     int P, TW, TH;
-    if (getenv("DRK_NO_SWAP")) return 0;
+    if (dRk_debug_switches()->no_swap) return 0;
     const double fill = swap_geometry(W, H, pool ? 1 : 0, &P, &TW, &TH);
     if (fill <= 0.0) return 0;
     const long long tiles = (long long)n * ((W + TW - 1) / TW) * ((H + TH - 1) / TH) * ((Cout + BM - 1) / BM);
-    if (tiles >= sms) {
-        const double margin = getenv("DRK_SWAP_MARGIN") ? atof(getenv("DRK_SWAP_MARGIN")) : -0.01;     /* A/B comparisons when profiling */
-        return variant == VAR_SWAP || fill >= halo_fill(W, H) + margin;
-    }
+    if (tiles >= sms) return variant == VAR_SWAP || fill >= halo_fill(W, H) - 0.01;
     const double tx = (W + HALO_TW - 1) / HALO_TW, ty = (H + 15) / 16;
     return Cout <= BM && (double)W * H / (tx * ty * SWAP_N) >= 0.8;
 }
@@ -1035,7 +1033,6 @@ static int pick_bn(int Cout, long long m_tiles, int sms)
     int best = 64;
     double best_cost = 1e30;
     const int cand[3] = {256, 128, 64};
-    if (getenv("DRK_FORCE_BN")) return atoi(getenv("DRK_FORCE_BN"));    /* A/B comparisons when profiling */
     for (int i = 0; i < 3; i++) {
         const int bn = cand[i];
         const long long tiles = m_tiles * ((Cout + bn - 1) / bn);
@@ -1093,7 +1090,7 @@ extern "C" int dRk_tensor_conv_describe(int n, int W, int H, int Cin, int Cout, 
             v = VAR_SWAP;
             swap_geometry(W, H, fuse_pool2 ? 1 : 0, P, TW, TH);
             *ncols = *P * *TH;
-        } else if (halo_fill(W, H) >= 0.55 && !getenv("DRK_NO_HALO")) {
+        } else if (halo_fill(W, H) >= 0.55 && !dRk_debug_switches()->no_halo) {
             v = VAR_HALO;
             *P = HALO_P; *TW = HALO_TW; *TH = HALO_TH; *ncols = 0;
         } else {
@@ -1174,7 +1171,7 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
         const cuuint32_t box[4] = {BK, (cuuint32_t)p.P, (cuuint32_t)(p.TH + 2), 1};
         r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void *)in, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    } else if ((variant == VAR_HALO || variant == VAR_SWAP) && halo_fill(W, H) >= 0.55 && !getenv("DRK_NO_HALO")) {
+    } else if ((variant == VAR_HALO || variant == VAR_SWAP) && halo_fill(W, H) >= 0.55 && !dRk_debug_switches()->no_halo) {
         pl->halo = 1;
         p.TW = HALO_TW; p.TH = HALO_TH; p.S = 1;
         p.tiles_x = (W + HALO_TW - 1) / HALO_TW; p.tiles_y = (H + HALO_TH - 1) / HALO_TH;

@@ -170,6 +170,12 @@ void dRk_tensor_fc_free(dRk_TensorFcPlan *plan);
  * a wait on a barrier that was arrived at (1), [2] how long the first wait took, in units of 1024 clocks. */
 int dRk_bounded_wait_probe(dRk_stream stream, int *status, long long limit_cycles, int *result);
 
+/* Debug switches of the library (environment variables DRK_NO_PAIR, DRK_NO_SWAP, DRK_NO_HALO, DRK_NO_INPUT_MAP,
+ * DRK_NO_DEP_LAUNCH; read once per process): each takes one kernel variant or launch feature out of use so that two runs can
+ * be timed against each other.  None changes results beyond rounding order.  No counterpart in the reference. */
+typedef struct { int no_pair, no_swap, no_halo, no_input_map, no_dep_launch; } drk_DebugSwitches;
+const drk_DebugSwitches *dRk_debug_switches(void);
+
 /* Number of kernel launches issued through this ABI by the calling thread since the last reset. */
 long dRk_launch_count(void);
 void dRk_launch_count_reset(void);

@@ -215,6 +215,29 @@ def test_truncated_model_files_fail_cleanly(tmp_path):
             dr.load_graph(env.create_graph("HWC"), d)
 
 
+def test_variable_files_of_the_wrong_size_are_rejected(tmp_path):
+    """A .var file shorter (or longer) than the node's shape implies, and shape parameters that are not positive, must make
+    dR_loadGraph fail: setVariables copies prod(shape) floats out of the file's buffer."""
+    with dr.Environment() as env:
+        g, _ = small_net(env)
+        dr.save_graph(g, str(tmp_path))
+        d = str(tmp_path / "dr_graph_export")
+        good = open(os.path.join(d, "0.var"), "rb").read()
+        nodes, _ = dr.load_graph(env.create_graph("HWC"), d)
+        assert len(nodes) == 10
+        for bad in (good[:-4], good + b"\0\0\0\0", good[:8]):
+            open(os.path.join(d, "0.var"), "wb").write(bad)
+            with pytest.raises(RuntimeError):
+                dr.load_graph(env.create_graph("HWC"), d)
+        open(os.path.join(d, "0.var"), "wb").write(good)
+        text = open(os.path.join(d, "graph.dr")).read()
+        assert "params: 1 1 3 3 3 8 1 1 1 1" in text
+        for params in ("1 1 3 3 -3 8 1 1 1 1", "1 1 3 3 3 0 1 1 1 1", "1 1 70000 70000 3 8 1 1 1 1"):
+            open(os.path.join(d, "graph.dr"), "w").write(text.replace("params: 1 1 3 3 3 8 1 1 1 1", "params: " + params, 1))
+            with pytest.raises(RuntimeError):
+                dr.load_graph(env.create_graph("HWC"), d)
+
+
 def test_tensor_planner_picks_the_expected_kernels_and_geometries():
     """Planner introspection (no device): the kernel and block geometry per VGG-16 / SqueezeNet layer shape on a 148-SM GPU."""
     import ctypes
