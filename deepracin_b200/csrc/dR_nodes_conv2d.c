@@ -13,7 +13,10 @@
 #include "dR_nodes_pooling.h"
 
 typedef struct {
-    cl_mem wbuf[5];                 /* packed weights per dR_ConvAlgo */
+    cl_mem wbuf[DR_CONV_ALGOS];     /* packed weights per dR_ConvAlgo */
+    dRk_TensorWinogradPlan *wplan;  /* tensor-core Winograd: the batched GEMM's TMA descriptors for this layer's buffers */
+    const float *wplanSrc;
+    float *wplanDst, *wplanScratch;
     dRk_TensorConvPlan *plan;       /* tensor path: TMA descriptors for this layer's buffers */
     gint fusedPool;                 /* 1 / 2: the following 2x2/2 max / average pooling is evaluated in this node's epilogue */
     dR_Node *mapSrc;                /* few-channel first layer: the Slice/scalar-op/Concat preamble in front of it is evaluated by its gather; */
@@ -174,6 +177,8 @@ static gboolean algoLegal(dR_Node *layer, gint algo)
     case DR_CONV_WINOGRAD: return is3x3s1(c);
     case DR_CONV_ONEBYONE: return is1x1s1(c);
     case DR_CONV_TENSOR: return tensorLegal(layer);
+    case DR_CONV_TENSOR_WINOGRAD:
+        return is3x3s1(c) && tensorLegal(layer) && dRk_tensor_winograd_supported(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
     }
     return FALSE;
 }
@@ -206,11 +211,11 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
         want = DR_CONV_AUTO;    /* a graph-wide wish only applies where it is legal */
     }
     c->chosenAlgo = want != DR_CONV_AUTO ? want : staticRule(net, layer);
-    c->chosenTensor = c->chosenAlgo == DR_CONV_TENSOR;
+    c->chosenTensor = c->chosenAlgo == DR_CONV_TENSOR || c->chosenAlgo == DR_CONV_TENSOR_WINOGRAD;
     /* conv -> 2x2/2 max pool with no other reader: the tensor kernel's epilogue stores the pooled tensor
        directly into the pooling node's buffer and the pooling node launches nothing */
     dev(c)->fusedPool = 0;
-    if (c->chosenTensor && net->config->fuseGraph && is3x3s1(c) && !layer->output && !layer->elided && layer->next_layers->length == 1 &&
+    if (c->chosenAlgo == DR_CONV_TENSOR && net->config->fuseGraph && is3x3s1(c) && !layer->output && !layer->elided && layer->next_layers->length == 1 &&
         layer->oshape.s0 % 2 == 0 && layer->oshape.s1 % 2 == 0) {
         dR_Node *nx = (dR_Node *)layer->next_layers->first->element;
         if (nx->type == tPooling && nx->previous_layers->length == 1) {
@@ -232,7 +237,7 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
     {
         dR_Node *in = dR_firstInput(layer);
         dR_Node *src = NULL;
-        if (c->chosenTensor && net->config->fuseGraph && !dRk_debug_switches()->no_input_map && is3x3s1(c) && c->shape.s2 <= 4 && in->type == tConcat && !in->output &&
+        if (c->chosenAlgo == DR_CONV_TENSOR && net->config->fuseGraph && !dRk_debug_switches()->no_input_map && is3x3s1(c) && c->shape.s2 <= 4 && in->type == tConcat && !in->output &&
             in->next_layers->length == 1 && dR_concat_gatherAsInputMap(in, &src, dev(c)->mapCh, dev(c)->mapScale, dev(c)->mapShift) &&
             src->type == tDataFeedNode /* feed buffers are never recycled by the buffer planner, so the source outlives the skipped nodes */) {
             guint seen = 0;                             /* the kernel wants a permutation of the source's first Cin channels */
@@ -248,6 +253,11 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
     layer->scratchFloats = 0;
     if (c->chosenAlgo == DR_CONV_WINOGRAD || (net->config->autotune && is3x3s1(c)))
         layer->scratchFloats = dRk_winograd_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
+    if (c->chosenAlgo == DR_CONV_TENSOR_WINOGRAD ||
+        (net->config->autotune && net->config->mathMode == DR_MATH_TF32 && algoLegal(layer, DR_CONV_TENSOR_WINOGRAD))) {
+        const size_t s = dRk_tensor_winograd_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
+        if (s > layer->scratchFloats) layer->scratchFloats = s;
+    }
     return TRUE;
 }
 
@@ -270,6 +280,7 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
     size_t n = (size_t)kw * kh * I * O;
     if (algo == DR_CONV_WINOGRAD) n = (size_t)16 * I * O;
     if (algo == DR_CONV_TENSOR) n = dRk_tensor_conv_packed_floats(c->ishape.s0, c->ishape.s1, I, O, kw, kh);
+    if (algo == DR_CONV_TENSOR_WINOGRAD) n = dRk_tensor_winograd_packed_floats(I, O);
     if (n == 0) return FALSE;
     gfloat *p = (gfloat *)g_malloc0(n * sizeof(gfloat));
     if (algo == DR_CONV_DIRECT) {
@@ -281,6 +292,8 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
     } else if (algo == DR_CONV_TENSOR) {
         /* K-major rows per output channel; the exact layout belongs to the tensor kernel picked for this shape */
         if (dRk_tensor_conv_pack_weights(c->weights, p, c->ishape.s0, c->ishape.s1, I, O, kw, kh) != 0) { g_free(p); return FALSE; }
+    } else if (algo == DR_CONV_TENSOR_WINOGRAD) {
+        if (dRk_tensor_winograd_pack_weights(c->weights, p, I, O) != 0) { g_free(p); return FALSE; }
     } else {
         /* U = G g G^T with G = [[1,0,0],[.5,.5,.5],[.5,-.5,.5],[0,0,1]] (reference :1162-1240),
            stored [16][Cin][Cout] so that each of the 16 positions is one K x N matrix */
@@ -353,6 +366,16 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
         }
         net->clConfig->clError = dRk_tensor_conv_run(s, d->plan);
         break;
+    case DR_CONV_TENSOR_WINOGRAD:
+        if (d->wplan && (d->wplanSrc != src || d->wplanDst != dst || d->wplanScratch != (float *)net->scratch)) { dRk_tensor_winograd_free(d->wplan); d->wplan = NULL; }
+        if (!d->wplan) {
+            d->wplanSrc = src; d->wplanDst = dst; d->wplanScratch = (float *)net->scratch;
+            d->wplan = dRk_tensor_winograd_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR_WINOGRAD], bias, dst, (float *)net->scratch, n, W, H,
+                                                c->shape.s2, c->shape.s3, act, in->act_cstride, layer->act_cstride, layer->act_coffset, (int *)net->statusWord);
+            if (!d->wplan) { g_print("Conv2d Layer %d: tensor-core Winograd plan could not be built\n", layer->layerID); return FALSE; }
+        }
+        net->clConfig->clError = dRk_tensor_winograd_run(s, d->wplan);
+        break;
     default:
         return FALSE;
     }
@@ -384,9 +407,9 @@ gboolean dR_conv2d_autotune(dR_Graph *net)
         if (dev(c)->fusedPool || dev(c)->mapSrc) continue;     /* only the tensor kernel can store the pooled tensor / read through the channel map */
         gint best = c->chosenAlgo;
         gdouble bestMs = 1e30;
-        for (gint algo = DR_CONV_DIRECT; algo <= DR_CONV_TENSOR; algo++) {
+        for (gint algo = DR_CONV_DIRECT; algo < DR_CONV_ALGOS; algo++) {
             if (!algoLegal(layer, algo)) continue;
-            if (algo == DR_CONV_TENSOR && net->config->mathMode != DR_MATH_TF32) continue;
+            if ((algo == DR_CONV_TENSOR || algo == DR_CONV_TENSOR_WINOGRAD) && net->config->mathMode != DR_MATH_TF32) continue;
             if (algo == DR_CONV_ONEBYONE) continue;             /* same kernel as DIRECT for 1x1 */
             for (gint i = 0; i < 3; i++) if (!dR_conv2d_runVariant(net, layer, algo, 0)) return FALSE;
             dR_timerStart(net);
@@ -399,10 +422,10 @@ gboolean dR_conv2d_autotune(dR_Graph *net)
         }
         if (best == DR_CONV_DIRECT && is1x1s1(c)) best = DR_CONV_ONEBYONE;
         c->chosenAlgo = best;
-        c->chosenTensor = best == DR_CONV_TENSOR;
+        c->chosenTensor = best == DR_CONV_TENSOR || best == DR_CONV_TENSOR_WINOGRAD;
         c->weightsBuf = dev(c)->wbuf[best == DR_CONV_ONEBYONE ? DR_CONV_DIRECT : best];
         /* drop the packings of the losers */
-        for (gint a = 1; a < 5; a++) {
+        for (gint a = 1; a < DR_CONV_ALGOS; a++) {
             if (dev(c)->wbuf[a] && dev(c)->wbuf[a] != c->weightsBuf) { dR_finish(net); dR_clMemoryBufferCleanup(net, dev(c)->wbuf[a]); dev(c)->wbuf[a] = NULL; }
         }
     }
@@ -423,10 +446,11 @@ gboolean dR_conv2d_cleanupBuffers(dR_Graph *net, dR_Node *layer)
     dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
     dR_ConvDevice *d = dev(c);
     gboolean ret = TRUE;
-    for (gint a = 0; a < 5; a++) if (d->wbuf[a]) { ret &= dR_clMemoryBufferCleanup(net, d->wbuf[a]); d->wbuf[a] = NULL; }
+    for (gint a = 0; a < DR_CONV_ALGOS; a++) if (d->wbuf[a]) { ret &= dR_clMemoryBufferCleanup(net, d->wbuf[a]); d->wbuf[a] = NULL; }
     if (c->biasBuf) { ret &= dR_clMemoryBufferCleanup(net, c->biasBuf); c->biasBuf = NULL; }
     if (d->plan) { dRk_tensor_conv_free(d->plan); d->plan = NULL; }
     if (d->planAlt) { dRk_tensor_conv_free(d->planAlt); d->planAlt = NULL; }
+    if (d->wplan) { dRk_tensor_winograd_free(d->wplan); d->wplan = NULL; }
     c->weightsBuf = NULL;
     return ret;
 }

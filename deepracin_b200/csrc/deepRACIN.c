@@ -331,7 +331,7 @@ gboolean dR_setInterfaceLayout(dR_Graph *net, gint layout)
 
 gboolean dR_setConvAlgo(dR_Node *node, gint algo)
 {
-    if (!node || node->type != tConv2d || algo < DR_CONV_AUTO || algo > DR_CONV_TENSOR) return FALSE;
+    if (!node || node->type != tConv2d || algo < DR_CONV_AUTO || algo >= DR_CONV_ALGOS) return FALSE;
     ((dR_Conv2d_Data *)node->layer)->algo = algo;
     return TRUE;
 }
@@ -339,7 +339,7 @@ gboolean dR_setConvAlgo(dR_Node *node, gint algo)
 gboolean dR_setGraphConvAlgo(dR_Graph *net, gint algo)
 {
     if (!beforePrepare(net, "dR_setGraphConvAlgo")) return FALSE;
-    if (algo < DR_CONV_AUTO || algo > DR_CONV_TENSOR) return FALSE;
+    if (algo < DR_CONV_AUTO || algo >= DR_CONV_ALGOS) return FALSE;
     net->config->convAlgo = algo;
     return TRUE;
 }

@@ -20,3 +20,8 @@ int drk_gemm_f32_launch(cudaStream_t st, const float *A, const float *B, const f
 /* 3x3 stride-1 convolution specialised for Cin <= 4 (k_conv_first.cu); returns 0 when it does not take the shape */
 int drk_conv3x3_smallcin_launch(cudaStream_t st, const float *in, const float *wpack, const float *bias, float *out, int n, int W, int H,
                                 int Cin, int Cout, int act, int ldi, int ldo, int coff, int *rc);
+
+/* Winograd F(2x2,3x3) transforms (k_winograd.cu): V[k][t][c] with Ts tiles between transform positions, and back. */
+int drk_wino_input_launch(cudaStream_t st, const float *in, float *V, int nimg, int W, int H, int C, int ldi, size_t T, size_t Ts);
+int drk_wino_output_launch(cudaStream_t st, const float *Mt, const float *bias, float *out, int W, int H, int O, int ldo, int coff,
+                           size_t T, size_t Ts, int act);

@@ -98,17 +98,19 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                 const int t = blockIdx.x;
                 const int ksi = t % p.ksplit, tt = t / p.ksplit;
                 const int nt = tt % p.n_tiles;
+                const int brow = nt * BN + (p.bgroup_tiles ? ((tt / p.n_tiles) / p.bgroup_tiles) * p.bgroup_rows : 0);
                 const int ks0 = ksi * p.kper, ks1 = min(p.kslabs, ks0 + p.kper);
                 for (int tap = 0; tap < p.taps && pre < C::STAGES; tap++)
                     for (int ks = ks0; ks < ks1 && pre < C::STAGES; ks++, pre++) {
                         mbar_expect_tx(full_bar(pre), (uint32_t)p.stage_tx);
-                        tma_load_2d(base + pre * C::STAGE_BYTES + A_STAGE_BYTES, &mapB, tap * p.CinPad + ks * BK, nt * BN, full_bar(pre));
+                        tma_load_2d(base + pre * C::STAGE_BYTES + A_STAGE_BYTES, &mapB, tap * p.CinPad + ks * BK, brow, full_bar(pre));
                     }
             }
             drk_dep_wait();
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
                 const int ksi = t % p.ksplit, tt = t / p.ksplit;
                 const int mt = tt / p.n_tiles, nt = tt - mt * p.n_tiles;
+                const int brow = nt * BN + (p.bgroup_tiles ? (mt / p.bgroup_tiles) * p.bgroup_rows : 0);
                 const int ks0 = ksi * p.kper, ks1 = min(p.kslabs, ks0 + p.kper);
                 for (int tap = 0; tap < p.taps && ok; tap++) {
                     const int ky = tap / p.kw, kx = tap - ky * p.kw;
@@ -131,7 +133,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                                 tma_load_4d(sa + q * sub_bytes, &mapA, ks * BK, txi * p.TW + kx - p.pad, tyi * p.TH + ky - p.pad, img, full_bar(stage));
                             }
                         }
-                        if (!armed) tma_load_2d(sb, &mapB, tap * p.CinPad + ks * BK, nt * BN, full_bar(stage));
+                        if (!armed) tma_load_2d(sb, &mapB, tap * p.CinPad + ks * BK, brow, full_bar(stage));
                         issued++;
                         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                     }
@@ -718,7 +720,6 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             if (!mbar_wait_warp(tfull_bar(acc), acc_phase, abort_flag, p.status, 4)) { ok = false; break; }
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * SWAP_N);
-#pragma unroll 1
             if (p.P != 16) {
                 /* 30- or 32-pixel pitch: a block row is one 32-column TMEM load starting at column row * P (the last P - TW columns
                    of it are idle, a load at pitch 30 also fetches two columns of the next row that are not used); the two warps of a
@@ -1365,3 +1366,158 @@ extern "C" int dRk_tensor_fc_run(dRk_stream stream, dRk_TensorFcPlan *fp)
 }
 
 extern "C" void dRk_tensor_fc_free(dRk_TensorFcPlan *fp) { free(fp); }
+
+/*
+ * Winograd F(2x2,3x3) with the transform-domain products on the tensor cores (TF32 mode).
+ *
+ * The reference's algorithm (Kernels/dR_winograd2.cl:23-254: input transform :64-157, product :177-189, output
+ * transform :198-217; filter transform src/dR_nodes_conv2d.c:1162-1240) split at its two seams: the FP32 transform kernels of
+ * k_winograd.cu write V[16][Tp][Cin] and read M[16][Tp][Cout] (Tp = tile count rounded up to whole 128-row GEMM tiles), and the
+ * sixteen products M_k = V_k U_k run as ONE launch of the flat tensor GEMM above: the sixteen V_k are stacked on M, and every
+ * Tp / 128 row tiles the filter operand moves on to the next U_k (UmmaParams::bgroup_*).  2.25x fewer multiplications than
+ * the direct tensor kernels, paid for with V and M passing through memory (16 * T * (Cin + Cout) floats written and read):
+ * it is a candidate for the autotuner, not the planner's static choice.  Layers larger than the scratch cap run in image chunks.
+ */
+#include "k_gemm_f32.cuh"
+
+#define TWINO_SCRATCH_CAP ((size_t)1 << 28)     /* floats (1 GiB) */
+
+struct dRk_TensorWinogradPlan {
+    dRk_TensorConvPlan gemm[2];                 /* full chunks, tail chunk */
+    size_t T[2], Tp[2];
+    int imgs[2], nfull;
+    const float *in, *bias;
+    float *out, *V, *M;
+    int n, W, H, Cin, Cout, act, ldi, ldo, coff;
+};
+
+static size_t twino_tiles(int W, int H) { return (size_t)((W + 1) / 2) * ((H + 1) / 2); }
+static size_t twino_pad(size_t T) { return (T + BM - 1) / BM * BM; }
+static int twino_chunk(int n, int W, int H, int Cin, int Cout)
+{
+    const size_t per = 16 * twino_tiles(W, H) * (size_t)(Cin + Cout);
+    size_t c = (TWINO_SCRATCH_CAP - 16 * (size_t)BM * (Cin + Cout)) / per;     /* room for the padding rows */
+    if (c < 1) c = 1;
+    if (c > (size_t)n) c = (size_t)n;
+    return (int)c;
+}
+
+extern "C" int dRk_tensor_winograd_supported(int W, int H, int Cin, int Cout)
+{
+    return dRk_tensor_conv_supported(W, H, Cin, Cout, 3, 3) && Cin >= 8 && twino_pad(twino_tiles(W, H)) * 16 <= 0x7fffffffull / 2;
+}
+
+extern "C" size_t dRk_tensor_winograd_scratch_floats(int n, int W, int H, int Cin, int Cout)
+{
+    if (n <= 0 || !dRk_tensor_winograd_supported(W, H, Cin, Cout)) return 0;
+    return 16 * twino_pad(twino_tiles(W, H) * twino_chunk(n, W, H, Cin, Cout)) * (size_t)(Cin + Cout);
+}
+
+extern "C" size_t dRk_tensor_winograd_packed_floats(int Cin, int Cout) { return (size_t)16 * Cout * Cin; }
+
+/* U_k = (G g G^T)_k per (input, output) channel pair from the reference's [Cin][Cout][3][3] filters, stored [16][Cout][Cin]
+ * (K contiguous): G = [[1,0,0],[.5,.5,.5],[.5,-.5,.5],[0,0,1]] (src/dR_nodes_conv2d.c:1173-1176) */
+extern "C" int dRk_tensor_winograd_pack_weights(const float *w, float *dst, int Cin, int Cout)
+{
+    static const float G[4][3] = {{1.f, 0.f, 0.f}, {.5f, .5f, .5f}, {.5f, -.5f, .5f}, {0.f, 0.f, 1.f}};
+    if (!w || !dst || Cin <= 0 || Cout <= 0) return -1;
+    for (int c = 0; c < Cin; c++)
+        for (int o = 0; o < Cout; o++) {
+            const float *g = w + ((size_t)c * Cout + o) * 9;
+            float t[4][3];
+            for (int i = 0; i < 4; i++)
+                for (int j = 0; j < 3; j++) t[i][j] = G[i][0] * g[0 * 3 + j] + G[i][1] * g[1 * 3 + j] + G[i][2] * g[2 * 3 + j];
+            for (int i = 0; i < 4; i++)
+                for (int j = 0; j < 4; j++)
+                    dst[((size_t)(i * 4 + j) * Cout + o) * Cin + c] = t[i][0] * G[j][0] + t[i][1] * G[j][1] + t[i][2] * G[j][2];
+        }
+    return 0;
+}
+
+/* the flat GEMM of one chunk: A = V [16*Tp][Cin], B = U [16*Cout][Cin], D = M [16*Tp][Cout] */
+static int twino_gemm_plan(dRk_TensorConvPlan *pl, const float *V, const float *U, float *M, size_t Tp, int Cin, int Cout, int *status, int sms)
+{
+    PFN_encodeTiled enc = get_encode();
+    if (!enc) return -1;
+    memset(pl, 0, sizeof *pl);
+    UmmaParams &p = pl->p;
+    p.n = 1; p.W = 1; p.H = 1; p.Cin = Cin; p.Cout = Cout;
+    p.CinPad = (Cin + BK - 1) / BK * BK;
+    p.taps = 1; p.kw = 1; p.pad = 0; p.kslabs = p.CinPad / BK;
+    p.S = 0; p.TW = BM; p.TH = 1; p.tiles_x = p.tiles_y = 1;
+    p.total_sub = (long long)(16 * Tp);
+    p.m_tiles = (int)(16 * Tp / BM);
+    p.bias = NULL; p.out = M; p.ldo = Cout; p.coff = 0; p.act = 0; p.pool = 0; p.status = status;
+    p.ksplit = 1; p.kper = p.kslabs; p.split_stride = 0;
+    p.bgroup_tiles = (int)(Tp / BM); p.bgroup_rows = Cout;
+    pl->in = V; pl->wT = U; pl->sms = sms;
+    pl->BN = pick_bn(Cout, p.m_tiles, sms);
+    p.n_tiles = (Cout + pl->BN - 1) / pl->BN;
+    p.stage_tx = A_STAGE_BYTES + pl->BN * BK * 4;
+    const cuuint32_t ones[2] = {1, 1};
+    const cuuint64_t adims[2] = {(cuuint64_t)Cin, (cuuint64_t)(16 * Tp)}, str[1] = {(cuuint64_t)Cin * 4};
+    const cuuint32_t abox[2] = {BK, BM};
+    CUresult r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)V, adims, str, abox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const cuuint64_t bdims[2] = {(cuuint64_t)Cin, (cuuint64_t)16 * Cout};
+    const cuuint32_t bbox[2] = {BK, (cuuint32_t)pl->BN};
+    if (r == CUDA_SUCCESS)
+        r = enc(&pl->mapB, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)U, bdims, str, bbox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { fprintf(stderr, "tensor winograd plan: tensor map rejected (%d)\n", (int)r); return -1; }
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    pl->grid = (int)(tiles < sms ? tiles : sms);
+    return 0;
+}
+
+extern "C" dRk_TensorWinogradPlan *dRk_tensor_winograd_plan(const float *in, const float *U, const float *bias, float *out, float *scratch,
+                                                            int n, int W, int H, int Cin, int Cout, int act, int ldi, int ldo, int coff, int *status)
+{
+    if (n <= 0 || !scratch || !dRk_tensor_winograd_supported(W, H, Cin, Cout)) return NULL;
+    if (ldi < Cin || ldo < coff + Cout || ((uintptr_t)scratch % 16) || ((uintptr_t)U % 16)) return NULL;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    dRk_TensorWinogradPlan *wp = (dRk_TensorWinogradPlan *)calloc(1, sizeof(dRk_TensorWinogradPlan));
+    if (!wp) return NULL;
+    wp->in = in; wp->bias = bias; wp->out = out; wp->n = n; wp->W = W; wp->H = H; wp->Cin = Cin; wp->Cout = Cout;
+    wp->act = act; wp->ldi = ldi; wp->ldo = ldo; wp->coff = coff;
+    const int chunk = twino_chunk(n, W, H, Cin, Cout);
+    wp->imgs[0] = chunk; wp->nfull = n / chunk; wp->imgs[1] = n - wp->nfull * chunk;
+    wp->V = scratch;
+    wp->M = scratch + 16 * twino_pad(twino_tiles(W, H) * chunk) * (size_t)Cin;
+    for (int i = 0; i < 2; i++) {
+        if (wp->imgs[i] == 0) continue;
+        wp->T[i] = twino_tiles(W, H) * wp->imgs[i];
+        wp->Tp[i] = twino_pad(wp->T[i]);
+        if (twino_gemm_plan(&wp->gemm[i], wp->V, U, wp->M, wp->Tp[i], Cin, Cout, status, sms) != 0) { free(wp); return NULL; }
+    }
+    return wp;
+}
+
+extern "C" int dRk_tensor_winograd_run(dRk_stream stream, dRk_TensorWinogradPlan *wp)
+{
+    if (!wp) return -1;
+    cudaStream_t st = drk_stream(stream);
+    int b0 = 0;
+    for (int c = 0; c < wp->nfull + (wp->imgs[1] ? 1 : 0); c++) {
+        const int i = c < wp->nfull ? 0 : 1;
+        const float *src = wp->in + (size_t)b0 * wp->H * wp->W * wp->ldi;
+        float *dst = wp->out + (size_t)b0 * wp->H * wp->W * wp->ldo;
+        int rc = drk_wino_input_launch(st, src, wp->V, wp->imgs[i], wp->W, wp->H, wp->Cin, wp->ldi, wp->T[i], wp->Tp[i]);
+        if (rc) return rc;
+        dRk_TensorConvPlan *g = &wp->gemm[i];
+        switch (g->BN) {
+        case 256: rc = launch_umma<256>(st, g); break;
+        case 128: rc = launch_umma<128>(st, g); break;
+        default: rc = launch_umma<64>(st, g); break;
+        }
+        if (rc) return rc;
+        rc = drk_wino_output_launch(st, wp->M, wp->bias, dst, wp->W, wp->H, wp->Cout, wp->ldo, wp->coff, wp->T[i], wp->Tp[i], wp->act);
+        if (rc) return rc;
+        b0 += wp->imgs[i];
+    }
+    return 0;
+}
+
+extern "C" void dRk_tensor_winograd_free(dRk_TensorWinogradPlan *wp) { free(wp); }

@@ -152,6 +152,21 @@ int dRk_tensor_conv_plan_describe(const dRk_TensorConvPlan *plan, int *P, int *T
 int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *plan);
 void dRk_tensor_conv_free(dRk_TensorConvPlan *plan);
 
+/* Winograd F(2x2,3x3) with its sixteen transform-domain products on the tensor cores (TF32 operands, FP32 accumulate; the
+ * transforms stay FP32): the algorithm of conv2dwinograd2 (Kernels/dR_winograd2.cl:23-254) with the product step (:177-189) as
+ * one batched tcgen05 GEMM.  3x3 stride-1 layers with Cin % 4 == 0, Cin >= 8, Cout % 4 == 0, Cout >= 16.  U is the transformed
+ * filter tensor [16][Cout][Cin] from dRk_tensor_winograd_pack_weights (G g G^T, src/dR_nodes_conv2d.c:1162-1240); scratch holds
+ * dRk_tensor_winograd_scratch_floats() floats; in / out are N-HWC with pixel strides ldi / ldo, out at channel offset coff. */
+typedef struct dRk_TensorWinogradPlan dRk_TensorWinogradPlan;
+int dRk_tensor_winograd_supported(int W, int H, int Cin, int Cout);
+size_t dRk_tensor_winograd_scratch_floats(int n, int W, int H, int Cin, int Cout);
+size_t dRk_tensor_winograd_packed_floats(int Cin, int Cout);
+int dRk_tensor_winograd_pack_weights(const float *w, float *dst, int Cin, int Cout);
+dRk_TensorWinogradPlan *dRk_tensor_winograd_plan(const float *in, const float *U, const float *bias, float *out, float *scratch,
+                                                 int n, int W, int H, int Cin, int Cout, int act, int ldi, int ldo, int coff, int *status);
+int dRk_tensor_winograd_run(dRk_stream stream, dRk_TensorWinogradPlan *plan);
+void dRk_tensor_winograd_free(dRk_TensorWinogradPlan *plan);
+
 /* Fully connected layer on the tensor cores (TF32 inputs, FP32 accumulate) for batches of 16..128 with
  * Nin % 32 == 0 and Nout % 4 == 0 (>= 64): split-K flat GEMM + the reduce step of dRk_fc_f32.  wT is [Nout][Nin]
  * (K contiguous); scratch holds dRk_tensor_fc_scratch_floats() floats.  Same reference kernels as dRk_fc_f32. */

@@ -15,8 +15,10 @@ enum dR_ConvAlgo {
     DR_CONV_DIRECT = 1,     /* FP32 FFMA implicit-GEMM evaluation of the direct sum; any filter/stride */
     DR_CONV_WINOGRAD = 2,   /* F(2x2,3x3): transform, 16 transform-domain GEMMs, inverse transform */
     DR_CONV_ONEBYONE = 3,   /* 1x1 stride 1 as one GEMM over pixels */
-    DR_CONV_TENSOR = 4      /* tcgen05 TF32 implicit GEMM (TMA-fed, TMEM accumulators) */
+    DR_CONV_TENSOR = 4,     /* tcgen05 TF32 implicit GEMM (TMA-fed, TMEM accumulators) */
+    DR_CONV_TENSOR_WINOGRAD = 5 /* F(2x2,3x3) with the 16 transform-domain GEMMs on the tcgen05 tensor cores (TF32 mode) */
 };
+#define DR_CONV_ALGOS 6
 typedef enum dR_ConvAlgo dR_ConvAlgo;
 
 struct dR_Conv2d_Data {
@@ -36,7 +38,7 @@ struct dR_Conv2d_Data {
     gint chosenTensor;          /* 1: TF32 tensor-core arithmetic, 0: exact FP32 FFMA */
     cl_mem weightsBufAlt;       /* second packing kept for the autotuner's alternative */
     void *tmaDescs;             /* host block of CUtensorMap descriptors (tensor path) */
-    gdouble tunedMs[5];         /* measured ms per dR_ConvAlgo (0 = not measured) */
+    gdouble tunedMs[DR_CONV_ALGOS]; /* measured ms per dR_ConvAlgo (0 = not measured) */
 };
 
 #ifdef __cplusplus

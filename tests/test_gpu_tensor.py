@@ -262,3 +262,64 @@ def test_random_layer_shapes_match_oracle(idx, n, cin, cout, h, w, k, pool):
         got = dr.apply(g)[0].reshape(ref.shape)
         assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
     assert rel_err(got, ref) <= TOL_TF32
+
+
+TENSOR_WINOGRAD_SHAPES = [
+    # name, n, cin, cout, h, w
+    ("tw_32_64_20x30", 2, 32, 64, 20, 30),
+    ("tw_odd_13x17", 3, 64, 192, 17, 13),             # odd width and height: ragged 2x2 output tiles
+    ("tw_16_16", 2, 16, 16, 12, 12),                  # channel counts below one 32-channel slab
+    ("tw_8_24_9x11", 1, 8, 24, 11, 9),
+    ("tw_48_72", 2, 48, 72, 28, 28),
+    ("tw_conv5", 64, 512, 512, 14, 14),               # the benchmark's 14x14 layers at batch 64
+    ("tw_conv4", 16, 256, 512, 28, 28),
+    ("tw_chunked", 23, 64, 64, 224, 224),             # more transform-domain data than the scratch cap: two full image chunks and a tail
+]
+
+
+@pytest.mark.parametrize("name,n,cin,cout,h,w", TENSOR_WINOGRAD_SHAPES)
+def test_tensor_core_winograd_matches_oracle(name, n, cin, cout, h, w):
+    """Winograd F(2x2,3x3) with the sixteen transform-domain GEMMs on the tensor cores (TF32 operands): same bound as the direct
+    tensor kernels, against the CPU oracle on the first and last image and against the exact-FP32 Winograd kernels on all."""
+    x, wt, b = cases.conv_case(name, n, cin, cout, h, w, 3, True)
+    res = {}
+    for math, algo in (("tf32", "tensor_winograd"), ("fp32", "winograd")):
+        with dr.Environment() as env:
+            g = env.create_graph("CHW")
+            g.batch = n
+            g.math = math
+            f = dr.feed_node(g, [cin, h, w])
+            o = conv_build(wt, b, 1, 1, algo=algo)(g, [f])
+            dr.mark_as_output(o)
+            dr.prepare(g)
+            assert dr.lib.dR_getConvAlgo(o.ptr) == dr.CONV_ALGO[algo]
+            dr.feed_data(f, x)
+            res[math] = dr.apply(g)[0].reshape(n, cout, h, w)
+            again = dr.apply(g)[0].reshape(n, cout, h, w)
+            assert np.array_equal(res[math], again)
+            assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    for i in (0, n - 1):
+        ref = oracle.conv2d(x[i:i + 1], wt, b, (1, 1), 1)
+        assert rel_err(res["tf32"][i:i + 1], ref) <= TOL_TF32
+        assert rel_err(res["fp32"][i:i + 1], ref) <= 1e-4
+    num = max(float(np.max(np.abs(res["tf32"][i] - res["fp32"][i]))) for i in range(n))
+    assert num / float(np.max(np.abs(res["fp32"]))) <= TOL_TF32
+
+
+def test_autotuner_may_choose_among_the_tensor_variants():
+    """TF32 mode with autotuning: direct tensor kernel and tensor-core Winograd are both timed; whichever wins, the result holds."""
+    x, wt, b = cases.conv_case("tw_autotune", 8, 128, 128, 28, 28, 3, True)
+    ref = oracle.conv2d(x[:1], wt, b, (1, 1), 1)
+    with dr.Environment() as env:
+        g = env.create_graph("CHW")
+        g.batch = 8
+        g.math = "tf32"
+        g.autotune = True
+        f = dr.feed_node(g, [128, 28, 28])
+        o = conv_build(wt, b, 1, 1)(g, [f])
+        dr.mark_as_output(o)
+        dr.prepare(g)
+        assert dr.lib.dR_getConvAlgo(o.ptr) in (dr.CONV_ALGO["tensor"], dr.CONV_ALGO["tensor_winograd"])
+        dr.feed_data(f, x)
+        got = dr.apply(g)[0].reshape(8, 128, 28, 28)
+    assert rel_err(got[:1], ref) <= TOL_TF32
