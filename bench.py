@@ -12,6 +12,7 @@ ranks); `e2e` is the same metric with the pinned-host -> device copy of every st
 of its class probabilities inside the timed region.  The same line carries, as objects of their own:
 
   fp32_exact   VGG-16 batch 64 in the reference's own arithmetic (FP32 FFMA kernels, tolerance 1e-4 per layer)
+  fp32_accurate_tensor  VGG-16 batch 64 in math mode fp32x3: FP32-class error bound from three TF32 tensor-core passes per product
   squeezenet   SqueezeNet v1.1 (the reference's example graph) at batch 64 (every N) and batch 1 (N = 1)
   sustained    >= 3 s of back-to-back dR_apply with the clock sampler running (N = 1)
   e2e_dropin   the reference-shaped blocking calls: dR_feedData ([C][H][W], pageable host memory) + dR_apply +
@@ -362,6 +363,7 @@ def run_ours(args):
         fp = measure(ctx, "vgg16", "fp32", batch, k2, 3, autotune=True, want_profile=True)
         sq = measure(ctx, "squeezenet", args.math, batch, max(args.steps, 20), 3)
         extra["fp32_exact"], extra["squeezenet_b64"] = fp, sq
+        extra["fp32x3"] = measure(ctx, "vgg16", "fp32x3", batch, k2, 3, want_profile=True)
         if ctx.world == 1:
             extra["squeezenet_b1"] = measure(ctx, "squeezenet", args.math, 1, max(args.steps, 50), 5, cuda_graph=True)
             single = measure_dropin(ctx, k2, 3, batch, args.math)
@@ -418,6 +420,14 @@ def run_ours(args):
                                   "frac_of_ffma_peak_executed": (real / FFMA_PEAK_NOMINAL) if real else None, "ffma_peak": FFMA_PEAK_NOMINAL,
                                   "ffma_peak_source": "nominal 148 SMs x 128 lanes x 2 x 1.965 GHz", "ms_per_layer": froof.get("ms_per_layer"),
                                   "tolerance": "1e-4 x max|ref| per layer (the reference's own arithmetic)"}
+        if "fp32x3" in extra:
+            x3 = extra["fp32x3"]
+            xroof, xagg, _ = vgg_roofline("tf32", batch, x3["profile"], peaks, None) if "profile" in x3 else ({}, None, None)
+            line["fp32_accurate_tensor"] = {"images_per_s": x3["images_per_s"], "ms_per_step": x3["ms_per_step"], "e2e_images_per_s": x3["e2e_images_per_s"],
+                                            "steps": x3["steps"], "dtype": "3xtf32", "conv_tflops_direct_equivalent": xagg,
+                                            "conv_tflops_executed_tf32": (3.0 * xagg) if xagg else None, "ms_per_layer": xroof.get("ms_per_layer"),
+                                            "what": "math mode fp32x3: 3x3 layers with >= 8 input channels evaluate x*w as hi*hi + hi*lo + lo*hi in three TF32 "
+                                                    "tensor-core passes (FP32-class error bound 1e-4 x max|ref| per layer); first layer, FC, pooling, softmax on the FP32 kernels"}
         if "squeezenet_b64" in extra:
             sq = extra["squeezenet_b64"]
             line["squeezenet"] = {"batch64": {"images_per_s": sq["images_per_s"], "ms_per_step": sq["ms_per_step"], "e2e_images_per_s": sq["e2e_images_per_s"],

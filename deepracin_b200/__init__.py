@@ -10,7 +10,7 @@ fed [C][H][W] buffers and weights are transposed HWIO -> [Cin][Cout][kh][kw]
 (__init__.py.in:458-462, 487-489, 559-562).
 
 Additions: ``Graph.batch`` (images per ``apply``; arrays gain a leading batch axis),
-``Graph.math`` ('fp32' | 'tf32'), ``Graph.conv_algo``, ``Graph.autotune``, ``Graph.cuda_graph``,
+``Graph.math`` ('fp32' | 'tf32' | 'fp32x3'), ``Graph.conv_algo``, ``Graph.autotune``, ``Graph.cuda_graph``,
 ``Graph.feed_overlap``.
 
 All computation happens in ``libdeepracin.so`` on the GPU; there is no CPU path here.
@@ -29,7 +29,7 @@ lib = load()
 
 act_dict = {"linear": 0, "relu": 1}
 pool_dict = {"max": 0, "average": 1}
-MATH = {"fp32": 0, "tf32": 1}
+MATH = {"fp32": 0, "tf32": 1, "fp32x3": 2}
 CONV_ALGO = {"auto": 0, "direct": 1, "winograd": 2, "1x1": 3, "tensor": 4, "tensor_winograd": 5}
 _FP = POINTER(c_float)
 

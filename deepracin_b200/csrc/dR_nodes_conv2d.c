@@ -159,26 +159,30 @@ static gboolean is3x3s1(dR_Conv2d_Data *c) { return c->shape.s0 == 3 && c->shape
 static gboolean is1x1s1(dR_Conv2d_Data *c) { return c->shape.s0 == 1 && c->shape.s1 == 1 && c->stride.s1 == 1 && c->stride.s2 == 1; }
 
 /* the tensor path wants stride 1, odd square 1x1/3x3 filters and channel counts TMA can address */
-static gboolean tensorLegal(dR_Node *layer)
+static gboolean x3Mode(dR_Graph *net) { return net->config->mathMode == DR_MATH_FP32_TENSOR; }
+
+static gboolean tensorLegal(dR_Graph *net, dR_Node *layer)
 {
     dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
     dR_Node *in = dR_firstInput(layer);
     if (!(is3x3s1(c) || is1x1s1(c))) return FALSE;
-    if (!dRk_tensor_conv_supported(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3, c->shape.s0, c->shape.s1)) return FALSE;
+    if (x3Mode(net)) {      /* the FP32-accurate three-pass tensor kernel exists for 3x3 layers only */
+        if (!is3x3s1(c) || !dRk_tensor_conv_x3_supported(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3)) return FALSE;
+    } else if (!dRk_tensor_conv_supported(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3, c->shape.s0, c->shape.s1)) return FALSE;
     if (in->act_cstride != in->oshape.s2) return FALSE;     /* input must be dense N-HWC */
     return TRUE;
 }
 
-static gboolean algoLegal(dR_Node *layer, gint algo)
+static gboolean algoLegal(dR_Graph *net, dR_Node *layer, gint algo)
 {
     dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
     switch (algo) {
     case DR_CONV_DIRECT: return TRUE;
     case DR_CONV_WINOGRAD: return is3x3s1(c);
     case DR_CONV_ONEBYONE: return is1x1s1(c);
-    case DR_CONV_TENSOR: return tensorLegal(layer);
+    case DR_CONV_TENSOR: return tensorLegal(net, layer);
     case DR_CONV_TENSOR_WINOGRAD:
-        return is3x3s1(c) && tensorLegal(layer) && dRk_tensor_winograd_supported(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
+        return is3x3s1(c) && !x3Mode(net) && tensorLegal(net, layer) && dRk_tensor_winograd_supported(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
     }
     return FALSE;
 }
@@ -188,7 +192,7 @@ static gboolean algoLegal(dR_Node *layer, gint algo)
 static gint staticRule(dR_Graph *net, dR_Node *layer)
 {
     dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
-    if (net->config->mathMode == DR_MATH_TF32 && tensorLegal(layer)) return DR_CONV_TENSOR;
+    if (net->config->mathMode != DR_MATH_FP32 && tensorLegal(net, layer)) return DR_CONV_TENSOR;
     /* a handful of input channels (RGB first layer): bound by writing the output, a direct kernel wins */
     if (is3x3s1(c) && c->shape.s2 <= 4) return DR_CONV_DIRECT;
     if (is3x3s1(c)) return DR_CONV_WINOGRAD;
@@ -206,12 +210,12 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
 {
     dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
     gint want = c->algo != DR_CONV_AUTO ? c->algo : net->config->convAlgo;
-    if (want != DR_CONV_AUTO && !algoLegal(layer, want)) {
+    if (want != DR_CONV_AUTO && !algoLegal(net, layer, want)) {
         if (c->algo != DR_CONV_AUTO) { g_print("Conv2d Layer %d: requested kernel family %d cannot evaluate this filter/stride\n", layer->layerID, want); return FALSE; }
         want = DR_CONV_AUTO;    /* a graph-wide wish only applies where it is legal */
     }
     c->chosenAlgo = want != DR_CONV_AUTO ? want : staticRule(net, layer);
-    c->chosenTensor = c->chosenAlgo == DR_CONV_TENSOR || c->chosenAlgo == DR_CONV_TENSOR_WINOGRAD;
+    c->chosenTensor = (c->chosenAlgo == DR_CONV_TENSOR || c->chosenAlgo == DR_CONV_TENSOR_WINOGRAD) ? (x3Mode(net) ? 2 : 1) : 0;
     /* conv -> 2x2/2 max pool with no other reader: the tensor kernel's epilogue stores the pooled tensor
        directly into the pooling node's buffer and the pooling node launches nothing */
     dev(c)->fusedPool = 0;
@@ -223,7 +227,7 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
             const gint ptype = pl->poolingType == tMax ? 1 : pl->poolingType == tAverage ? 2 : 0;
             if (ptype && pl->shape.s1 == 2 && pl->shape.s2 == 2 && pl->shape.s3 == 1 &&
                 pl->stride.s1 == 2 && pl->stride.s2 == 2 && pl->stride.s3 == 1 &&
-                dRk_tensor_conv_can_fuse_pool(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3, c->shape.s0, c->shape.s1, ptype)) {
+                (x3Mode(net) ? ptype == 1 : dRk_tensor_conv_can_fuse_pool(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3, c->shape.s0, c->shape.s1, ptype))) {
                 dev(c)->fusedPool = ptype;
                 pl->useLMEM = TRUE;                 /* marks "computed by the producer" for dR_pooling_compute */
                 layer->elided = TRUE;
@@ -237,7 +241,7 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
     {
         dR_Node *in = dR_firstInput(layer);
         dR_Node *src = NULL;
-        if (c->chosenAlgo == DR_CONV_TENSOR && net->config->fuseGraph && !dRk_debug_switches()->no_input_map && is3x3s1(c) && c->shape.s2 <= 4 && in->type == tConcat && !in->output &&
+        if (c->chosenAlgo == DR_CONV_TENSOR && !x3Mode(net) && net->config->fuseGraph && !dRk_debug_switches()->no_input_map && is3x3s1(c) && c->shape.s2 <= 4 && in->type == tConcat && !in->output &&
             in->next_layers->length == 1 && dR_concat_gatherAsInputMap(in, &src, dev(c)->mapCh, dev(c)->mapScale, dev(c)->mapShift) &&
             src->type == tDataFeedNode /* feed buffers are never recycled by the buffer planner, so the source outlives the skipped nodes */) {
             guint seen = 0;                             /* the kernel wants a permutation of the source's first Cin channels */
@@ -254,7 +258,7 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
     if (c->chosenAlgo == DR_CONV_WINOGRAD || (net->config->autotune && is3x3s1(c)))
         layer->scratchFloats = dRk_winograd_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
     if (c->chosenAlgo == DR_CONV_TENSOR_WINOGRAD ||
-        (net->config->autotune && net->config->mathMode == DR_MATH_TF32 && algoLegal(layer, DR_CONV_TENSOR_WINOGRAD))) {
+        (net->config->autotune && net->config->mathMode == DR_MATH_TF32 && algoLegal(net, layer, DR_CONV_TENSOR_WINOGRAD))) {
         const size_t s = dRk_tensor_winograd_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
         if (s > layer->scratchFloats) layer->scratchFloats = s;
     }
@@ -279,7 +283,7 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
     if (d->wbuf[algo]) return TRUE;
     size_t n = (size_t)kw * kh * I * O;
     if (algo == DR_CONV_WINOGRAD) n = (size_t)16 * I * O;
-    if (algo == DR_CONV_TENSOR) n = dRk_tensor_conv_packed_floats(c->ishape.s0, c->ishape.s1, I, O, kw, kh);
+    if (algo == DR_CONV_TENSOR) n = x3Mode(net) ? dRk_tensor_conv_x3_packed_floats(I, O) : dRk_tensor_conv_packed_floats(c->ishape.s0, c->ishape.s1, I, O, kw, kh);
     if (algo == DR_CONV_TENSOR_WINOGRAD) n = dRk_tensor_winograd_packed_floats(I, O);
     if (n == 0) return FALSE;
     gfloat *p = (gfloat *)g_malloc0(n * sizeof(gfloat));
@@ -291,7 +295,8 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
                     p[((size_t)t * I + i) * O + o] = c->weights[((size_t)i * O + o) * kh * kw + t];
     } else if (algo == DR_CONV_TENSOR) {
         /* K-major rows per output channel; the exact layout belongs to the tensor kernel picked for this shape */
-        if (dRk_tensor_conv_pack_weights(c->weights, p, c->ishape.s0, c->ishape.s1, I, O, kw, kh) != 0) { g_free(p); return FALSE; }
+        if ((x3Mode(net) ? dRk_tensor_conv_x3_pack_weights(c->weights, p, I, O)
+                         : dRk_tensor_conv_pack_weights(c->weights, p, c->ishape.s0, c->ishape.s1, I, O, kw, kh)) != 0) { g_free(p); return FALSE; }
     } else if (algo == DR_CONV_TENSOR_WINOGRAD) {
         if (dRk_tensor_winograd_pack_weights(c->weights, p, I, O) != 0) { g_free(p); return FALSE; }
     } else {
@@ -356,8 +361,11 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
         }
         if (!d->plan) {
             d->planSrc = src; d->planDst = dst;
-            d->plan = dRk_tensor_conv_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR], bias, dst, n, W, H, c->shape.s2, c->shape.s3,
-                                           c->shape.s0, c->shape.s1, act, layer->act_cstride, layer->act_coffset, d->fusedPool, (int *)net->statusWord);
+            d->plan = x3Mode(net)
+                ? dRk_tensor_conv_x3_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR], bias, dst, n, W, H, c->shape.s2, c->shape.s3, act,
+                                          layer->act_cstride, layer->act_coffset, d->fusedPool, (int *)net->statusWord)
+                : dRk_tensor_conv_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR], bias, dst, n, W, H, c->shape.s2, c->shape.s3,
+                                       c->shape.s0, c->shape.s1, act, layer->act_cstride, layer->act_coffset, d->fusedPool, (int *)net->statusWord);
             if (!d->plan) { g_print("Conv2d Layer %d: tensor-core plan could not be built\n", layer->layerID); return FALSE; }
             if (d->mapSrc && dRk_tensor_conv_set_input_map(d->plan, d->mapSrc->act_cstride, d->mapCh, d->mapScale, d->mapShift) != 0) {
                 g_print("Conv2d Layer %d: input channel map rejected\n", layer->layerID);
@@ -408,8 +416,8 @@ gboolean dR_conv2d_autotune(dR_Graph *net)
         gint best = c->chosenAlgo;
         gdouble bestMs = 1e30;
         for (gint algo = DR_CONV_DIRECT; algo < DR_CONV_ALGOS; algo++) {
-            if (!algoLegal(layer, algo)) continue;
-            if ((algo == DR_CONV_TENSOR || algo == DR_CONV_TENSOR_WINOGRAD) && net->config->mathMode != DR_MATH_TF32) continue;
+            if (!algoLegal(net, layer, algo)) continue;
+            if ((algo == DR_CONV_TENSOR || algo == DR_CONV_TENSOR_WINOGRAD) && net->config->mathMode == DR_MATH_FP32) continue;
             if (algo == DR_CONV_ONEBYONE) continue;             /* same kernel as DIRECT for 1x1 */
             for (gint i = 0; i < 3; i++) if (!dR_conv2d_runVariant(net, layer, algo, 0)) return FALSE;
             dR_timerStart(net);
@@ -422,7 +430,7 @@ gboolean dR_conv2d_autotune(dR_Graph *net)
         }
         if (best == DR_CONV_DIRECT && is1x1s1(c)) best = DR_CONV_ONEBYONE;
         c->chosenAlgo = best;
-        c->chosenTensor = best == DR_CONV_TENSOR || best == DR_CONV_TENSOR_WINOGRAD;
+        c->chosenTensor = (best == DR_CONV_TENSOR || best == DR_CONV_TENSOR_WINOGRAD) ? (x3Mode(net) ? 2 : 1) : 0;
         c->weightsBuf = dev(c)->wbuf[best == DR_CONV_ONEBYONE ? DR_CONV_DIRECT : best];
         /* drop the packings of the losers */
         for (gint a = 1; a < DR_CONV_ALGOS; a++) {

@@ -316,7 +316,7 @@ gboolean dR_setBatchSize(dR_Graph *net, gint n)
 gboolean dR_setMathMode(dR_Graph *net, gint mode)
 {
     if (!beforePrepare(net, "dR_setMathMode")) return FALSE;
-    if (mode != DR_MATH_FP32 && mode != DR_MATH_TF32) return FALSE;
+    if (mode != DR_MATH_FP32 && mode != DR_MATH_TF32 && mode != DR_MATH_FP32_TENSOR) return FALSE;
     net->config->mathMode = mode;
     return TRUE;
 }

@@ -575,11 +575,24 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 #define SWAP_W_BYTES (BM * BK * 4)                     /* filter stage: 128 rows x 128 B */
 #define SWAP_NW 9
 #define SWAP_EPI_WARPS 8
-#define SWAP_THREADS ((2 + SWAP_EPI_WARPS) * 32)
+#define SWAP_SPLIT_WARPS 4                             /* X3 mode only */
+#define SWAP_THREADS(X3) ((2 + SWAP_EPI_WARPS + ((X3) ? SWAP_SPLIT_WARPS : 0)) * 32)
 #define SWAP_SMEM (SWAP_NH * SWAP_HALO_SLOT + SWAP_NW * SWAP_W_BYTES + 1024 + 512)
 
-__global__ void __launch_bounds__(SWAP_THREADS, 1)
-k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW, const UmmaParams p)
+/*
+ * X3 = true: FP32-accurate evaluation on the tensor cores ("3xTF32").  A kind::tf32 MMA reads only the upper 19 bits of
+ * each FP32 operand (sign, exponent, 10 mantissa bits): x = hi(x) + lo(x) with hi(x) = x with its low 13 mantissa bits
+ * cleared.  The product x*w is then evaluated as hi(x)*hi(w) + hi(x)*lo(w) + lo(x)*hi(w) in three passes over the nine
+ * taps into the same FP32 accumulator; the dropped lo*lo term and the truncation of the lo parts are below 2^-21 of
+ * the product, so a layer stays inside the exact-FP32 kernels' 1e-4 bound at three times the direct TF32 kernel's MMA count
+ * instead of the FFMA rate.  The tensor maps are plain FLOAT32 here (no rounding by TMA): passes 0 and 1 read the haloed
+ * block as loaded (the MMA ignores the low bits = hi(x)) against the filters W and a precomputed lo(W) tensor (mapWlo);
+ * then four extra warps replace the block in place by lo(x) = x - hi(x) -- exact in FP32 -- and pass 2 multiplies it with W.
+ */
+template <bool X3>
+__global__ void __launch_bounds__(SWAP_THREADS(X3), 1)
+k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapW, const __grid_constant__ CUtensorMap mapWlo,
+                 const UmmaParams p)
 {
     extern __shared__ uint8_t smem_raw[];
     drk_dep_trigger();
@@ -588,7 +601,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     uint8_t *gen = smem_raw + (base - raw);
     const uint32_t h_base = base, w_base = base + SWAP_NH * SWAP_HALO_SLOT;
     const uint32_t bars = w_base + SWAP_NW * SWAP_W_BYTES;
-    constexpr int NBARS = 2 * SWAP_NH + 2 * SWAP_NW + 5;
+    constexpr int NBARS = 4 * SWAP_NH + 2 * SWAP_NW + 5;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + SWAP_NH * SWAP_HALO_SLOT + SWAP_NW * SWAP_W_BYTES + 8 * NBARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     auto hfull = [&](int s) { return bars + 8u * s; };
@@ -598,6 +611,9 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     auto tfull_bar = [&](int a) { return bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + a); };
     auto tempty_bar = [&](int a) { return bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + 2 + a); };
     const uint32_t drain_bar = bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + 4);
+    auto split_go = [&](int s) { return bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + 5 + s); };            /* X3: passes 0 and 1 have read the block */
+    auto split_done = [&](int s) { return bars + 8u * (3 * SWAP_NH + 2 * SWAP_NW + 5 + s); };          /* X3: the block now holds lo(x) */
+    constexpr int PASSES = X3 ? 3 : 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles * p.n_tiles;
@@ -609,6 +625,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         for (int s = 0; s < SWAP_NH; s++) { mbar_init(hfull(s), 1); mbar_init(hempty(s), 1); }
         for (int s = 0; s < SWAP_NW; s++) { mbar_init(wfull(s), 1); mbar_init(wempty(s), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), SWAP_EPI_WARPS); }
+        for (int s = 0; s < SWAP_NH; s++) { mbar_init(split_go(s), 1); mbar_init(split_done(s), SWAP_SPLIT_WARPS); }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -624,6 +641,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&mapX) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&mapW) : "memory");
+            if (X3) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapWlo) : "memory");
             int hs = 0, ws = 0;
             uint32_t hph = 0, wph = 0;
             long long h_issued = 0, w_issued = 0;
@@ -638,10 +656,11 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                     tma_load_4d(h_base + hs * SWAP_HALO_SLOT, &mapX, ks * BK, txi * p.TW - 1, tyi * p.TH - 1, img, hfull(hs));
                     h_issued++;
                     if (++hs == SWAP_NH) { hs = 0; hph ^= 1u; }
-                    for (int tap = 0; tap < 9; tap++) {
+                    for (int pt = 0; pt < 9 * PASSES; pt++) {                   /* X3: filters, their low parts, filters again */
+                        const int tap = pt % 9;
                         if (!mbar_wait(wempty(ws), wph ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
                         mbar_expect_tx(wfull(ws), SWAP_W_BYTES);
-                        tma_load_2d(w_base + ws * SWAP_W_BYTES, &mapW, tap * p.CinPad + ks * BK, nt * BM, wfull(ws));
+                        tma_load_2d(w_base + ws * SWAP_W_BYTES, (X3 && pt / 9 == 1) ? &mapWlo : &mapW, tap * p.CinPad + ks * BK, nt * BM, wfull(ws));
                         w_issued++;
                         if (++ws == SWAP_NW) { ws = 0; wph ^= 1u; }
                     }
@@ -680,7 +699,13 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                 for (int ks = 0; ks < p.kslabs && ok; ks++) {
                     if (!mbar_wait(hfull(hs), hph, abort_flag, p.status, 6)) { ok = false; break; }
                     const uint32_t sh = h_base + hs * SWAP_HALO_SLOT;
-                    for (int tap = 0; tap < 9; tap++) {
+                    for (int pt = 0; pt < 9 * PASSES; pt++) {
+                        const int tap = pt % 9;
+                        if (X3 && pt == 18) {
+                            /* passes 0 and 1 are issued: once they have read the block the splitter warps turn it into lo(x) */
+                            umma_commit(split_go(hs));
+                            if (!mbar_wait(split_done(hs), hph, abort_flag, p.status, 12)) { ok = false; break; }
+                        }
                         if (!mbar_wait(wfull(ws), wph, abort_flag, p.status, 3)) { ok = false; break; }
                         tc_fence_after();
                         const int ky = tap / 3, kx = tap - ky * 3;
@@ -688,7 +713,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                         const uint64_t bdesc = make_smem_desc(sh + (uint32_t)((ky * p.P + kx) * BK * 4));
 #pragma unroll
                         for (int j = 0; j < BK / 8; j++)
-                            umma_tf32(d_tmem, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, (ks | tap | j) ? 1u : 0u);
+                            umma_tf32(d_tmem, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, (ks | pt | j) ? 1u : 0u);
                         umma_commit(wempty(ws));
                         if (++ws == SWAP_NW) { ws = 0; wph ^= 1u; }
                     }
@@ -699,7 +724,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             }
             if (!ok) umma_drain(drain_bar);
         }
-    } else {
+    } else if (warp < 2 + SWAP_EPI_WARPS) {
         /* eight epilogue warps: two per 32-lane quarter of TMEM, each taking half of the 256 pixel columns (with four, the
            224 scalar stores per lane and tile of a layer without pooling outlasted the 72 MMAs of a 64-channel-deep tile) */
         const int quarter = warp & 3, half = (warp - 2) >> 2;
@@ -798,6 +823,33 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
         }
+    } else if (X3) {
+        /* splitter warps: block -> lo(block) in place between passes 1 and 2 of every channel slab */
+        const int sw = warp - (2 + SWAP_EPI_WARPS);
+        int hs = 0;
+        uint32_t hph = 0;
+        bool ok = true;
+        const int chunks = (int)(halo_bytes / 16);
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            for (int ks = 0; ks < p.kslabs; ks++) {
+                /* the block was written by TMA: wait on its own barrier first (visibility), then for the MMAs that read it */
+                if (!mbar_wait_warp(hfull(hs), hph, abort_flag, p.status, 10)) { ok = false; break; }
+                if (!mbar_wait_warp(split_go(hs), hph, abort_flag, p.status, 11)) { ok = false; break; }
+                uint4 *blk = reinterpret_cast<uint4 *>(gen + hs * SWAP_HALO_SLOT);
+                for (int i = sw * 32 + lane; i < chunks; i += SWAP_SPLIT_WARPS * 32) {
+                    uint4 v = blk[i];
+                    v.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(v.x & 0xffffe000u));
+                    v.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(v.y & 0xffffe000u));
+                    v.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(v.z & 0xffffe000u));
+                    v.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(v.w & 0xffffe000u));
+                    blk[i] = v;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(split_done(hs));
+                if (++hs == SWAP_NH) { hs = 0; hph ^= 1u; }
+            }
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -838,6 +890,7 @@ struct dRk_TensorConvPlan {
     int swap;           /* 1: k_umma_conv_swap (channels on M, 256 pixels on N) for Cout <= 128 */
     int first;          /* 1: k_umma_conv_first (Cin <= 4: patches gathered by producer warps, no tensor maps) */
     int pair;           /* 1: k_umma_conv_pair (Cout <= 64: two output rows stacked on M); mapA = odd input rows, mapA2 = even */
+    int x3;             /* 1: k_umma_conv_swap<true>, FP32-accurate three-pass evaluation; mapA2 = the filters' low parts */
     CUtensorMap mapA2;
     const float *in, *wT;
     int sms;
@@ -1213,6 +1266,87 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     return pl;
 }
 
+/*
+ * FP32-accurate 3x3 convolution on the tensor cores (see k_umma_conv_swap<true>): stride 1, Cin % 4 == 0, Cin >= 8,
+ * Cout % 4 == 0, Cout >= 16, any image size.  wT2 holds the filters [Cout][9*CinPad] (as dRk_tensor_conv_pack_weights writes
+ * them for the transposed kernel) followed by their low parts in the same layout.
+ */
+extern "C" int dRk_tensor_conv_x3_supported(int W, int H, int Cin, int Cout)
+{
+    int P, TW, TH;
+    return dRk_tensor_conv_supported(W, H, Cin, Cout, 3, 3) && Cin >= 8 && swap_geometry(W, H, 0, &P, &TW, &TH) > 0.0;
+}
+
+extern "C" size_t dRk_tensor_conv_x3_packed_floats(int Cin, int Cout) { return (size_t)2 * Cout * 9 * ((Cin + BK - 1) / BK * BK); }
+
+extern "C" int dRk_tensor_conv_x3_pack_weights(const float *w, float *dst, int Cin, int Cout)
+{
+    if (!w || !dst || Cin <= 0 || Cout <= 0) return -1;
+    const size_t cp = (size_t)(Cin + BK - 1) / BK * BK, half = (size_t)Cout * 9 * cp;
+    memset(dst, 0, 2 * half * sizeof(float));
+    for (int c = 0; c < Cin; c++)
+        for (int o = 0; o < Cout; o++)
+            for (int t = 0; t < 9; t++) {
+                const float v = w[((size_t)c * Cout + o) * 9 + t];
+                uint32_t bits;
+                memcpy(&bits, &v, 4);
+                bits &= 0xffffe000u;                        /* what a kind::tf32 MMA reads of v */
+                float hi;
+                memcpy(&hi, &bits, 4);
+                dst[(size_t)o * 9 * cp + (size_t)t * cp + c] = v;
+                dst[half + (size_t)o * 9 * cp + (size_t)t * cp + c] = v - hi;
+            }
+    return 0;
+}
+
+extern "C" dRk_TensorConvPlan *dRk_tensor_conv_x3_plan(const float *in, const float *wT2, const float *bias, float *out, int n, int W, int H,
+                                                       int Cin, int Cout, int act, int ldo, int coff, int fuse_pool2, int *status)
+{
+    if (n <= 0 || !dRk_tensor_conv_x3_supported(W, H, Cin, Cout)) return NULL;
+    if (fuse_pool2 && (fuse_pool2 != 1 || (W & 1) || (H & 1))) return NULL;
+    if (ldo % 4 || coff % 4 || ((uintptr_t)out % 16) || ((uintptr_t)in % 16) || ((uintptr_t)wT2 % 16) || (bias && ((uintptr_t)bias % 16))) return NULL;
+    PFN_encodeTiled enc = get_encode();
+    if (!enc) return NULL;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    dRk_TensorConvPlan *pl = (dRk_TensorConvPlan *)calloc(1, sizeof(dRk_TensorConvPlan));
+    if (!pl) return NULL;
+    UmmaParams &p = pl->p;
+    pl->in = in; pl->wT = wT2; pl->sms = sms; pl->swap = 1; pl->x3 = 1; pl->BN = BM;
+    p.n = n; p.W = W; p.H = H; p.Cin = Cin; p.Cout = Cout;
+    p.CinPad = (Cin + BK - 1) / BK * BK;
+    p.taps = 9; p.kw = 3; p.pad = 1; p.kslabs = p.CinPad / BK;
+    p.bias = bias; p.out = out; p.ldo = ldo; p.coff = coff; p.act = act; p.status = status; p.pool = fuse_pool2 ? 1 : 0;
+    p.ksplit = 1; p.kper = p.kslabs; p.S = 1;
+    swap_geometry(W, H, fuse_pool2 ? 1 : 0, &p.P, &p.TW, &p.TH);
+    p.ncols = p.P * p.TH;
+    p.tiles_x = (W + p.TW - 1) / p.TW; p.tiles_y = (H + p.TH - 1) / p.TH;
+    p.total_sub = (long long)n * p.tiles_x * p.tiles_y;
+    p.m_tiles = (int)p.total_sub;
+    p.n_tiles = (Cout + BM - 1) / BM;
+    const cuuint32_t ones[4] = {1, 1, 1, 1};
+    const cuuint64_t dims[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)n};
+    const cuuint64_t strides[3] = {(cuuint64_t)Cin * 4, (cuuint64_t)W * Cin * 4, (cuuint64_t)H * W * Cin * 4};
+    const cuuint32_t box[4] = {BK, (cuuint32_t)p.P, (cuuint32_t)(p.TH + 2), 1};
+    /* FLOAT32 maps: TMA must deliver the bits unchanged, the split into high and low parts happens in the kernel */
+    CUresult r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void *)in, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    const cuuint64_t K = (cuuint64_t)9 * p.CinPad;
+    const cuuint64_t wdims[2] = {K, (cuuint64_t)Cout}, wstr[1] = {K * 4};
+    const cuuint32_t wbox[2] = {BK, BM};
+    if (r == CUDA_SUCCESS)
+        r = enc(&pl->mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)wT2, wdims, wstr, wbox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS)
+        r = enc(&pl->mapA2, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)(wT2 + (size_t)Cout * K), wdims, wstr, wbox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { fprintf(stderr, "tensor conv x3 plan: tensor map rejected (%d)\n", (int)r); free(pl); return NULL; }
+    const long long tiles = (long long)p.m_tiles * p.n_tiles;
+    pl->grid = (int)(tiles < sms ? tiles : sms);
+    return pl;
+}
+
 /* The kernel and block geometry of a built plan, in the numbering of dRk_tensor_conv_describe. */
 extern "C" int dRk_tensor_conv_plan_describe(const dRk_TensorConvPlan *pl, int *P, int *TW, int *TH, int *ncols)
 {
@@ -1253,11 +1387,13 @@ extern "C" int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *pl)
         static bool attr_done[DRK_MAX_DEVICES];
         const int dev = current_device();
         if (!attr_done[dev]) {
-            cudaError_t e = cudaFuncSetAttribute(k_umma_conv_swap, cudaFuncAttributeMaxDynamicSharedMemorySize, SWAP_SMEM);
+            cudaError_t e = cudaFuncSetAttribute(k_umma_conv_swap<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SWAP_SMEM);
+            if (e == cudaSuccess) e = cudaFuncSetAttribute(k_umma_conv_swap<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SWAP_SMEM);
             if (e != cudaSuccess) return (int)e;
             attr_done[dev] = true;
         }
-        drk_launch_dep(k_umma_conv_swap, dim3(pl->grid), dim3(SWAP_THREADS), SWAP_SMEM, st, pl->mapA, pl->mapB, pl->p);
+        if (pl->x3) drk_launch_dep(k_umma_conv_swap<true>, dim3(pl->grid), dim3(SWAP_THREADS(1)), SWAP_SMEM, st, pl->mapA, pl->mapB, pl->mapA2, pl->p);
+        else drk_launch_dep(k_umma_conv_swap<false>, dim3(pl->grid), dim3(SWAP_THREADS(0)), SWAP_SMEM, st, pl->mapA, pl->mapB, pl->mapB, pl->p);
         DRK_COUNT_LAUNCH();
         return DRK_LAUNCH_RESULT();
     }

@@ -12,7 +12,9 @@ extern "C" {
 #endif
 enum dR_MathMode {
     DR_MATH_FP32 = 0,   /* every contraction in FP32 FFMA (validation-grade, the default) */
-    DR_MATH_TF32 = 1    /* dense contractions on the tcgen05 tensor cores with TF32 inputs, FP32 accumulate */
+    DR_MATH_TF32 = 1,   /* dense contractions on the tcgen05 tensor cores with TF32 inputs, FP32 accumulate */
+    DR_MATH_FP32_TENSOR = 2 /* FP32-accurate results from the tensor cores: 3x3 layers evaluate every product in three TF32 passes
+                               (high x high, high x low, low x high parts; error bound of the FP32 class), the rest runs DR_MATH_FP32 */
 };
 enum dR_InterfaceLayout {
     DR_LAYOUT_CHW = 0,  /* reference layout of feed/output buffers: [C][H][W] per image */
@@ -35,7 +37,7 @@ gboolean dR_setDevice(dR_Graph *net, gint ordinal);
 gboolean dR_synchronize(dR_Graph *net);
 /* dR_apply bracketed by events on the graph's own stream; returns milliseconds (<0 on failure). */
 gdouble dR_applyTimed(dR_Graph *net, gint iterations);
-/* Kernel family / arithmetic a prepared convolution node runs (dR_ConvAlgo, 0/1). */
+/* Kernel family / arithmetic a prepared convolution node runs (dR_ConvAlgo; 0 FP32 FFMA, 1 TF32 tensor cores, 2 three-pass TF32). */
 gint dR_getConvAlgo(dR_Node *node);
 gint dR_getConvTensor(dR_Node *node);
 /* The tensor-core kernel a convolution node's launches run once it has been applied (numbering and geometry of

@@ -323,3 +323,73 @@ def test_autotuner_may_choose_among_the_tensor_variants():
         dr.feed_data(f, x)
         got = dr.apply(g)[0].reshape(8, 128, 28, 28)
     assert rel_err(got[:1], ref) <= TOL_TF32
+
+
+X3_SHAPES = [
+    # name, n, cin, cout, h, w, pool
+    ("x3_32_64_20x30", 2, 32, 64, 20, 30, False),
+    ("x3_odd_13x17", 3, 64, 192, 17, 13, False),
+    ("x3_swap_odd", 40, 8, 136, 29, 27, False),            # odd image, Cout ends inside a warp, one zero-filled K slab
+    ("x3_16_16", 2, 16, 16, 12, 12, False),
+    ("x3_48_72_pool", 2, 48, 72, 28, 30, True),
+    ("x3_pool_p30", 6, 16, 64, 56, 56, True),
+    ("x3_conv3_2", 40, 256, 256, 56, 56, False),           # the benchmark's geometries at full depth
+    ("x3_conv5_pool", 64, 512, 512, 14, 14, True),
+    ("x3_conv1_2", 4, 64, 64, 224, 224, True),
+]
+
+
+@pytest.mark.parametrize("name,n,cin,cout,h,w,pool", X3_SHAPES)
+def test_fp32_accurate_tensor_conv_matches_oracle_at_the_fp32_bound(name, n, cin, cout, h, w, pool):
+    """math = 'fp32x3': 3x3 layers on the tensor cores with every product split into high and low TF32 parts (three passes).
+    The bound is the exact-FP32 kernels' 1e-4 * max|ref|, thirty times tighter than the TF32 class."""
+    x, wt, b = cases.conv_case(name, n, cin, cout, h, w, 3, True)
+    with dr.Environment() as env:
+        g = env.create_graph("CHW")
+        g.batch = n
+        g.math = "fp32x3"
+        f = dr.feed_node(g, [cin, h, w])
+        c = conv_build(wt, b, 1, 1)(g, [f])
+        o = dr.Pooling(c, "max", [1, 2, 2, 1], [1, 2, 2, 1]) if pool else c
+        dr.mark_as_output(o)
+        dr.prepare(g)
+        assert dr.lib.dR_getConvAlgo(c.ptr) == dr.CONV_ALGO["tensor"] and dr.lib.dR_getConvTensor(c.ptr) == 2
+        dr.feed_data(f, x)
+        got = dr.apply(g)[0]
+        launches = dr.lib.dR_getLaunchCount(g.ptr)
+        assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    ho, wo = (h // 2, w // 2) if pool else (h, w)
+    got = got.reshape(n, cout, ho, wo)
+    assert launches == 3                                # feed layout, convolution (+ pool in its epilogue), output layout
+    worst = 0.0
+    for i in sorted({0, n // 2, n - 1}):
+        ref = oracle.conv2d(x[i:i + 1], wt, b, (1, 1), 1)
+        if pool:
+            ref = oracle.pool(ref, (2, 2, 1), (2, 2, 1), 0)
+        worst = max(worst, rel_err(got[i:i + 1], ref))
+    print("fp32x3 %s: max rel err %.2e" % (name, worst))
+    assert worst <= 1e-4
+    assert worst <= 2e-5, "three-pass TF32 should be far inside the FP32 bound; a larger error means an operand split is off"
+
+
+def test_fp32_accurate_tensor_mode_on_a_whole_network():
+    """VGG-style network in 'fp32x3' mode: 3x3 layers with >= 8 input channels on the tensor cores, first layer / FC / pooling /
+    softmax on the FP32 kernels; probabilities against the exact-FP32 run at the FP32 class's whole-network bound."""
+    imgs = nets.synthetic_images("x3_net", 4, 64)
+    outs, tensor_layers = {}, {}
+    for math in ("fp32", "fp32x3"):
+        with dr.Environment() as env:
+            g = env.create_graph("HWC")
+            g.batch = 4
+            g.math = math
+            x, out = nets.vgg16(g, size=64, width_div=2, fc_dims=(1024, 1024, 200))
+            dr.mark_as_output(out)
+            dr.prepare(g)
+            dr.feed_data(x, imgs)
+            outs[math] = dr.apply(g)[0].reshape(4, -1)
+            tensor_layers[math] = [dr.lib.dR_getConvTensor(nd.ptr) for nd in g.nodes if nd.desc == "Conv2D"]
+            assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    assert tensor_layers["fp32"] == [0] * 13
+    assert tensor_layers["fp32x3"] == [0] + [2] * 12
+    assert np.array_equal(outs["fp32"].argmax(1), outs["fp32x3"].argmax(1))
+    assert rel_err(outs["fp32x3"], outs["fp32"]) <= 5e-4
