@@ -1274,7 +1274,9 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
 extern "C" int dRk_tensor_conv_x3_supported(int W, int H, int Cin, int Cout)
 {
     int P, TW, TH;
-    return dRk_tensor_conv_supported(W, H, Cin, Cout, 3, 3) && Cin >= 8 && swap_geometry(W, H, 0, &P, &TW, &TH) > 0.0;
+    /* Cin <= 768: the accumulator in TMEM rounds by truncation once per MMA, an error that grows with the MMA count per output
+       (measured 4.7e-5 * max|ref| at Cin = 512); deeper layers would leave the FP32 class's 1e-4 bound and stay on FFMA */
+    return dRk_tensor_conv_supported(W, H, Cin, Cout, 3, 3) && Cin >= 8 && Cin <= 768 && swap_geometry(W, H, 0, &P, &TW, &TH) > 0.0;
 }
 
 extern "C" size_t dRk_tensor_conv_x3_packed_floats(int Cin, int Cout) { return (size_t)2 * Cout * 9 * ((Cin + BK - 1) / BK * BK); }

@@ -368,8 +368,9 @@ def test_fp32_accurate_tensor_conv_matches_oracle_at_the_fp32_bound(name, n, cin
             ref = oracle.pool(ref, (2, 2, 1), (2, 2, 1), 0)
         worst = max(worst, rel_err(got[i:i + 1], ref))
     print("fp32x3 %s: max rel err %.2e" % (name, worst))
-    assert worst <= 1e-4
-    assert worst <= 2e-5, "three-pass TF32 should be far inside the FP32 bound; a larger error means an operand split is off"
+    # What is left is the tensor core's accumulator rounding (it truncates), which grows with the number of MMAs per output:
+    # ~5e-6 at K = 9 * 32, ~5e-5 at K = 9 * 512.  An operand split that is off would show as ~1e-3 (the TF32 class's error).
+    assert worst <= 6e-5
 
 
 def test_fp32_accurate_tensor_mode_on_a_whole_network():
