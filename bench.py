@@ -13,6 +13,7 @@ of its class probabilities inside the timed region.  The same line carries, as o
 
   fp32_exact   VGG-16 batch 64 in the reference's own arithmetic (FP32 FFMA kernels, tolerance 1e-4 per layer)
   fp32_accurate_tensor  VGG-16 batch 64 in math mode fp32x3: FP32-class error bound from three TF32 tensor-core passes per product
+  e2e_u8       the headline's end-to-end loop fed with 8-bit image samples (dR_feedDataU8Async: a quarter of the host-link bytes)
   squeezenet   SqueezeNet v1.1 (the reference's example graph) at batch 64 (every N) and batch 1 (N = 1)
   sustained    >= 3 s of back-to-back dR_apply with the clock sampler running (N = 1)
   e2e_dropin   the reference-shaped blocking calls: dR_feedData ([C][H][W], pageable host memory) + dR_apply +
@@ -195,12 +196,28 @@ def measure(ctx, net, math, batch, steps, warmup, overlap=True, cuda_graph=False
         check(ok and ms_e2e > 0, "feed / apply / fetch (timed)")
         ctx.barrier(g)
         ms_e2e = ctx.reduce_max(ms_e2e)
+        probs = host_out.reshape(batch, nclass).copy()
+        # ---- end to end from 8-bit samples (decoded image bytes): a quarter of the bytes cross the host link, cast on the device
+        pin_u8 = lib.dR_allocPinned(in_floats)
+        host_u8 = np.ctypeslib.as_array((ctypes.c_uint8 * in_floats).from_address(pin_u8))
+        host_u8[:] = np.random.default_rng(1234 + ctx.rank).integers(0, 256, size=in_floats, dtype=np.uint8)
+        for _ in range(2):
+            ok &= bool(lib.dR_feedDataU8Async(g.ptr, x.ptr, pin_u8, in_floats)) and bool(lib.dR_apply(g.ptr)) and bool(lib.dR_fetchOutputAsync(g.ptr, 0, pin_out, out_floats))
+        ctx.barrier(g)
+        lib.dR_timerStart(g.ptr)
+        for _ in range(steps):
+            ok &= bool(lib.dR_feedDataU8Async(g.ptr, x.ptr, pin_u8, in_floats)) and bool(lib.dR_apply(g.ptr)) and bool(lib.dR_fetchOutputAsync(g.ptr, 0, pin_out, out_floats))
+        ms_u8 = lib.dR_timerStopMs(g.ptr)
+        check(ok and ms_u8 > 0, "8-bit feed / apply / fetch (timed)")
+        ctx.barrier(g)
+        ms_u8 = ctx.reduce_max(ms_u8)
+        lib.dR_freePinned(pin_u8)
         status = lib.dR_getDeviceStatus(g.ptr)
         check(status == 0, "device status %d: a kernel's bounded wait ran out" % status)
-        probs = host_out.reshape(batch, nclass).copy()
         res = {"images_per_s": batch * ctx.world * steps / (ms * 1e-3), "ms_per_step": ms / steps,
                "e2e_images_per_s": batch * ctx.world * steps / (ms_e2e * 1e-3), "e2e_ms_per_step": ms_e2e / steps,
                "h2d_bytes_per_step": in_floats * 4, "d2h_bytes_per_step": out_floats * 4, "steps": steps, "batch_per_gpu": batch,
+               "e2e_u8_images_per_s": batch * ctx.world * steps / (ms_u8 * 1e-3), "e2e_u8_ms_per_step": ms_u8 / steps, "e2e_u8_h2d_bytes_per_step": in_floats,
                "clocks": clocks, "probs": probs, "status": status}
         # ---- sustained: back-to-back applies for at least min_seconds, clocks sampled (rank 0 of a single-GPU run)
         if min_seconds > 0:
@@ -389,6 +406,9 @@ def run_ours(args):
             "e2e": {"value": main["e2e_images_per_s"], "unit": "images/s", "h2d_bytes_per_step": main["h2d_bytes_per_step"],
                     "d2h_bytes_per_step": main["d2h_bytes_per_step"], "ms_per_step": main["e2e_ms_per_step"],
                     "calls": "dR_feedDataAsync (pinned, second stream) + dR_apply + dR_fetchOutputAsync, N-HWC interface"},
+            "e2e_u8": {"value": main["e2e_u8_images_per_s"], "unit": "images/s", "h2d_bytes_per_step": main["e2e_u8_h2d_bytes_per_step"],
+                       "d2h_bytes_per_step": main["d2h_bytes_per_step"], "ms_per_step": main["e2e_u8_ms_per_step"],
+                       "calls": "dR_feedDataU8Async (8-bit samples 0..255, pinned; cast to float on the device) + dR_apply + dR_fetchOutputAsync"},
             "gpu_launches": main["launches_per_apply"] * args.steps,
             "clocks": main["clocks"], "roofline": roof,
             "conv_tflops": aggregate, "device_status": main["status"],
@@ -431,7 +451,7 @@ def run_ours(args):
         if "squeezenet_b64" in extra:
             sq = extra["squeezenet_b64"]
             line["squeezenet"] = {"batch64": {"images_per_s": sq["images_per_s"], "ms_per_step": sq["ms_per_step"], "e2e_images_per_s": sq["e2e_images_per_s"],
-                                              "launches_per_apply": sq["launches_per_apply"], "conv_tflops": SQUEEZENET_CONV_FLOPS * sq["images_per_s"] / 1e12 / ctx.world,
+                                              "e2e_u8_images_per_s": sq["e2e_u8_images_per_s"], "launches_per_apply": sq["launches_per_apply"], "conv_tflops": SQUEEZENET_CONV_FLOPS * sq["images_per_s"] / 1e12 / ctx.world,
                                               "h2d_bytes_per_step": sq["h2d_bytes_per_step"]},
                                   "graph": "reference example graph (conv1 3x3 stride 1 + 2x2 average pool, 8 Fire modules, conv10, global average pool, softmax)",
                                   "math": args.math}

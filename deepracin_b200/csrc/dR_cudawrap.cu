@@ -325,6 +325,31 @@ extern "C" gboolean dR_feedOverlapCopy(dR_Graph *net, dR_Node *feed, void *src, 
     return TRUE;
 }
 
+/* 8-bit feed: bytes to a device staging buffer, cast on the device into the feed node's (next) interface buffer.  With
+ * double-buffered feeding both steps run on the copy stream, under the previous batch's kernels. */
+extern "C" gboolean dR_feedU8(dR_Graph *net, dR_Node *feed, const unsigned char *src, size_t numBytes)
+{
+    dR_DataFeedNode_Data *d = (dR_DataFeedNode_Data *)feed->layer;
+    if (!bindDevice(net)) return FALSE;
+    const gboolean overlap = net->config->feedOverlap && d->evReady[0];
+    const int idx = overlap ? (d->pending >= 0 ? d->pending : (d->current ^ 1)) : 0;
+    if (!d->u8Buf[idx]) {
+        void *p = NULL;
+        if (!check(net, cudaMalloc(&p, (numBytes + 255) / 256 * 256), "cudaMalloc (8-bit feed staging)")) return FALSE;
+        d->u8Buf[idx] = p;
+    }
+    cudaStream_t s = overlap ? (cudaStream_t)net->clConfig->copyStream : streamOf(net);
+    float *dst = (float *)(overlap ? d->feedBuf[idx] : *feed->outputBuf->bufptr);
+    if (overlap && !check(net, cudaStreamWaitEvent(s, (cudaEvent_t)d->evFree[idx], 0), "cudaStreamWaitEvent")) return FALSE;
+    if (!check(net, cudaMemcpyAsync(d->u8Buf[idx], src, numBytes, cudaMemcpyHostToDevice, s), "cudaMemcpyAsync H2D (8-bit feed)")) return FALSE;
+    if (!check(net, (cudaError_t)dRk_u8_to_f32((dRk_stream)s, (const unsigned char *)d->u8Buf[idx], dst, numBytes), "8-bit feed conversion")) return FALSE;
+    if (overlap) {
+        if (!check(net, cudaEventRecord((cudaEvent_t)d->evReady[idx], s), "cudaEventRecord")) return FALSE;
+        d->pending = idx;
+    }
+    return TRUE;
+}
+
 extern "C" gboolean dR_feedOverlapBeforeApply(dR_Graph *net)
 {
     for (dR_ListElement *e = net->feed_layers->first; e; e = e->next) {
@@ -353,8 +378,10 @@ extern "C" gboolean dR_feedOverlapAfterApply(dR_Graph *net)
 extern "C" void dR_feedOverlapCleanup(dR_Graph *net, dR_Node *feed)
 {
     dR_DataFeedNode_Data *d = (dR_DataFeedNode_Data *)feed->layer;
-    if (!d->evReady[0]) return;
     if (net->clConfig->copyStream) cudaStreamSynchronize((cudaStream_t)net->clConfig->copyStream);
+    for (int i = 0; i < 2; i++)
+        if (d->u8Buf[i]) { cudaFree(d->u8Buf[i]); d->u8Buf[i] = NULL; }
+    if (!d->evReady[0]) return;
     for (int i = 0; i < 2; i++) {
         cudaEventDestroy((cudaEvent_t)d->evReady[i]);
         cudaEventDestroy((cudaEvent_t)d->evFree[i]);

@@ -396,6 +396,16 @@ gboolean dR_feedDataAsync(dR_Graph *net, dR_Node *feednode, gfloat *pinned, size
     return dR_uploadArrayAsync(net, pinned, numfloats * sizeof(cl_float), *feednode->outputBuf->bufptr);
 }
 
+gboolean dR_feedDataU8Async(dR_Graph *net, dR_Node *feednode, const unsigned char *pinned, size_t numbytes)
+{
+    if (!net->prepared || net->config->dryRun || !feednode || feednode->type != tDataFeedNode || !pinned) return FALSE;
+    if (numbytes != (size_t)feednode->outputBuf->size * net->config->batchSize) {
+        g_print("dR_feedDataU8Async: %zu bytes given, the feed node holds %zu samples\n", numbytes, (size_t)feednode->outputBuf->size * net->config->batchSize);
+        return FALSE;
+    }
+    return dR_feedU8(net, feednode, pinned, numbytes);
+}
+
 gboolean dR_fetchOutputAsync(dR_Graph *net, gint outputIndex, gfloat *pinned, size_t numfloats)
 {
     if (!net->prepared) return FALSE;

@@ -41,6 +41,33 @@ static int transpose_launch(dRk_stream s, const float *src, float *dst, int n, i
     return DRK_LAUNCH_RESULT();
 }
 
+/* 8-bit image samples -> float, element by element (the layout stays what it is): out[i] = (float)in[i].  The reference's
+ * examples do this cast on the host while they reorder the decoded PNG rows (examples/vgg16/vgg_deployed.c:153-157); doing it on
+ * the device lets the host copy a quarter of the bytes.  16 samples per thread per step: one 128-bit load, four 128-bit stores. */
+__global__ void k_u8_to_f32(const unsigned char *__restrict__ in, float *__restrict__ out, size_t count)
+{
+    drk_dep_trigger();
+    drk_dep_wait();
+    const size_t vec = count / 16;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < vec; i += (size_t)gridDim.x * blockDim.x) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(in) + i);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+        float4 *o = reinterpret_cast<float4 *>(out) + i * 4;
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            o[k] = make_float4((float)(w[k] & 0xffu), (float)((w[k] >> 8) & 0xffu), (float)((w[k] >> 16) & 0xffu), (float)(w[k] >> 24));
+    }
+    for (size_t i = vec * 16 + (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) out[i] = (float)in[i];
+}
+
+extern "C" int dRk_u8_to_f32(dRk_stream s, const unsigned char *in, float *out, size_t count)
+{
+    if (!in || !out || count == 0 || ((uintptr_t)in % 16) || ((uintptr_t)out % 16)) return -1;
+    k_u8_to_f32<<<drk_blocks(count / 16 + 1, 256, 148u * 16u), 256, 0, drk_stream(s)>>>(in, out, count);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}
+
 extern "C" int dRk_chw_to_hwc(dRk_stream s, const float *src, float *dst, int n, int W, int H, int C)
 {
     return transpose_launch(s, src, dst, n, C, W * H);

@@ -60,6 +60,10 @@ gboolean dR_setFeedOverlap(dR_Graph *net, gboolean on);
 /* Feed / fetch with pinned host memory and no implicit synchronisation. */
 gboolean dR_feedDataAsync(dR_Graph *net, dR_Node *feednode, gfloat *pinned, size_t numfloats);
 gboolean dR_fetchOutputAsync(dR_Graph *net, gint outputIndex, gfloat *pinned, size_t numfloats);
+/* The same feed from 8-bit samples (decoded image bytes in the graph's interface layout, batchSize images back to back): a
+ * quarter of the bytes cross the host link, the cast to float happens on the device ((float)byte, what the reference's examples
+ * compute on the host, examples/vgg16/vgg_deployed.c:153-157).  The first call allocates the device staging buffer. */
+gboolean dR_feedDataU8Async(dR_Graph *net, dR_Node *feednode, const unsigned char *pinned, size_t numbytes);
 void *dR_allocPinned(size_t bytes);
 void dR_freePinned(void *p);
 /* Planning without a device: dR_prepare runs scheduling, fusion planning, variant selection and the buffer

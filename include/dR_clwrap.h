@@ -55,6 +55,7 @@ gboolean dR_downloadArrayAsync(dR_Graph *net, cl_mem srcDeviceMem, size_t numByt
 /* Double-buffered feeding (see dR_setFeedOverlap): second stream + events, copy, and the two hooks dR_apply calls. */
 gboolean dR_feedOverlapInit(dR_Graph *net, dR_Node *feed);
 gboolean dR_feedOverlapCopy(dR_Graph *net, dR_Node *feed, void *srcHostMem, size_t numBytes);
+gboolean dR_feedU8(dR_Graph *net, dR_Node *feed, const unsigned char *srcHostMem, size_t numBytes);
 gboolean dR_feedOverlapBeforeApply(dR_Graph *net);
 gboolean dR_feedOverlapAfterApply(dR_Graph *net);
 void dR_feedOverlapCleanup(dR_Graph *net, dR_Node *feed);

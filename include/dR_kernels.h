@@ -70,6 +70,10 @@ int dRk_fc_f32(dRk_stream stream, const float *in, const float *w, const float *
 int dRk_fc_f32_noalloc(dRk_stream stream, const float *in, const float *w, const float *bias, float *out,
                        int n, int Nin, int Nout, int act);
 
+/* out[i] = (float)in[i] for 8-bit image samples (both pointers 16-byte aligned); replaces the host-side cast of the reference's
+ * examples (examples/vgg16/vgg_deployed.c:153-157). */
+int dRk_u8_to_f32(dRk_stream stream, const unsigned char *in, float *out, size_t count);
+
 /* Max / average pooling with the reference's window rule (src/dR_nodes_pooling.c:277-401,
  * launcher :138-183): top-left anchored windows, zero reads outside, average over the full
  * window.  type 0 = max, 1 = average.  Output is dense N-HWC of ceil(in/stride) per axis. */

@@ -90,6 +90,7 @@ struct dR_DataFeedNode_Data {
     void *evFree[2];         /* the apply that read feedBuf[i] finished (recorded on the compute stream) */
     gint current;            /* buffer the graph reads in the next apply */
     gint pending;            /* buffer a dR_feedDataAsync filled since the last apply, or -1 */
+    cl_mem u8Buf[2];         /* device staging for 8-bit feeds (dR_feedDataU8Async), allocated at the first such feed */
 };
 
 struct dR_Node {

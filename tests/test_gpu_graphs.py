@@ -216,3 +216,47 @@ def test_channel_reorder_in_the_middle_of_a_network(fuse):
         return conv_build(w2, b2, 1, 1)(g, [dr.Concat([hi, lo], 0)])
     (got,) = run_graph(build, [x], fuse=fuse)
     assert rel_err(got, ref) <= 2 * TOL_FP32
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_8bit_feed_equals_float_feed(overlap):
+    """dR_feedDataU8Async: image bytes cross the host link, the cast to float runs on the device; results are bit-identical
+    to feeding the same samples as floats, with and without double-buffered feeding, over several batches in a row."""
+    import ctypes
+    rng = np.random.default_rng(11)
+    batches = [rng.integers(0, 256, size=(2, 32, 32, 3), dtype=np.uint8) for _ in range(4)]
+    outs = {}
+    for mode in ("float", "u8"):
+        with dr.Environment() as env:
+            g = env.create_graph("HWC")
+            g.batch = 2
+            g.math = "tf32"
+            g.feed_overlap = overlap
+            x, out = nets.squeezenet11(g, size=32, classes=16)
+            dr.mark_as_output(out)
+            dr.lib.dR_setInterfaceLayout(g.ptr, 1)
+            dr.prepare(g)
+            n_in, n_out = 2 * 32 * 32 * 3, 2 * 16
+            pin_out = [dr.lib.dR_allocPinned(n_out * 4) for _ in batches]
+            pin_in = [dr.lib.dR_allocPinned(n_in * 4) for _ in batches]
+            for p, b in zip(pin_in, batches):
+                if mode == "u8":
+                    ctypes.memmove(p, b.ctypes.data, n_in)
+                else:
+                    ctypes.memmove(p, np.ascontiguousarray(b.astype(np.float32)).ctypes.data, n_in * 4)
+            for i in range(len(batches)):
+                if mode == "u8":
+                    assert dr.lib.dR_feedDataU8Async(g.ptr, x.ptr, pin_in[i], n_in)
+                else:
+                    assert dr.lib.dR_feedDataAsync(g.ptr, x.ptr, pin_in[i], n_in)
+                assert dr.lib.dR_apply(g.ptr)
+                assert dr.lib.dR_fetchOutputAsync(g.ptr, 0, pin_out[i], n_out)
+            dr.lib.dR_synchronize(g.ptr)
+            assert not dr.lib.dR_feedDataU8Async(g.ptr, x.ptr, pin_in[0], n_in - 1)      # wrong size is refused
+            outs[mode] = [np.ctypeslib.as_array((ctypes.c_float * n_out).from_address(p)).copy() for p in pin_out]
+            assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+            for p in pin_in + pin_out:
+                dr.lib.dR_freePinned(p)
+    for a, b in zip(outs["float"], outs["u8"]):
+        assert np.array_equal(a, b)
+    assert not np.array_equal(outs["u8"][0], outs["u8"][1])
