@@ -158,7 +158,8 @@ def test_overlapped_feeding_gives_the_same_results_in_order():
             pin_out = [dr.lib.dR_allocPinned(n_out * 4) for _ in batches]
             for p, b in zip(pin_in, batches):
                 # the feed buffer is [C][H][W] per image (reference interface layout)
-                ctypes.memmove(p, np.ascontiguousarray(b.transpose(0, 3, 1, 2)).ctypes.data, n_in * 4)
+                chw = np.ascontiguousarray(b.transpose(0, 3, 1, 2))             # named: it must outlive the copy
+                ctypes.memmove(p, chw.ctypes.data, n_in * 4)
             for i in range(len(batches)):       # no synchronisation between steps
                 assert dr.lib.dR_feedDataAsync(g.ptr, x.ptr, pin_in[i], n_in)
                 assert dr.lib.dR_apply(g.ptr)
@@ -243,7 +244,8 @@ def test_8bit_feed_equals_float_feed(overlap):
                 if mode == "u8":
                     ctypes.memmove(p, b.ctypes.data, n_in)
                 else:
-                    ctypes.memmove(p, np.ascontiguousarray(b.astype(np.float32)).ctypes.data, n_in * 4)
+                    as_float = np.ascontiguousarray(b.astype(np.float32))      # named: it must outlive the copy
+                    ctypes.memmove(p, as_float.ctypes.data, n_in * 4)
             for i in range(len(batches)):
                 if mode == "u8":
                     assert dr.lib.dR_feedDataU8Async(g.ptr, x.ptr, pin_in[i], n_in)
