@@ -276,7 +276,7 @@ def measure_dropin(ctx, steps, warmup, batch=64, math="tf32"):
 
 
 def per_node_profile(dr, lib, g):
-    """One apply with per-kernel events; returns [(kind, ms)] per node."""
+    """One apply with per-kernel events; returns [(kind, ms, output shape WxHxC)] per node."""
     res = []
     lib.dR_config(g.ptr, b"", 1, 0, 1, 0, (g.env.model_path).encode())
     # the C library prints a summary line per apply when profiling; keep stdout clean for the JSON line
@@ -293,7 +293,8 @@ def per_node_profile(dr, lib, g):
         os.close(devnull)
     for node in g.nodes:
         kind = {"Conv2D": "conv", "FullyConnected": "fc", "Pooling": "pool", "Softmax": "softmax"}.get(node.desc, "other")
-        res.append((kind, lib.dR_getNodeGpuMs(node.ptr)))
+        sh = lib.dR_getOutputShape(node.ptr).contents
+        res.append((kind, lib.dR_getNodeGpuMs(node.ptr), "%dx%dx%d" % (sh.s0, sh.s1, sh.s2)))
     lib.dR_config(g.ptr, b"", 1, 0, 0, 0, (g.env.model_path).encode())
     return res
 
@@ -338,6 +339,7 @@ def vgg_roofline(math, batch, prof, peaks, yard):
     """Roofline of the dominant kernel (conv3_2's launch) and of the 13 convolution launches together, from the per-node
     event times of one profiled apply.  Per-launch times are sub-millisecond, so the denominator is the BURST peak."""
     conv_flops, _ = vgg_flops_per_image()
+    prof = [(k, t) for k, t, _ in prof]
     conv_times = [t for kind, t in prof if kind == "conv"]
     conv_ms, n_conv = sum(conv_times), len(conv_times)
     tensor = math == "tf32"
@@ -394,6 +396,9 @@ def run_ours(args):
         conv_share = None
         if args.net == "vgg16":
             roof, aggregate, conv_share = vgg_roofline(args.math, batch, main["profile"], peaks, yard)
+        else:
+            roof["ms_per_layer"] = [[k, sh, round(t, 4)] for k, t, sh in main["profile"] if t > 0]      # launch order; fused nodes launch nothing
+            roof["note"] = "SqueezeNet: per-node event times of one profiled apply (each carries ~5 us of event overhead); no single dominant kernel"
         klass = "TF32 tensor-core class (fp32 storage, TF32 operands, FP32 accumulate)" if tensor else "exact FP32 class (FFMA)"
         line = {
             "metric": "images/sec", "value": main["images_per_s"], "unit": "images/s", "n_gpus": ctx.world, "steps": args.steps, "warmup": args.warmup,

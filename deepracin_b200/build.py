@@ -52,7 +52,7 @@ def build_library(force=False, verbose=False):
         with ThreadPoolExecutor(max_workers=8) as ex:
             logs = list(ex.map(lambda j: _compile(j[0], j[1], verbose), jobs))
     if jobs or not os.path.exists(OUT):
-        cmd = [NVCC, *ARCH, "-shared", "-o", OUT, *objs, "-lcudart"]
+        cmd = [NVCC, *ARCH, "-shared", "-o", OUT, *objs, "-lcudart", "-lpthread"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n%s\n%s" % (r.stdout, r.stderr))
