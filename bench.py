@@ -342,7 +342,7 @@ def vgg_roofline(math, batch, prof, peaks, yard):
     prof = [(k, t) for k, t, _ in prof]
     conv_times = [t for kind, t in prof if kind == "conv"]
     conv_ms, n_conv = sum(conv_times), len(conv_times)
-    tensor = math == "tf32"
+    tensor = math in ("tf32", "fp32x3")
     if tensor:
         peak, peak_sus = peaks["bf16"] / 2.0, peaks["bf16_sustained"] / 2.0
         peak_src = "%s bf16 cuBLAS burst / 2 (TF32 issues at half the bf16 rate; MEASURED_PEAKS.json holds no TF32 figure)" % peaks["source"]
@@ -399,11 +399,12 @@ def run_ours(args):
         else:
             roof["ms_per_layer"] = [[k, sh, round(t, 4)] for k, t, sh in main["profile"] if t > 0]      # launch order; fused nodes launch nothing
             roof["note"] = "SqueezeNet: per-node event times of one profiled apply (each carries ~5 us of event overhead); no single dominant kernel"
-        klass = "TF32 tensor-core class (fp32 storage, TF32 operands, FP32 accumulate)" if tensor else "exact FP32 class (FFMA)"
+        klass = ("TF32 tensor-core class (fp32 storage, TF32 operands, FP32 accumulate)" if tensor else
+                 "FP32-accurate tensor-core class (three TF32 passes per product)" if args.math == "fp32x3" else "exact FP32 class (FFMA)")
         line = {
             "metric": "images/sec", "value": main["images_per_s"], "unit": "images/s", "n_gpus": ctx.world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": main["ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "tf32" if tensor else "f32", "data": "synthetic",
+            "dtype": "tf32" if tensor else ("3xtf32" if args.math == "fp32x3" else "f32"), "data": "synthetic",
             "config": {"workload": "%s inference, %s, batch %d per GPU, 224x224x3 uniform[0,255]-128 inputs, seeded He-normal weights; "
                                    "inputs larger than L2 (no flush)" % ("VGG-16" if args.net == "vgg16" else "SqueezeNet v1.1 (reference example graph)", klass, batch),
                        "global_batch": batch * ctx.world, "parallelism": "replicas x%d (batch sharded, no collective)" % ctx.world,
@@ -584,7 +585,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--net", default="vgg16", choices=["vgg16", "squeezenet"])
     ap.add_argument("--batch", type=int, default=64)
-    ap.add_argument("--math", default=os.environ.get("DR_BENCH_MATH", "tf32"), choices=["fp32", "tf32"])
+    ap.add_argument("--math", default=os.environ.get("DR_BENCH_MATH", "tf32"), choices=["fp32", "tf32", "fp32x3"])
     ap.add_argument("--autotune", type=int, default=-1, help="time conv variants at prepare; default: only in fp32 mode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=20.0)

@@ -574,6 +574,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
 #define SWAP_NH 2
 #define SWAP_W_BYTES (BM * BK * 4)                     /* filter stage: 128 rows x 128 B */
 #define SWAP_NW 9
+#define SWAP_NW_X3 6                                   /* X3 mode: 2 blocks + the lo(x) buffer + 6 filter stages = 210 KB */
 #define SWAP_EPI_WARPS 8
 #define SWAP_SPLIT_WARPS 4                             /* X3 mode only */
 #define SWAP_THREADS(X3) ((2 + SWAP_EPI_WARPS + ((X3) ? SWAP_SPLIT_WARPS : 0)) * 32)
@@ -587,7 +588,7 @@ k_umma_conv_halo(const __grid_constant__ CUtensorMap mapA, const __grid_constant
  * the product, so a layer stays inside the exact-FP32 kernels' 1e-4 bound at three times the direct TF32 kernel's MMA count
  * instead of the FFMA rate.  The tensor maps are plain FLOAT32 here (no rounding by TMA): passes 0 and 1 read the haloed
  * block as loaded (the MMA ignores the low bits = hi(x)) against the filters W and a precomputed lo(W) tensor (mapWlo);
- * then four extra warps replace the block in place by lo(x) = x - hi(x) -- exact in FP32 -- and pass 2 multiplies it with W.
+ * meanwhile four extra warps write lo(x) = x - hi(x) -- exact in FP32 -- into a buffer of its own, which pass 2 multiplies with W.
  */
 template <bool X3>
 __global__ void __launch_bounds__(SWAP_THREADS(X3), 1)
@@ -599,20 +600,23 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
     const uint32_t raw = smem_u32(smem_raw);
     const uint32_t base = (raw + 1023u) & ~1023u;
     uint8_t *gen = smem_raw + (base - raw);
-    const uint32_t h_base = base, w_base = base + SWAP_NH * SWAP_HALO_SLOT;
-    const uint32_t bars = w_base + SWAP_NW * SWAP_W_BYTES;
-    constexpr int NBARS = 4 * SWAP_NH + 2 * SWAP_NW + 5;
-    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + SWAP_NH * SWAP_HALO_SLOT + SWAP_NW * SWAP_W_BYTES + 8 * NBARS);
+    /* X3: one more block-sized buffer holds lo(x) of the slab in work, the filter ring is shorter to make room for it */
+    constexpr int NW = X3 ? SWAP_NW_X3 : SWAP_NW;
+    constexpr int XLO_BYTES = X3 ? SWAP_HALO_SLOT : 0;
+    const uint32_t h_base = base, xlo_base = base + SWAP_NH * SWAP_HALO_SLOT, w_base = xlo_base + XLO_BYTES;
+    const uint32_t bars = w_base + NW * SWAP_W_BYTES;
+    constexpr int NBARS = 2 * SWAP_NH + 2 * NW + 7;
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + SWAP_NH * SWAP_HALO_SLOT + XLO_BYTES + NW * SWAP_W_BYTES + 8 * NBARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     auto hfull = [&](int s) { return bars + 8u * s; };
     auto hempty = [&](int s) { return bars + 8u * (SWAP_NH + s); };
     auto wfull = [&](int s) { return bars + 8u * (2 * SWAP_NH + s); };
-    auto wempty = [&](int s) { return bars + 8u * (2 * SWAP_NH + SWAP_NW + s); };
-    auto tfull_bar = [&](int a) { return bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + a); };
-    auto tempty_bar = [&](int a) { return bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + 2 + a); };
-    const uint32_t drain_bar = bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + 4);
-    auto split_go = [&](int s) { return bars + 8u * (2 * SWAP_NH + 2 * SWAP_NW + 5 + s); };            /* X3: passes 0 and 1 have read the block */
-    auto split_done = [&](int s) { return bars + 8u * (3 * SWAP_NH + 2 * SWAP_NW + 5 + s); };          /* X3: the block now holds lo(x) */
+    auto wempty = [&](int s) { return bars + 8u * (2 * SWAP_NH + NW + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * SWAP_NH + 2 * NW + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * SWAP_NH + 2 * NW + 2 + a); };
+    const uint32_t drain_bar = bars + 8u * (2 * SWAP_NH + 2 * NW + 4);
+    const uint32_t xlo_full = bars + 8u * (2 * SWAP_NH + 2 * NW + 5);          /* X3: the lo(x) buffer holds the current slab's low parts */
+    const uint32_t xlo_free = bars + 8u * (2 * SWAP_NH + 2 * NW + 6);          /* X3: pass 2 of the previous slab has read it */
     constexpr int PASSES = X3 ? 3 : 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -623,9 +627,10 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SWAP_NH; s++) { mbar_init(hfull(s), 1); mbar_init(hempty(s), 1); }
-        for (int s = 0; s < SWAP_NW; s++) { mbar_init(wfull(s), 1); mbar_init(wempty(s), 1); }
+        for (int s = 0; s < NW; s++) { mbar_init(wfull(s), 1); mbar_init(wempty(s), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(tfull_bar(a), 1); mbar_init(tempty_bar(a), SWAP_EPI_WARPS); }
-        for (int s = 0; s < SWAP_NH; s++) { mbar_init(split_go(s), 1); mbar_init(split_done(s), SWAP_SPLIT_WARPS); }
+        mbar_init(xlo_full, SWAP_SPLIT_WARPS);
+        mbar_init(xlo_free, 1);
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -662,7 +667,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                         mbar_expect_tx(wfull(ws), SWAP_W_BYTES);
                         tma_load_2d(w_base + ws * SWAP_W_BYTES, (X3 && pt / 9 == 1) ? &mapWlo : &mapW, tap * p.CinPad + ks * BK, nt * BM, wfull(ws));
                         w_issued++;
-                        if (++ws == SWAP_NW) { ws = 0; wph ^= 1u; }
+                        if (++ws == NW) { ws = 0; wph ^= 1u; }
                     }
                 }
             }
@@ -674,10 +679,10 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                     const long long t0 = clock64();
                     while (!mbar_try(hfull(s), ph) && clock64() - t0 < WAIT_CYCLES) { }
                 }
-                pend = w_issued < SWAP_NW ? w_issued : SWAP_NW;
+                pend = w_issued < NW ? w_issued : NW;
                 s = ws; ph = wph;
                 for (long long i = 0; i < pend; i++) {
-                    if (--s < 0) { s = SWAP_NW - 1; ph ^= 1u; }
+                    if (--s < 0) { s = NW - 1; ph ^= 1u; }
                     const long long t0 = clock64();
                     while (!mbar_try(wfull(s), ph) && clock64() - t0 < WAIT_CYCLES) { }
                 }
@@ -689,6 +694,7 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             int hs = 0, ws = 0;
             uint32_t hph = 0, wph = 0;
             int it = 0;
+            uint32_t xph = 0;                        /* X3: parity of the lo(x) buffer's current use */
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
                 const int acc = it & 1;
@@ -698,13 +704,15 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                 const uint32_t d_tmem = tmem_base + (uint32_t)(acc * SWAP_N);
                 for (int ks = 0; ks < p.kslabs && ok; ks++) {
                     if (!mbar_wait(hfull(hs), hph, abort_flag, p.status, 6)) { ok = false; break; }
-                    const uint32_t sh = h_base + hs * SWAP_HALO_SLOT;
+                    uint32_t sh = h_base + hs * SWAP_HALO_SLOT;
                     for (int pt = 0; pt < 9 * PASSES; pt++) {
                         const int tap = pt % 9;
                         if (X3 && pt == 18) {
-                            /* passes 0 and 1 are issued: once they have read the block the splitter warps turn it into lo(x) */
-                            umma_commit(split_go(hs));
-                            if (!mbar_wait(split_done(hs), hph, abort_flag, p.status, 12)) { ok = false; break; }
+                            /* passes 0 and 1 (block as loaded) are issued; pass 2 reads lo(x), which the splitter warps wrote to their
+                               own buffer while those passes ran.  The block's slot is free once passes 0 and 1 have completed. */
+                            if (!mbar_wait(xlo_full, xph, abort_flag, p.status, 12)) { ok = false; break; }
+                            umma_commit(hempty(hs));
+                            sh = xlo_base;
                         }
                         if (!mbar_wait(wfull(ws), wph, abort_flag, p.status, 3)) { ok = false; break; }
                         tc_fence_after();
@@ -715,9 +723,10 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
                         for (int j = 0; j < BK / 8; j++)
                             umma_tf32(d_tmem, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, (ks | pt | j) ? 1u : 0u);
                         umma_commit(wempty(ws));
-                        if (++ws == SWAP_NW) { ws = 0; wph ^= 1u; }
+                        if (++ws == NW) { ws = 0; wph ^= 1u; }
                     }
-                    if (ok) umma_commit(hempty(hs));
+                    if (X3) { if (ok) umma_commit(xlo_free); xph ^= 1u; }
+                    else if (ok) umma_commit(hempty(hs));
                     if (++hs == SWAP_NH) { hs = 0; hph ^= 1u; }
                 }
                 if (ok) umma_commit(tfull_bar(acc));
@@ -824,29 +833,32 @@ k_umma_conv_swap(const __grid_constant__ CUtensorMap mapX, const __grid_constant
             if (lane == 0) mbar_arrive(tempty_bar(acc));
         }
     } else if (X3) {
-        /* splitter warps: block -> lo(block) in place between passes 1 and 2 of every channel slab */
+        /* splitter warps: lo(block) of every channel slab into the lo(x) buffer, while passes 0 and 1 of that slab run */
         const int sw = warp - (2 + SWAP_EPI_WARPS);
         int hs = 0;
-        uint32_t hph = 0;
+        uint32_t hph = 0, xph = 0;
         bool ok = true;
         const int chunks = (int)(halo_bytes / 16);
         for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
             for (int ks = 0; ks < p.kslabs; ks++) {
-                /* the block was written by TMA: wait on its own barrier first (visibility), then for the MMAs that read it */
+                /* the block was written by TMA: wait on its barrier (visibility); the buffer is free once pass 2 of the slab before
+                   has read it (first use: the wait on the preceding phase returns at once) */
                 if (!mbar_wait_warp(hfull(hs), hph, abort_flag, p.status, 10)) { ok = false; break; }
-                if (!mbar_wait_warp(split_go(hs), hph, abort_flag, p.status, 11)) { ok = false; break; }
-                uint4 *blk = reinterpret_cast<uint4 *>(gen + hs * SWAP_HALO_SLOT);
+                if (!mbar_wait_warp(xlo_free, xph ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
+                const uint4 *blk = reinterpret_cast<const uint4 *>(gen + hs * SWAP_HALO_SLOT);
+                uint4 *lo = reinterpret_cast<uint4 *>(gen + SWAP_NH * SWAP_HALO_SLOT);
                 for (int i = sw * 32 + lane; i < chunks; i += SWAP_SPLIT_WARPS * 32) {
                     uint4 v = blk[i];
                     v.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(v.x & 0xffffe000u));
                     v.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(v.y & 0xffffe000u));
                     v.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(v.z & 0xffffe000u));
                     v.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(v.w & 0xffffe000u));
-                    blk[i] = v;
+                    lo[i] = v;
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
-                if (lane == 0) mbar_arrive(split_done(hs));
+                if (lane == 0) mbar_arrive(xlo_full);
+                xph ^= 1u;
                 if (++hs == SWAP_NH) { hs = 0; hph ^= 1u; }
             }
         }
