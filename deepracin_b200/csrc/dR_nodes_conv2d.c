@@ -24,6 +24,8 @@ typedef struct {
     gfloat mapScale[4], mapShift[4];
     const float *planSrc;           /* buffers the plan's tensor maps were encoded for */
     float *planDst;
+    dR_Node *mergeWith;             /* Fire-module expand pair: this 3x3 node also evaluates that 1x1 sibling (same input, neighbouring channels of one Concat) */
+    cl_mem mergedBias;              /* the sibling's bias followed by this node's */
     dRk_TensorConvPlan *planAlt;    /* the plan for the other buffer pair when the input alternates (double-buffered feeding) */
     const float *planAltSrc;
     float *planAltDst;
@@ -253,6 +255,29 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
             }
         }
     }
+    /* Fire-module expand pair (SqueezeNet: 1x1 and 3x3 convolutions of the same squeezed tensor, concatenated along channels,
+       examples/squeezenet-v1.1/squeezenet_whole/graph.dr): a 1x1 filter is a 3x3 filter whose eight outer taps are zero, so both are
+       ONE 3x3 layer with O1 + O3 output channels written at the 1x1 node's channel offset.  On the transposed kernel the extra
+       channels fill MMA rows that a 64-channel layer leaves idle anyway, and the graph launches one kernel less per module. */
+    dev(c)->mergeWith = NULL;
+    if (c->chosenAlgo == DR_CONV_TENSOR && !x3Mode(net) && net->config->fuseGraph && !net->config->autotune && is3x3s1(c) && layer->elided &&
+        !dev(c)->fusedPool && c->algo == DR_CONV_AUTO && net->config->convAlgo == DR_CONV_AUTO && !layer->output) {
+        dR_Node *in = dR_firstInput(layer);
+        dR_Node *cat = (dR_Node *)layer->next_layers->first->element;
+        for (dR_ListElement *e = in->next_layers->first; e; e = e->next) {
+            dR_Node *sib = (dR_Node *)e->element;
+            if (sib == layer || sib->type != tConv2d) continue;
+            dR_Conv2d_Data *sc = (dR_Conv2d_Data *)sib->layer;
+            if (!is1x1s1(sc) || sc->chosenAlgo != DR_CONV_TENSOR || sc->algo != DR_CONV_AUTO || !sib->elided || sib->output || sib->fusedAway) continue;
+            if (sib->next_layers->length != 1 || sib->next_layers->first->element != cat || cat->type != tConcat) continue;
+            if (sc->activation != c->activation || sc->useBias != c->useBias || sc->shape.s2 != c->shape.s2) continue;
+            if (sib->act_cstride != layer->act_cstride || sib->act_coffset + sc->shape.s3 != layer->act_coffset) continue;
+            if (!dRk_tensor_conv_supported(c->ishape.s0, c->ishape.s1, c->shape.s2, sc->shape.s3 + c->shape.s3, 3, 3)) continue;
+            dev(c)->mergeWith = sib;
+            sib->fusedAway = TRUE;
+            break;
+        }
+    }
     /* scratch for every variant the autotuner may try */
     layer->scratchFloats = 0;
     if (c->chosenAlgo == DR_CONV_WINOGRAD || (net->config->autotune && is3x3s1(c)))
@@ -281,6 +306,24 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
     const gint kw = c->shape.s0, kh = c->shape.s1, I = c->shape.s2, O = c->shape.s3;
     if (algo == DR_CONV_ONEBYONE) algo = DR_CONV_DIRECT;        /* same [K][Cout] packing */
     if (d->wbuf[algo]) return TRUE;
+    if (algo == DR_CONV_TENSOR && d->mergeWith) {
+        /* [Cin][O1 + O][3][3]: the sibling's 1x1 filters on the centre tap of the first O1 channels, then this node's filters */
+        dR_Conv2d_Data *sc = (dR_Conv2d_Data *)d->mergeWith->layer;
+        const gint O1 = sc->shape.s3, Om = O1 + O;
+        if (!sc->hasVariables) { g_print("Conv2d Layer %d has no weights (call dR_Conv2d_setVariables)\n", d->mergeWith->layerID); return FALSE; }
+        const size_t nm = dRk_tensor_conv_packed_floats(c->ishape.s0, c->ishape.s1, I, Om, 3, 3);
+        gfloat *wm = (gfloat *)g_malloc0((size_t)I * Om * 9 * sizeof(gfloat));
+        gfloat *pm = nm ? (gfloat *)g_malloc0(nm * sizeof(gfloat)) : NULL;
+        gboolean okm = pm != NULL;
+        for (gint i = 0; i < I && okm; i++) {
+            for (gint o = 0; o < O1; o++) wm[((size_t)i * Om + o) * 9 + 4] = sc->weights[(size_t)i * O1 + o];
+            memcpy(wm + ((size_t)i * Om + O1) * 9, c->weights + (size_t)i * O * 9, (size_t)O * 9 * sizeof(gfloat));
+        }
+        okm = okm && dRk_tensor_conv_pack_weights(wm, pm, c->ishape.s0, c->ishape.s1, I, Om, 3, 3) == 0 &&
+              dR_createFloatBufferL(net, &d->wbuf[algo], nm) && dR_uploadArray(net, "", pm, 0, nm * sizeof(gfloat), d->wbuf[algo]);
+        g_free(wm); g_free(pm);
+        return okm;
+    }
     size_t n = (size_t)kw * kh * I * O;
     if (algo == DR_CONV_WINOGRAD) n = (size_t)16 * I * O;
     if (algo == DR_CONV_TENSOR) n = x3Mode(net) ? dRk_tensor_conv_x3_packed_floats(I, O) : dRk_tensor_conv_packed_floats(c->ishape.s0, c->ishape.s1, I, O, kw, kh);
@@ -320,6 +363,13 @@ gboolean dR_conv2d_fillBuffers(dR_Graph *net, dR_Node *layer)
 {
     dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
     if (c->useBias && !dR_uploadArray(net, "", c->biases, 0, (size_t)c->shape.s3 * sizeof(cl_float), c->biasBuf)) return FALSE;
+    if (dev(c)->mergeWith && c->useBias) {
+        dR_Conv2d_Data *sc = (dR_Conv2d_Data *)dev(c)->mergeWith->layer;
+        const size_t o1 = (size_t)sc->shape.s3, o3 = (size_t)c->shape.s3;
+        if (!dR_createFloatBufferL(net, &dev(c)->mergedBias, o1 + o3) ||
+            !dR_uploadArray(net, "", sc->biases, 0, o1 * sizeof(cl_float), dev(c)->mergedBias) ||
+            !dR_uploadArray(net, "", c->biases, o1 * sizeof(cl_float), o3 * sizeof(cl_float), dev(c)->mergedBias)) return FALSE;
+    }
     if (!ensurePacked(net, layer, c->chosenAlgo)) return FALSE;
     c->weightsBuf = dev(c)->wbuf[c->chosenAlgo == DR_CONV_ONEBYONE ? DR_CONV_DIRECT : c->chosenAlgo];
     return TRUE;
@@ -361,6 +411,12 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
         }
         if (!d->plan) {
             d->planSrc = src; d->planDst = dst;
+            if (d->mergeWith) {
+                dR_Conv2d_Data *sc = (dR_Conv2d_Data *)d->mergeWith->layer;
+                d->plan = dRk_tensor_conv_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR], c->useBias ? (const float *)d->mergedBias : NULL, dst, n, W, H,
+                                               c->shape.s2, sc->shape.s3 + c->shape.s3, 3, 3, act, layer->act_cstride, d->mergeWith->act_coffset, 0,
+                                               (int *)net->statusWord);
+            } else
             d->plan = x3Mode(net)
                 ? dRk_tensor_conv_x3_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR], bias, dst, n, W, H, c->shape.s2, c->shape.s3, act,
                                           layer->act_cstride, layer->act_coffset, d->fusedPool, (int *)net->statusWord)
@@ -459,6 +515,7 @@ gboolean dR_conv2d_cleanupBuffers(dR_Graph *net, dR_Node *layer)
     if (d->plan) { dRk_tensor_conv_free(d->plan); d->plan = NULL; }
     if (d->planAlt) { dRk_tensor_conv_free(d->planAlt); d->planAlt = NULL; }
     if (d->wplan) { dRk_tensor_winograd_free(d->wplan); d->wplan = NULL; }
+    if (d->mergedBias) { ret &= dR_clMemoryBufferCleanup(net, d->mergedBias); d->mergedBias = NULL; }
     c->weightsBuf = NULL;
     return ret;
 }

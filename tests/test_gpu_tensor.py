@@ -394,3 +394,35 @@ def test_fp32_accurate_tensor_mode_on_a_whole_network():
     assert tensor_layers["fp32x3"] == [0] + [2] * 12
     assert np.array_equal(outs["fp32"].argmax(1), outs["fp32x3"].argmax(1))
     assert rel_err(outs["fp32x3"], outs["fp32"]) <= 5e-4
+
+
+@pytest.mark.parametrize("s,e,hw,n", [(16, 64, 28, 4), (32, 128, 14, 3), (48, 192, 14, 70), (16, 24, 11, 2)])
+def test_fire_expand_pair_runs_as_one_layer(s, e, hw, n):
+    """Fire module in TF32 mode: the 1x1 and 3x3 expand convolutions of one squeezed tensor, concatenated along channels, are one
+    3x3 launch (the 1x1 filters sit on the centre tap): one kernel less than without fusion, same results as the oracle's two
+    convolutions, and the same as the unfused graph within TF32 rounding order."""
+    x, w1, b1 = cases.conv_case("fire_e1_%d" % e, n, s, e, hw, hw, 1, True)
+    _, w3, b3 = cases.conv_case("fire_e3_%d" % e, 1, s, e, hw, hw, 3, True)
+    ref = np.concatenate([oracle.conv2d(x[:2], w1, b1, (1, 1), 1), oracle.conv2d(x[:2], w3, b3, (1, 1), 1)], axis=1)
+    res, launches = {}, {}
+    for fuse in (True, False):
+        with dr.Environment() as env:
+            g = env.create_graph("CHW")
+            g.batch = n
+            g.math = "tf32"
+            g.fuse = fuse
+            f = dr.feed_node(g, [s, hw, hw])
+            e1 = conv_build(w1, b1, 1, 1)(g, [f])
+            e3 = conv_build(w3, b3, 1, 1)(g, [f])
+            cat = dr.Concat([e1, e3], 0)
+            dr.mark_as_output(cat)
+            dr.prepare(g)
+            dr.feed_data(f, x)
+            res[fuse] = dr.apply(g)[0].reshape(n, 2 * e, hw, hw)
+            launches[fuse] = dr.lib.dR_getLaunchCount(g.ptr)
+            assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    assert launches[True] == 3                          # feed layout, ONE convolution, output layout
+    assert launches[False] == 6                         # feed layout, two convolutions, two concat placements, output layout
+    assert rel_err(res[True][:2], ref) <= TOL_TF32
+    assert rel_err(res[False][:2], ref) <= TOL_TF32
+    assert rel_err(res[True], res[False]) <= 1e-6 * 50  # same TF32 products; the accumulation order of the centre tap differs
