@@ -280,16 +280,8 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
     }
     /* scratch for every variant the autotuner may try */
     layer->scratchFloats = 0;
-    if (c->chosenAlgo == DR_CONV_TENSOR && !x3Mode(net))
-        layer->scratchFloats = dRk_tensor_conv_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3, c->shape.s0, c->shape.s1);
-    if (c->chosenAlgo == DR_CONV_WINOGRAD || (net->config->autotune && is3x3s1(c))) {
-        const size_t s = dRk_winograd_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
-        if (s > layer->scratchFloats) layer->scratchFloats = s;
-    }
-    if (net->config->autotune && net->config->mathMode == DR_MATH_TF32 && tensorLegal(net, layer)) {
-        const size_t s = dRk_tensor_conv_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3, c->shape.s0, c->shape.s1);
-        if (s > layer->scratchFloats) layer->scratchFloats = s;
-    }
+    if (c->chosenAlgo == DR_CONV_WINOGRAD || (net->config->autotune && is3x3s1(c)))
+        layer->scratchFloats = dRk_winograd_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
     if (c->chosenAlgo == DR_CONV_TENSOR_WINOGRAD ||
         (net->config->autotune && net->config->mathMode == DR_MATH_TF32 && algoLegal(net, layer, DR_CONV_TENSOR_WINOGRAD))) {
         const size_t s = dRk_tensor_winograd_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
@@ -431,10 +423,6 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
                 : dRk_tensor_conv_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR], bias, dst, n, W, H, c->shape.s2, c->shape.s3,
                                        c->shape.s0, c->shape.s1, act, layer->act_cstride, layer->act_coffset, d->fusedPool, (int *)net->statusWord);
             if (!d->plan) { g_print("Conv2d Layer %d: tensor-core plan could not be built\n", layer->layerID); return FALSE; }
-            if (!x3Mode(net) && dRk_tensor_conv_set_scratch(d->plan, (float *)net->scratch) != 0) {
-                g_print("Conv2d Layer %d: staging tensor rejected\n", layer->layerID);
-                return FALSE;
-            }
             if (d->mapSrc && dRk_tensor_conv_set_input_map(d->plan, d->mapSrc->act_cstride, d->mapCh, d->mapScale, d->mapShift) != 0) {
                 g_print("Conv2d Layer %d: input channel map rejected\n", layer->layerID);
                 return FALSE;

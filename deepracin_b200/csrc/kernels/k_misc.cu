@@ -475,7 +475,6 @@ extern "C" int dRk_channel_map(dRk_stream s, const drk_ChannelMap *map, float *o
  * of the library asks (results stay within rounding order whatever they are set to):
  *   DRK_NO_PAIR / DRK_NO_SWAP / DRK_NO_HALO  take the row-pair / transposed / halo tensor kernels out of the planner's choice
  *                                            (the next of pair -> transposed -> halo -> plain is used)
- *   DRK_NO_C4                                take the 4-channel-pixel first-layer kernel out of the choice (the gather kernel is used)
  *   DRK_NO_INPUT_MAP                         keep a Slice / scalar-op / Concat preamble as a kernel of its own
  *   DRK_NO_DEP_LAUNCH                        launch every kernel in plain stream order (no programmatic dependent launch) */
 extern "C" const drk_DebugSwitches *dRk_debug_switches(void)
@@ -486,7 +485,6 @@ extern "C" const drk_DebugSwitches *dRk_debug_switches(void)
         sw.no_pair = getenv("DRK_NO_PAIR") != NULL;
         sw.no_swap = getenv("DRK_NO_SWAP") != NULL;
         sw.no_halo = getenv("DRK_NO_HALO") != NULL;
-        sw.no_c4 = getenv("DRK_NO_C4") != NULL;
         sw.no_input_map = getenv("DRK_NO_INPUT_MAP") != NULL;
         sw.no_dep_launch = getenv("DRK_NO_DEP_LAUNCH") != NULL;
         read = 1;

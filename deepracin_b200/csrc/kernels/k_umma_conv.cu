@@ -903,8 +903,6 @@ struct dRk_TensorConvPlan {
     int first;          /* 1: k_umma_conv_first (Cin <= 4: patches gathered by producer warps, no tensor maps) */
     int pair;           /* 1: k_umma_conv_pair (Cout <= 64: two output rows stacked on M); mapA = odd input rows, mapA2 = even */
     int x3;             /* 1: k_umma_conv_swap<true>, FP32-accurate three-pass evaluation; mapA2 = the filters' low parts */
-    int smallc;         /* 1: k_umma_conv_c4 (Cin <= 4: input re-laid as 4-channel pixels in `pad`, blocks read through overlapping no-swizzle descriptors) */
-    float *pad;         /* smallc: [n][H][W][4] staging tensor, handed over by dRk_tensor_conv_set_scratch */
     CUtensorMap mapA2;
     const float *in, *wT;
     int sms;
@@ -916,13 +914,6 @@ struct dRk_TensorConvPlan {
 double drk_umma_pair_fill(int W, int H);
 double drk_umma_pair_geometry(int W, int H, int *P, int *TW, int *TJ);
 int drk_umma_pair_launch(cudaStream_t st, const CUtensorMap *mapO, const CUtensorMap *mapE, const CUtensorMap *mapW, const UmmaParams *p, int grid);
-int drk_umma_c4_supported(int Cin, int Cout, int kw, int kh);
-double drk_umma_c4_geometry(int W, int H, int pool, int *P, int *TW, int *TH);
-size_t drk_umma_c4_packed_floats(void);
-int drk_umma_c4_pack_weights(const float *w, float *dst, int Cin, int Cout);
-int drk_umma_c4_pad_launch(cudaStream_t st, const float *in, float *padded, size_t pixels, int Cin, int ldi, const int *map_ch, const float *map_scale,
-                           const float *map_shift);
-int drk_umma_c4_launch(cudaStream_t st, const CUtensorMap *mapX, const CUtensorMap *mapW, const UmmaParams *p, int grid);
 int drk_umma_first_supported(int Cin, int Cout, int kw, int kh);
 int drk_umma_first_can_pool(int W, int H, int Cin, int Cout);
 int drk_umma_first_launch(cudaStream_t st, const float *in, const float *wT, const float *bias, float *out, int n, int W, int H, int Cin,
@@ -1018,17 +1009,10 @@ static double swap_fill(int W, int H)
 
 /* which kernel evaluates a layer shape; the packed-filter layout depends on it, so packing and planning both ask here.
  * The debug switches (dRk_debug_switches) exist for A/B comparisons of the variants when profiling. */
-enum { VAR_NONE = 0, VAR_FLAT, VAR_PLAIN, VAR_HALO, VAR_SWAP, VAR_PAIR, VAR_FIRST, VAR_SMALLC };
-
-static int smallc_ok(int W, int H, int Cin, int Cout, int kw, int kh)
-{
-    int P, TW, TH;
-    return drk_umma_c4_supported(Cin, Cout, kw, kh) && !dRk_debug_switches()->no_c4 && drk_umma_c4_geometry(W, H, 0, &P, &TW, &TH) > 0.0;
-}
+enum { VAR_NONE = 0, VAR_FLAT, VAR_PLAIN, VAR_HALO, VAR_SWAP, VAR_PAIR, VAR_FIRST };
 static int pick_variant(int W, int H, int Cin, int Cout, int kw, int kh)
 {
     if (!dRk_tensor_conv_supported(W, H, Cin, Cout, kw, kh)) return VAR_NONE;
-    if (smallc_ok(W, H, Cin, Cout, kw, kh)) return VAR_SMALLC;
     if (drk_umma_first_supported(Cin, Cout, kw, kh)) return VAR_FIRST;
     if (kw == 1) return VAR_FLAT;
     const drk_DebugSwitches *sw = dRk_debug_switches();
@@ -1046,7 +1030,6 @@ extern "C" int dRk_tensor_conv_can_fuse_pool(int W, int H, int Cin, int Cout, in
     if (pool_type == 0) return 1;
     const int v = pick_variant(W, H, Cin, Cout, kw, kh);
     if (v == VAR_NONE || v == VAR_FLAT || kw != 3 || (W & 1) || (H & 1)) return 0;
-    if (v == VAR_SMALLC) { int P, TW, TH; return (pool_type == 1 || pool_type == 2) && drk_umma_c4_geometry(W, H, 1, &P, &TW, &TH) > 0.0; }
     if (v == VAR_FIRST) return (pool_type == 1 || pool_type == 2) && drk_umma_first_can_pool(W, H, Cin, Cout);
     return pool_type == 1;
 }
@@ -1057,7 +1040,6 @@ extern "C" size_t dRk_tensor_conv_packed_floats(int W, int H, int Cin, int Cout,
     if (v == VAR_NONE) return 0;
     const size_t cp = (size_t)dRk_tensor_conv_cin_pad(Cin);
     if (v == VAR_PAIR) return (size_t)BM * 12 * cp;
-    if (v == VAR_SMALLC) return drk_umma_c4_packed_floats();
     return (size_t)Cout * kw * kh * cp;
 }
 
@@ -1067,7 +1049,6 @@ extern "C" int dRk_tensor_conv_pack_weights(const float *w, float *dst, int W, i
     if (v == VAR_NONE) return -1;
     const size_t cp = (size_t)dRk_tensor_conv_cin_pad(Cin);
     const int taps = kw * kh;
-    if (v == VAR_SMALLC) return drk_umma_c4_pack_weights(w, dst, Cin, Cout);
     memset(dst, 0, dRk_tensor_conv_packed_floats(W, H, Cin, Cout, kw, kh) * sizeof(float));
     if (v == VAR_PAIR) {
         /* [128 rows][(i*3 + kx)*CinPad + c]: row r < 64 = channel r with ky = i (upper output row), row 64 + o = channel o with
@@ -1170,9 +1151,6 @@ extern "C" int dRk_tensor_conv_describe(int n, int W, int H, int Cin, int Cout, 
     if (v == VAR_PAIR) {
         drk_umma_pair_geometry(W, H, P, TW, TH);
         *ncols = *P * *TH;
-    } else if (v == VAR_SMALLC) {
-        drk_umma_c4_geometry(W, H, fuse_pool2 ? 1 : 0, P, TW, TH);
-        *ncols = *P * *TH;
     } else if (v == VAR_SWAP || v == VAR_HALO) {
         if (use_swap_kernel(v, n, W, H, Cout, fuse_pool2, sms)) {
             v = VAR_SWAP;
@@ -1204,28 +1182,6 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     UmmaParams &p = pl->p;
     pl->in = in; pl->wT = wT; pl->sms = sms;
     const int variant = pick_variant(W, H, Cin, Cout, kw, kh);
-    if (variant == VAR_SMALLC) {
-        pl->smallc = 1;
-        pl->ldi = Cin;
-        p.n = n; p.W = W; p.H = H; p.Cin = Cin; p.Cout = Cout; p.bias = bias; p.out = out; p.ldo = ldo; p.coff = coff; p.act = act; p.status = status;
-        p.pool = fuse_pool2;
-        p.S = 1;
-        drk_umma_c4_geometry(W, H, fuse_pool2 ? 1 : 0, &p.P, &p.TW, &p.TH);
-        p.ncols = p.P * p.TH;
-        p.tiles_x = (W + p.TW - 1) / p.TW; p.tiles_y = (H + p.TH - 1) / p.TH;
-        p.total_sub = (long long)n * p.tiles_x * p.tiles_y;
-        p.m_tiles = (int)p.total_sub;
-        p.n_tiles = 1;
-        pl->BN = BM;
-        const cuuint32_t one2[2] = {1, 1};
-        const cuuint64_t wdims[2] = {48, BM}, wstr[1] = {48 * 4};
-        const cuuint32_t wbox[2] = {4, BM};
-        CUresult rw = enc(&pl->mapB, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)wT, wdims, wstr, wbox, one2, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (rw != CUDA_SUCCESS) { fprintf(stderr, "tensor conv plan: filter tensor map rejected (%d)\n", (int)rw); free(pl); return NULL; }
-        pl->grid = (int)(p.total_sub < sms ? p.total_sub : sms);
-        return pl;                  /* the activation map is encoded when the staging tensor is known (dRk_tensor_conv_set_scratch) */
-    }
     if (variant == VAR_FIRST) {
         pl->first = 1;
         pl->ldi = Cin;
@@ -1410,7 +1366,6 @@ extern "C" int dRk_tensor_conv_plan_describe(const dRk_TensorConvPlan *pl, int *
 {
     *P = *TW = *TH = *ncols = 0;
     if (!pl) return VAR_NONE;
-    if (pl->smallc) { *P = pl->p.P; *TW = pl->p.TW; *TH = pl->p.TH; *ncols = pl->p.ncols; return VAR_SMALLC; }
     if (pl->first) return VAR_FIRST;
     if (pl->p.S == 0) return VAR_FLAT;
     *TW = pl->p.TW; *TH = pl->p.TH;
@@ -1421,7 +1376,7 @@ extern "C" int dRk_tensor_conv_plan_describe(const dRk_TensorConvPlan *pl, int *
 
 extern "C" int dRk_tensor_conv_set_input_map(dRk_TensorConvPlan *pl, int ldi, const int *ch, const float *scale, const float *shift)
 {
-    if (!pl || !(pl->first || pl->smallc) || !ch || !scale || !shift || ldi < pl->p.Cin) return -1;
+    if (!pl || !pl->first || !ch || !scale || !shift || ldi < pl->p.Cin) return -1;
     unsigned seen = 0;
     for (int c = 0; c < pl->p.Cin; c++) {
         if (ch[c] < 0 || ch[c] >= pl->p.Cin || (seen >> ch[c]) & 1u) return -1;      /* a permutation of the first Cin source channels */
@@ -1433,42 +1388,10 @@ extern "C" int dRk_tensor_conv_set_input_map(dRk_TensorConvPlan *pl, int ldi, co
     return 0;
 }
 
-extern "C" size_t dRk_tensor_conv_scratch_floats(int n, int W, int H, int Cin, int Cout, int kw, int kh)
-{
-    if (n <= 0 || pick_variant(W, H, Cin, Cout, kw, kh) != VAR_SMALLC) return 0;
-    return (size_t)n * H * W * 4;
-}
-
-extern "C" int dRk_tensor_conv_set_scratch(dRk_TensorConvPlan *pl, float *scratch)
-{
-    if (!pl) return -1;
-    if (!pl->smallc) return 0;
-    if (!scratch || ((uintptr_t)scratch % 16)) return -1;
-    PFN_encodeTiled enc = get_encode();
-    if (!enc) return -1;
-    const UmmaParams &p = pl->p;
-    const cuuint32_t ones[4] = {1, 1, 1, 1};
-    const cuuint64_t dims[4] = {4, (cuuint64_t)p.W, (cuuint64_t)p.H, (cuuint64_t)p.n};
-    const cuuint64_t strides[3] = {16, (cuuint64_t)p.W * 16, (cuuint64_t)p.H * p.W * 16};
-    const cuuint32_t box[4] = {4, (cuuint32_t)p.P, (cuuint32_t)(p.TH + 2), 1};
-    CUresult r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 4, (void *)scratch, dims, strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                     CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) { fprintf(stderr, "tensor conv plan: staging tensor map rejected (%d)\n", (int)r); return -1; }
-    pl->pad = scratch;
-    return 0;
-}
-
 extern "C" int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *pl)
 {
     if (!pl) return -1;
     cudaStream_t st = drk_stream(stream);
-    if (pl->smallc) {
-        if (!pl->pad) return -5;            /* dRk_tensor_conv_set_scratch was not called */
-        int rc = drk_umma_c4_pad_launch(st, pl->in, pl->pad, (size_t)pl->p.n * pl->p.H * pl->p.W, pl->p.Cin, pl->ldi, pl->mapped ? pl->map_ch : NULL,
-                                        pl->map_scale, pl->map_shift);
-        if (rc) return rc;
-        return drk_umma_c4_launch(st, &pl->mapA, &pl->mapB, &pl->p, pl->grid);
-    }
     if (pl->first)
         return drk_umma_first_launch(st, pl->in, pl->wT, pl->p.bias, pl->p.out, pl->p.n, pl->p.W, pl->p.H, pl->p.Cin, pl->p.Cout, pl->p.act,
                                      pl->ldi, pl->p.ldo, pl->p.coff, pl->p.pool, pl->p.status, pl->sms, pl->mapped ? pl->map_ch : NULL,

@@ -142,12 +142,6 @@ int dRk_tensor_conv_pack_weights(const float *w, float *dst, int W, int H, int C
 dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float *wT, const float *bias, float *out,
                                          int n, int W, int H, int Cin, int Cout, int kw, int kh, int act,
                                          int ldo, int coff, int fuse_pool2, int *status);
-/* Layers with Cin <= 4 and 16 <= Cout <= 128 run on a kernel that reads the input re-laid as 4-channel pixels: such a plan needs a
- * staging tensor of dRk_tensor_conv_scratch_floats() floats (0 for every other shape), handed over by dRk_tensor_conv_set_scratch
- * before the first run (dRk_tensor_conv_run returns -5 without it).  Every run rewrites the staging tensor, so plans that run one
- * after the other on a stream may share it. */
-size_t dRk_tensor_conv_scratch_floats(int n, int W, int H, int Cin, int Cout, int kw, int kh);
-int dRk_tensor_conv_set_scratch(dRk_TensorConvPlan *plan, float *scratch);
 /* Few-channel first layers only (Cin <= 4): the convolution then reads channel ch[c] of a source with pixel stride ldi,
  * times scale[c] plus shift[c], as its input channel c (ch a permutation of 0..Cin-1); `in` of the plan is that source.  Replaces a Slice -> scalar op ->
  * Concat preamble (examples/squeezenet-v1.1/squeezenet_whole/graph.dr:7-41) in front of the layer.  -1 if the plan is for
@@ -165,7 +159,7 @@ int dRk_tensor_conv_x3_pack_weights(const float *w, float *dst, int Cin, int Cou
 dRk_TensorConvPlan *dRk_tensor_conv_x3_plan(const float *in, const float *wT2, const float *bias, float *out, int n, int W, int H,
                                             int Cin, int Cout, int act, int ldo, int coff, int fuse_pool2, int *status);
 /* Planner introspection, no device needed: the kernel (1 flat 1x1, 2 plain, 3 halo, 4 transposed, 5 row pair, 6 few-channel
- * first layer by gather, 7 few-channel first layer on 4-channel pixels; 0 = shape or pooling not supported) and block geometry a plan for this layer on a GPU with `sms` SMs would use. */
+ * first layer; 0 = shape or pooling not supported) and block geometry a plan for this layer on a GPU with `sms` SMs would use. */
 int dRk_tensor_conv_describe(int n, int W, int H, int Cin, int Cout, int kw, int kh, int fuse_pool2, int sms,
                              int *P, int *TW, int *TH, int *ncols);
 /* The same for a plan that was built: what its launches actually run. */
@@ -206,10 +200,10 @@ void dRk_tensor_fc_free(dRk_TensorFcPlan *plan);
  * a wait on a barrier that was arrived at (1), [2] how long the first wait took, in units of 1024 clocks. */
 int dRk_bounded_wait_probe(dRk_stream stream, int *status, long long limit_cycles, int *result);
 
-/* Debug switches of the library (environment variables DRK_NO_PAIR, DRK_NO_SWAP, DRK_NO_HALO, DRK_NO_C4, DRK_NO_INPUT_MAP,
+/* Debug switches of the library (environment variables DRK_NO_PAIR, DRK_NO_SWAP, DRK_NO_HALO, DRK_NO_INPUT_MAP,
  * DRK_NO_DEP_LAUNCH; read once per process): each takes one kernel variant or launch feature out of use so that two runs can
  * be timed against each other.  None changes results beyond rounding order.  No counterpart in the reference. */
-typedef struct { int no_pair, no_swap, no_halo, no_c4, no_input_map, no_dep_launch; } drk_DebugSwitches;
+typedef struct { int no_pair, no_swap, no_halo, no_input_map, no_dep_launch; } drk_DebugSwitches;
 const drk_DebugSwitches *dRk_debug_switches(void);
 
 /* Number of kernel launches issued through this ABI by the calling thread since the last reset. */

@@ -250,8 +250,8 @@ def test_tensor_planner_picks_the_expected_kernels_and_geometries():
         v = lib.dRk_tensor_conv_describe(n, w, h, cin, cout, k, k, pool, 148, *[ctypes.byref(x) for x in vals])
         return (v,) + tuple(x.value for x in vals)
 
-    FLAT, PLAIN, HALO, SWAP, PAIR, FIRST, SMALLC = 1, 2, 3, 4, 5, 6, 7
-    assert describe(64, 224, 224, 3, 64, 3, 0) == (SMALLC, 30, 28, 8, 240)           # conv1_1: input re-laid as 4-channel pixels, no gather
+    FLAT, PLAIN, HALO, SWAP, PAIR, FIRST = 1, 2, 3, 4, 5, 6
+    assert describe(64, 224, 224, 3, 64, 3, 0)[0] == FIRST
     assert describe(64, 224, 224, 64, 64, 3, 1) == (PAIR, 30, 28, 8, 240)            # conv1_2: 28 x 16-pixel tiles, two rows per MMA
     assert describe(64, 112, 112, 128, 128, 3, 1) == (SWAP, 30, 28, 8, 240)          # conv2_2
     assert describe(64, 56, 56, 256, 256, 3, 0) == (SWAP, 30, 28, 8, 240)            # conv3_2: two channel blocks per pixel tile
@@ -259,8 +259,7 @@ def test_tensor_planner_picks_the_expected_kernels_and_geometries():
     assert describe(64, 14, 14, 512, 512, 3, 0) == (SWAP, 16, 14, 14, 224)           # conv5: one image per tile
     assert describe(64, 28, 28, 256, 512, 1, 0)[0] == FLAT
     assert describe(1, 14, 14, 64, 256, 3, 0)[0] == HALO                             # batch 1: fewer tiles than SMs, smaller tiles spread further
-    assert describe(64, 224, 224, 3, 64, 3, 2)[0] == SMALLC                          # first layer with the average pool fused
-    assert describe(64, 224, 224, 3, 192, 3, 0)[0] == 0                              # more than 128 filters on 3 channels: FP32 kernels
+    assert describe(64, 224, 224, 3, 64, 3, 2)[0] == FIRST                           # first layer with the average pool fused
     assert describe(64, 56, 56, 256, 256, 3, 2)[0] == 0                              # average pooling is only fused into the first-layer kernel
     assert describe(2, 20, 20, 64, 64, 5, 0)[0] == 0                                 # 5x5 filters stay on the FP32 kernels
 
