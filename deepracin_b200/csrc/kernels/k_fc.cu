@@ -227,6 +227,7 @@ extern "C" int dRk_fc_f32(dRk_stream stream, const float *in, const float *w, co
  * message naming the limit.  All calls on a device share the array: it keeps whatever the last
  * call left in it (every element a call reads was written by that same call first, so nothing has
  * to be cleared), and two calls that may overlap on the GPU (different streams) would race on it.
+ * The device that is current at the call must be the stream's device (checked: -6 otherwise).
  */
 #define DRK_FC_STATIC_SCRATCH_FLOATS (2u << 20)
 static __device__ __align__(256) float g_fc_static_scratch[DRK_FC_STATIC_SCRATCH_FLOATS];
@@ -239,7 +240,16 @@ extern "C" int dRk_fc_f32_noalloc(dRk_stream stream, const float *in, const floa
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev < 0 || dev >= 64) return -1;
-    if (!g_fc_static_scratch_addr[dev]) {
+    {
+        /* the array's address is looked up for the CURRENT device: the stream must belong to it */
+        int sdev = dev;
+        if (cudaStreamGetDevice(drk_stream(stream), &sdev) == cudaSuccess && sdev != dev) {
+            fprintf(stderr, "dRk_fc_f32_noalloc: the stream belongs to device %d but device %d is current\n", sdev, dev);
+            return -6;
+        }
+        (void)cudaGetLastError();
+    }
+    if (!__atomic_load_n(&g_fc_static_scratch_addr[dev], __ATOMIC_ACQUIRE)) {
         /* in host code the array's name is only a handle; the kernels need its device address */
         float *addr = NULL;
         e = cudaGetSymbolAddress((void **)&addr, g_fc_static_scratch);
@@ -247,7 +257,7 @@ extern "C" int dRk_fc_f32_noalloc(dRk_stream stream, const float *in, const floa
             fprintf(stderr, "dRk_fc_f32_noalloc: cannot resolve the built-in scratch array on device %d: %s\n", dev, cudaGetErrorString(e));
             return e != cudaSuccess ? (int)e : -1;
         }
-        g_fc_static_scratch_addr[dev] = addr;
+        __atomic_store_n(&g_fc_static_scratch_addr[dev], addr, __ATOMIC_RELEASE);      /* threads racing here store the same value */
     }
     const size_t need = dRk_fc_scratch_floats(n, Nin, Nout);
     if (need == 0) return -1;

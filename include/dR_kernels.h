@@ -65,7 +65,8 @@ int dRk_fc_f32(dRk_stream stream, const float *in, const float *w, const float *
  * reference.  The split-K scratch is a fixed 8 MiB array inside the library (2 Mi floats, resident on
  * every GPU that loads the library); shapes needing more (dRk_fc_scratch_floats) are refused with -4.
  * The first call on a device resolves the array's address -- make it before any stream capture; calls
- * share the array, so calls that may overlap on the GPU race.  Allocates nothing.
+ * share the array, so calls that may overlap on the GPU race.  The stream's device must be the current device (-6 otherwise).
+ * Allocates nothing.
  */
 int dRk_fc_f32_noalloc(dRk_stream stream, const float *in, const float *w, const float *bias, float *out,
                        int n, int Nin, int Nout, int act);
