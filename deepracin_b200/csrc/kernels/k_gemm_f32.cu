@@ -229,21 +229,21 @@ __global__ void __launch_bounds__(256, BM == 128 ? (CONV ? 2 : 1) : 3) k_gemm_f3
 #define AS_STAGES 4
 #define AS_APITCH (BK + 4)          /* floats per staged A row: 16 + 4 keeps rows 16-byte aligned and spreads banks */
 #define AS_BM 128
-#define AS_BN 128
-#define AS_SMEM (AS_STAGES * (AS_BM * AS_APITCH + BK * AS_BN) * 4)
+#define AS_SMEM(NCH) (AS_STAGES * (AS_BM * AS_APITCH + BK * 64 * (NCH)) * 4)      /* NCH = 64-column chunks per CTA tile: BN = 64 or 128 */
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int bytes)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
 
-template <bool CONV, int MINB>
-__global__ void __launch_bounds__(256, MINB) k_gemm_f32_async(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias,
+template <bool CONV, int NCH>
+__global__ void __launch_bounds__(256, 2) k_gemm_f32_async(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias,
                                                            float *__restrict__ C, int M, int N, int K, int lda, int ldb, int ldc, int coff, int act,
                                                            size_t strideA, size_t strideB, size_t strideC, int vecC, drk_ConvGeom g)
 {
     extern __shared__ __align__(16) float smem_f[];
     float *As = smem_f;                                         /* [STAGES][BM][APITCH] */
+    constexpr int AS_BN = 64 * NCH;
     float *Bs = smem_f + AS_STAGES * AS_BM * AS_APITCH;         /* [STAGES][BK][BN] */
     const uint32_t as_u = (uint32_t)__cvta_generic_to_shared(As), bs_u = (uint32_t)__cvta_generic_to_shared(Bs);
     const int tid = threadIdx.x;
@@ -253,9 +253,10 @@ __global__ void __launch_bounds__(256, MINB) k_gemm_f32_async(const float *__res
     B += (size_t)blockIdx.z * strideB;
     C += (size_t)blockIdx.z * strideC;
 
-    /* staging assignment: A unit i = row tid/4 + 64 i, K segment (tid%4)*4; B unit i = K row tid/32 + 8 i, columns (tid%32)*4 */
+    /* staging assignment: A unit i = row tid/4 + 64 i, K segment (tid%4)*4; B unit i = K row tid/(BN/4) + 8 i (one unit covers
+       all 16 rows when BN = 64), columns (tid%(BN/4))*4 */
     const int a_kseg = (tid & 3) * 4, a_row0 = tid >> 2;
-    const int b_n = (tid & 31) * 4, b_k0 = tid >> 5;
+    const int b_n = (tid % (AS_BN / 4)) * 4, b_k0 = tid / (AS_BN / 4);
     bool a_ok[2];
     size_t a_base[2];
     int a_iy0[2], a_ix0[2];
@@ -299,7 +300,7 @@ __global__ void __launch_bounds__(256, MINB) k_gemm_f32_async(const float *__res
             cp_async16(as_u + (uint32_t)(((slot * AS_BM + a_row0 + 64 * i) * AS_APITCH + a_kseg) * 4), src, bytes);
         }
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < NCH; i++) {
             const int kr = kt * BK + b_k0 + 8 * i;
             const bool ok = kr < K && bn_bytes > 0;
             cp_async16(bs_u + (uint32_t)(((slot * BK + b_k0 + 8 * i) * AS_BN + b_n) * 4), ok ? (const void *)(B + (size_t)kr * ldb + n0 + b_n) : (const void *)B, ok ? bn_bytes : 0);
@@ -308,11 +309,11 @@ __global__ void __launch_bounds__(256, MINB) k_gemm_f32_async(const float *__res
 
     /* accumulators as pairs of neighbouring columns: one packed FFMA2 (fma.rn.f32x2, two IEEE round-to-nearest FMAs, the same
        results as two scalar ones) per pair halves the instruction and register-port traffic of the 8 x 8 outer product */
-    float2 acc[8][4];
+    float2 acc[8][2 * NCH];
 #pragma unroll
     for (int i = 0; i < 8; i++)
 #pragma unroll
-        for (int j = 0; j < 4; j++) acc[i][j] = make_float2(0.f, 0.f);
+        for (int j = 0; j < 2 * NCH; j++) acc[i][j] = make_float2(0.f, 0.f);
 
     const int numKT = (K + BK - 1) / BK;
 #pragma unroll
@@ -338,9 +339,9 @@ __global__ void __launch_bounds__(256, MINB) k_gemm_f32_async(const float *__res
                     a4[r * 4 + i] = *reinterpret_cast<const float4 *>(as + (r * 64 + ty * 4 + i) * AS_APITCH + kk);
 #pragma unroll
             for (int k4 = 0; k4 < 4; k4++) {
-                float2 b[4];
+                float2 b[2 * NCH];
 #pragma unroll
-                for (int c = 0; c < 2; c++) {
+                for (int c = 0; c < NCH; c++) {
                     const float4 t = *reinterpret_cast<const float4 *>(bs + (kk + k4) * AS_BN + c * 64 + tx * 4);
                     b[c * 2 + 0] = make_float2(t.x, t.y); b[c * 2 + 1] = make_float2(t.z, t.w);
                 }
@@ -349,7 +350,7 @@ __global__ void __launch_bounds__(256, MINB) k_gemm_f32_async(const float *__res
                     const float av = k4 == 0 ? a4[i].x : k4 == 1 ? a4[i].y : k4 == 2 ? a4[i].z : a4[i].w;
                     const float2 a2 = make_float2(av, av);
 #pragma unroll
-                    for (int j = 0; j < 4; j++) acc[i][j] = __ffma2_rn(a2, b[j], acc[i][j]);
+                    for (int j = 0; j < 2 * NCH; j++) acc[i][j] = __ffma2_rn(a2, b[j], acc[i][j]);
                 }
             }
         }
@@ -364,7 +365,7 @@ __global__ void __launch_bounds__(256, MINB) k_gemm_f32_async(const float *__res
             if (m >= M) continue;
             float *crow = C + (size_t)m * ldc + coff;
 #pragma unroll
-            for (int c = 0; c < 2; c++) {
+            for (int c = 0; c < NCH; c++) {
                 const int n = n0 + c * 64 + tx * 4;
                 if (n >= N) continue;
                 float v[4];
@@ -384,7 +385,7 @@ __global__ void __launch_bounds__(256, MINB) k_gemm_f32_async(const float *__res
         }
 }
 
-template <bool CONV, int MINB>
+template <bool CONV, int NCH>
 static int launch_async(cudaStream_t st, dim3 grid, const float *A, const float *B, const float *bias, float *C, int M, int N, int K, int lda, int ldb,
                         int ldc, int coff, int act, size_t sA, size_t sB, size_t sC, int vecC, const drk_ConvGeom &g)
 {
@@ -393,11 +394,11 @@ static int launch_async(cudaStream_t st, dim3 grid, const float *A, const float 
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm_f32_async<CONV, MINB>, cudaFuncAttributeMaxDynamicSharedMemorySize, AS_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(k_gemm_f32_async<CONV, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, AS_SMEM(NCH));
         if (e != cudaSuccess) return (int)e;
         attr_done[dev] = true;
     }
-    k_gemm_f32_async<CONV, MINB><<<grid, 256, AS_SMEM, st>>>(A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g);
+    k_gemm_f32_async<CONV, NCH><<<grid, 256, AS_SMEM(NCH), st>>>(A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g);
     return 0;
 }
 
@@ -424,14 +425,21 @@ int drk_gemm_f32_launch(cudaStream_t st, const float *A, const float *B, const f
     if (small) grid = dim3((N + 63) / 64, (M + 63) / 64, batch);
     else grid = dim3((N + 127) / 128, (M + 127) / 128, batch);
     if (grid.y > 65535u || grid.z > 65535u) return -2;
-    if (!small && vecA && vecB) {
-        /* 16-byte-aligned operands: the cp.async-staged kernel */
-        /* two CTAs per SM (128 registers): measured 8 % faster than one CTA with 152 registers */
-        const int rc = geom ? launch_async<true, 2>(st, grid, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g)
-                            : launch_async<false, 2>(st, grid, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g);
-        if (rc) return rc;
-        DRK_COUNT_LAUNCH();
-        return DRK_LAUNCH_RESULT();
+    if (vecA && vecB && M > 64) {
+        /* 16-byte-aligned operands: the cp.async-staged kernel, 128 x 128 tiles or 128 x 64 for narrow outputs, as long as the
+           launch has about a tile per SM (two CTAs per SM, 128 registers: measured 8 % faster than one CTA with 152) */
+        const int nch = N <= 64 ? 1 : 2;
+        const dim3 ga((N + 64 * nch - 1) / (64 * nch), (M + 127) / 128, batch);
+        if ((long)ga.x * ga.y * ga.z >= 100 && ga.y <= 65535u && ga.z <= 65535u) {
+            int rc;
+            if (nch == 2) rc = geom ? launch_async<true, 2>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g)
+                                    : launch_async<false, 2>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g);
+            else rc = geom ? launch_async<true, 1>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g)
+                           : launch_async<false, 1>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g);
+            if (rc) return rc;
+            DRK_COUNT_LAUNCH();
+            return DRK_LAUNCH_RESULT();
+        }
     }
     if (geom) {
         if (small) k_gemm_f32<64, 64, 4, 4, true><<<grid, 256, 0, st>>>(A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecA, vecB, vecC, g);
