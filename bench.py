@@ -276,7 +276,7 @@ def measure_dropin(ctx, steps, warmup, batch=64, math="tf32"):
 
 
 def per_node_profile(dr, lib, g):
-    """One apply with per-kernel events; returns [(kind, ms, output shape WxHxC)] per node."""
+    """One apply with per-kernel events; returns [(kind, ms, output shape WxHxC, kernel family of a convolution or None)] per node."""
     res = []
     lib.dR_config(g.ptr, b"", 1, 0, 1, 0, (g.env.model_path).encode())
     # the C library prints a summary line per apply when profiling; keep stdout clean for the JSON line
@@ -294,7 +294,7 @@ def per_node_profile(dr, lib, g):
     for node in g.nodes:
         kind = {"Conv2D": "conv", "FullyConnected": "fc", "Pooling": "pool", "Softmax": "softmax"}.get(node.desc, "other")
         sh = lib.dR_getOutputShape(node.ptr).contents
-        res.append((kind, lib.dR_getNodeGpuMs(node.ptr), "%dx%dx%d" % (sh.s0, sh.s1, sh.s2)))
+        res.append((kind, lib.dR_getNodeGpuMs(node.ptr), "%dx%dx%d" % (sh.s0, sh.s1, sh.s2), lib.dR_getConvAlgo(node.ptr) if kind == "conv" else None))
     lib.dR_config(g.ptr, b"", 1, 0, 0, 0, (g.env.model_path).encode())
     return res
 
@@ -339,7 +339,7 @@ def vgg_roofline(math, batch, prof, peaks, yard):
     """Roofline of the dominant kernel (conv3_2's launch) and of the 13 convolution launches together, from the per-node
     event times of one profiled apply.  Per-launch times are sub-millisecond, so the denominator is the BURST peak."""
     conv_flops, _ = vgg_flops_per_image()
-    prof = [(k, t) for k, t, _ in prof]
+    prof = [(p[0], p[1]) for p in prof]
     conv_times = [t for kind, t in prof if kind == "conv"]
     conv_ms, n_conv = sum(conv_times), len(conv_times)
     tensor = math in ("tf32", "fp32x3")
@@ -397,7 +397,7 @@ def run_ours(args):
         if args.net == "vgg16":
             roof, aggregate, conv_share = vgg_roofline(args.math, batch, main["profile"], peaks, yard)
         else:
-            roof["ms_per_layer"] = [[k, sh, round(t, 4)] for k, t, sh in main["profile"] if t > 0]      # launch order; fused nodes launch nothing
+            roof["ms_per_layer"] = [[k, sh, round(t, 4)] for k, t, sh, _ in main["profile"] if t > 0]      # launch order; fused nodes launch nothing
             roof["note"] = "SqueezeNet: per-node event times of one profiled apply (each carries ~5 us of event overhead); no single dominant kernel"
         klass = ("TF32 tensor-core class (fp32 storage, TF32 operands, FP32 accumulate)" if tensor else
                  "FP32-accurate tensor-core class (three TF32 passes per product)" if args.math == "fp32x3" else "exact FP32 class (FFMA)")
@@ -435,17 +435,29 @@ def run_ours(args):
         if "fp32_exact" in extra:
             fp = extra["fp32_exact"]
             froof, fagg, _ = vgg_roofline("fp32", batch, fp["profile"], peaks, None) if "profile" in fp else ({}, None, None)
-            # Winograd F(2x2,3x3) executes 2.25x fewer multiplications than the direct-convolution count on 3x3 stride-1 layers
-            # (all of them but conv1_1, which runs a direct kernel)
-            real = None
-            if fagg:
-                direct = 2 * 9 * 3 * 64 * 224 * 224
-                real = fagg * (direct + (conv_flops - direct) / 2.25) / conv_flops
+            # FFMA work really executed: a Winograd layer multiplies 16 (F(2x2,3x3)) or 36 (F(4x4,3x3)) transform-domain values per
+            # tile of 4 or 16 outputs (whole tiles, so 14x14 planes pay for 16x16 under F(4x4)) instead of 9 per output
+            real, families = None, None
+            convs = [(t, algo) for kind, t, _, algo in fp["profile"] if kind == "conv" and t > 0] if "profile" in fp else []
+            if fagg and len(convs) == len(VGG_CONVS):
+                executed, conv_ms, families = 0.0, 0.0, []
+                for (ci, co, hw), (t, algo) in zip(VGG_CONVS, convs):
+                    if algo == 2:
+                        per_image = 2.0 * 16 * ci * co * ((hw + 1) // 2) ** 2
+                    elif algo == 6:
+                        per_image = 2.0 * 36 * ci * co * ((hw + 3) // 4) ** 2
+                    else:
+                        per_image = 2.0 * 9 * ci * co * hw * hw
+                    executed += per_image * batch
+                    conv_ms += t
+                    families.append({1: "direct", 2: "winograd F(2x2,3x3)", 3: "1x1", 6: "winograd F(4x4,3x3)"}.get(algo, str(algo)))
+                real = executed / (conv_ms * 1e-3) / 1e12
             line["fp32_exact"] = {"images_per_s": fp["images_per_s"], "ms_per_step": fp["ms_per_step"], "e2e_images_per_s": fp["e2e_images_per_s"],
                                   "steps": fp["steps"], "dtype": "f32", "conv_tflops_direct_equivalent": fagg, "conv_tflops_executed_ffma": real,
                                   "frac_of_ffma_peak_executed": (real / FFMA_PEAK_NOMINAL) if real else None, "ffma_peak": FFMA_PEAK_NOMINAL,
                                   "ffma_peak_source": "nominal 148 SMs x 128 lanes x 2 x 1.965 GHz", "ms_per_layer": froof.get("ms_per_layer"),
-                                  "tolerance": "1e-4 x max|ref| per layer (the reference's own arithmetic)"}
+                                  "conv_kernel_family_per_layer": families,
+                                  "tolerance": "1e-4 x max|ref| per layer (FP32 FFMA arithmetic; F(4x4,3x3) layers measure about 2e-5, F(2x2,3x3) -- the reference's transform -- 1e-6)"}
         if "fp32x3" in extra:
             x3 = extra["fp32x3"]
             xroof, xagg, _ = vgg_roofline("tf32", batch, x3["profile"], peaks, None) if "profile" in x3 else ({}, None, None)

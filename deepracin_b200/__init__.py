@@ -30,7 +30,7 @@ lib = load()
 act_dict = {"linear": 0, "relu": 1}
 pool_dict = {"max": 0, "average": 1}
 MATH = {"fp32": 0, "tf32": 1, "fp32x3": 2}
-CONV_ALGO = {"auto": 0, "direct": 1, "winograd": 2, "1x1": 3, "tensor": 4, "tensor_winograd": 5}
+CONV_ALGO = {"auto": 0, "direct": 1, "winograd": 2, "1x1": 3, "tensor": 4, "tensor_winograd": 5, "winograd4": 6}
 _FP = POINTER(c_float)
 
 

@@ -133,11 +133,12 @@ gchar *dR_conv2d_printLayer(dR_Node *layer)
 {
     dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
     static const char *acts[] = {"Linear", "ReLU", "Sigmoid", "Tan"};
-    static const char *algos[] = {"auto", "direct (FP32 implicit GEMM)", "Winograd F(2x2,3x3)", "1x1 GEMM", "tcgen05 TF32 implicit GEMM"};
+    static const char *algos[DR_CONV_ALGOS] = {"auto", "direct (FP32 implicit GEMM)", "Winograd F(2x2,3x3)", "1x1 GEMM", "tcgen05 TF32 implicit GEMM",
+                                               "Winograd F(2x2,3x3), tcgen05 TF32 products", "Winograd F(4x4,3x3)"};
     return g_strdup_printf("Conv2d Layer: %d\n Filter dimensions: %dx%d\n Input channels: %d\n Output channels: %d\n Activation: %s\n"
                            " Stride: %d, %d, %d, %d\n Use bias: %s\n Kernel family: %s\n",
                            layer->layerID, c->shape.s0, c->shape.s1, c->shape.s2, c->shape.s3, acts[c->activation & 3],
-                           c->stride.s0, c->stride.s1, c->stride.s2, c->stride.s3, c->useBias ? "Yes" : "No", algos[c->chosenAlgo % 5]);
+                           c->stride.s0, c->stride.s1, c->stride.s2, c->stride.s3, c->useBias ? "Yes" : "No", algos[c->chosenAlgo % DR_CONV_ALGOS]);
 }
 
 /* reference src/dR_nodes_conv2d.c:238-256: the node keeps its own copies */
@@ -181,6 +182,7 @@ static gboolean algoLegal(dR_Graph *net, dR_Node *layer, gint algo)
     switch (algo) {
     case DR_CONV_DIRECT: return TRUE;
     case DR_CONV_WINOGRAD: return is3x3s1(c);
+    case DR_CONV_WINOGRAD4: return is3x3s1(c);
     case DR_CONV_ONEBYONE: return is1x1s1(c);
     case DR_CONV_TENSOR: return tensorLegal(net, layer);
     case DR_CONV_TENSOR_WINOGRAD:
@@ -190,14 +192,18 @@ static gboolean algoLegal(dR_Graph *net, dR_Node *layer, gint algo)
 }
 
 /* The reference's static rule (src/dR_nodes_conv2d.c:36-81): 3x3 stride 1 -> Winograd,
- * 1x1 stride 1 -> 1x1 kernel, otherwise direct.  In TF32 mode dense layers go to the tensor cores. */
+ * 1x1 stride 1 -> 1x1 kernel, otherwise direct.  In TF32 mode dense layers go to the tensor cores.
+ * Winograd layers with at least 16 channels on both sides take the F(4x4,3x3) form (fewer products AND fewer
+ * transform-domain values per output than the reference's F(2x2,3x3); error about 1e-5 of max|ref|, inside the FP32
+ * class bound); narrower layers keep F(2x2,3x3).  dR_setConvAlgo / dR_setGraphConvAlgo(DR_CONV_WINOGRAD) restores
+ * the reference's transform everywhere. */
 static gint staticRule(dR_Graph *net, dR_Node *layer)
 {
     dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
     if (net->config->mathMode != DR_MATH_FP32 && tensorLegal(net, layer)) return DR_CONV_TENSOR;
     /* a handful of input channels (RGB first layer): bound by writing the output, a direct kernel wins */
     if (is3x3s1(c) && c->shape.s2 <= 4) return DR_CONV_DIRECT;
-    if (is3x3s1(c)) return DR_CONV_WINOGRAD;
+    if (is3x3s1(c)) return (c->shape.s2 >= 16 && c->shape.s3 >= 16) ? DR_CONV_WINOGRAD4 : DR_CONV_WINOGRAD;
     if (is1x1s1(c)) return DR_CONV_ONEBYONE;
     return DR_CONV_DIRECT;
 }
@@ -282,6 +288,10 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
     layer->scratchFloats = 0;
     if (c->chosenAlgo == DR_CONV_WINOGRAD || (net->config->autotune && is3x3s1(c)))
         layer->scratchFloats = dRk_winograd_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
+    if (c->chosenAlgo == DR_CONV_WINOGRAD4 || (net->config->autotune && is3x3s1(c))) {
+        const size_t s = dRk_winograd4_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
+        if (s > layer->scratchFloats) layer->scratchFloats = s;
+    }
     if (c->chosenAlgo == DR_CONV_TENSOR_WINOGRAD ||
         (net->config->autotune && net->config->mathMode == DR_MATH_TF32 && algoLegal(net, layer, DR_CONV_TENSOR_WINOGRAD))) {
         const size_t s = dRk_tensor_winograd_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
@@ -326,6 +336,7 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
     }
     size_t n = (size_t)kw * kh * I * O;
     if (algo == DR_CONV_WINOGRAD) n = (size_t)16 * I * O;
+    if (algo == DR_CONV_WINOGRAD4) n = (size_t)36 * I * O;
     if (algo == DR_CONV_TENSOR) n = x3Mode(net) ? dRk_tensor_conv_x3_packed_floats(I, O) : dRk_tensor_conv_packed_floats(c->ishape.s0, c->ishape.s1, I, O, kw, kh);
     if (algo == DR_CONV_TENSOR_WINOGRAD) n = dRk_tensor_winograd_packed_floats(I, O);
     if (n == 0) return FALSE;
@@ -342,6 +353,8 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
                          : dRk_tensor_conv_pack_weights(c->weights, p, c->ishape.s0, c->ishape.s1, I, O, kw, kh)) != 0) { g_free(p); return FALSE; }
     } else if (algo == DR_CONV_TENSOR_WINOGRAD) {
         if (dRk_tensor_winograd_pack_weights(c->weights, p, I, O) != 0) { g_free(p); return FALSE; }
+    } else if (algo == DR_CONV_WINOGRAD4) {
+        if (dRk_winograd4_pack_weights(c->weights, p, I, O) != 0) { g_free(p); return FALSE; }
     } else {
         /* U = G g G^T with G = [[1,0,0],[.5,.5,.5],[.5,-.5,.5],[0,0,1]] (reference :1162-1240),
            stored [16][Cin][Cout] so that each of the 16 positions is one K x N matrix */
@@ -399,6 +412,10 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
     case DR_CONV_WINOGRAD:
         net->clConfig->clError = dRk_conv2d_winograd_f32(s, src, (const float *)d->wbuf[DR_CONV_WINOGRAD], bias, dst, (float *)net->scratch, n, W, H,
                                                          c->shape.s2, c->shape.s3, act, in->act_cstride, layer->act_cstride, layer->act_coffset);
+        break;
+    case DR_CONV_WINOGRAD4:
+        net->clConfig->clError = dRk_conv2d_winograd4_f32(s, src, (const float *)d->wbuf[DR_CONV_WINOGRAD4], bias, dst, (float *)net->scratch, n, W, H,
+                                                          c->shape.s2, c->shape.s3, act, in->act_cstride, layer->act_cstride, layer->act_coffset);
         break;
     case DR_CONV_TENSOR:
         if (d->plan && (d->planSrc != src || d->planDst != dst)) {

@@ -1,6 +1,6 @@
 """Single-layer microbenchmarks through the C API of libdeepracin.so (one node per graph).
 
-  python deepracin_b200/layer_bench.py conv CIN COUT HW BATCH [--k 3] [--math tf32|fp32] [--algo auto|direct|winograd|1x1|tensor]
+  python deepracin_b200/layer_bench.py conv CIN COUT HW BATCH [--k 3] [--math tf32|fp32] [--algo auto|direct|winograd|winograd4|1x1|tensor|tensor_winograd]
   python deepracin_b200/layer_bench.py fc NIN NOUT BATCH [--math ...]
   python deepracin_b200/layer_bench.py sweep           # the conv-sweep and 1x1/FC configurations of the benchmark spec
   python deepracin_b200/layer_bench.py vgg [BATCH]     # every distinct VGG-16 3x3 layer shape: direct tensor kernel vs tensor-core Winograd (TF32), Winograd vs direct (FP32)
@@ -61,7 +61,7 @@ def conv_layer(cin, cout, hw, batch, k=3, math="tf32", algo="auto", iters=20, wa
     flops = 2.0 * k * k * cin * cout * hw * hw * batch
     bytes_min = 4.0 * (batch * hw * hw * (cin + cout) + k * k * cin * cout)
     return {"layer": "conv%dx%d %d->%d @%dx%d batch %d" % (k, k, cin, cout, hw, hw, batch), "math": math,
-            "algo": ["auto", "direct", "winograd", "1x1", "tensor", "tensor_winograd"][chosen], "ms": ms, "tflops": flops / ms / 1e9,
+            "algo": ["auto", "direct", "winograd", "1x1", "tensor", "tensor_winograd", "winograd4"][chosen], "ms": ms, "tflops": flops / ms / 1e9,
             "min_bytes": bytes_min, "gbs_at_min_bytes": bytes_min / ms / 1e6, "flop_per_byte": flops / bytes_min, "device_status": status}
 
 
@@ -140,7 +140,7 @@ def sweep(iters, warmup):
 def vgg_layers(batch, iters, warmup):
     out = []
     for cin, cout, hw in ((64, 64, 224), (64, 128, 112), (128, 128, 112), (128, 256, 56), (256, 256, 56), (256, 512, 28), (512, 512, 28), (512, 512, 14)):
-        for math, algo in (("tf32", "tensor"), ("tf32", "tensor_winograd"), ("fp32", "winograd"), ("fp32", "direct")):
+        for math, algo in (("tf32", "tensor"), ("tf32", "tensor_winograd"), ("fp32", "winograd"), ("fp32", "winograd4"), ("fp32", "direct")):
             out.append(conv_layer(cin, cout, hw, batch, 3, math, algo, iters, warmup))
     return out
 

@@ -48,6 +48,18 @@ int dRk_conv2d_winograd_f32(dRk_stream stream, const float *in, const float *U, 
                             float *scratch, int n, int W, int H, int Cin, int Cout, int act, int ldi, int ldo, int coff);
 
 /*
+ * The same convolution (conv2dwinograd2, Kernels/dR_winograd2.cl:23-254) as Winograd F(4x4,3x3) in FP32: 6x6 input tiles,
+ * 36 transform-domain GEMMs, 4x4 outputs per tile; 4x fewer multiplications than the direct sum (F(2x2,3x3): 2.25x) at an
+ * error of about 1e-5 of max|ref| (inside the FP32 class bound of 1e-4, above F(2x2,3x3)'s 1e-6).  U = G g G^T as
+ * [36][Cin][Cout] from dRk_winograd4_pack_weights (w is the reference's [Cin][Cout][3][3] filter array);
+ * scratch must hold dRk_winograd4_scratch_floats() floats.
+ */
+size_t dRk_winograd4_scratch_floats(int n, int W, int H, int Cin, int Cout);
+int dRk_winograd4_pack_weights(const float *w, float *U, int Cin, int Cout);
+int dRk_conv2d_winograd4_f32(dRk_stream stream, const float *in, const float *U, const float *bias, float *out,
+                             float *scratch, int n, int W, int H, int Cin, int Cout, int act, int ldi, int ldo, int coff);
+
+/*
  * Fully connected layer out[b][o] = act(bias[o] + sum_k in[b][k] * w[k][o]); `in` is the
  * N-HWC activation, whose flattening is exactly the (y,x,z) order the reference's kernel
  * reads through mapToDepthMajor (Kernels/dR_fcl.cl:59-120, Kernels/dR_helper.cl:131-142).

@@ -16,9 +16,10 @@ enum dR_ConvAlgo {
     DR_CONV_WINOGRAD = 2,   /* F(2x2,3x3): transform, 16 transform-domain GEMMs, inverse transform */
     DR_CONV_ONEBYONE = 3,   /* 1x1 stride 1 as one GEMM over pixels */
     DR_CONV_TENSOR = 4,     /* tcgen05 TF32 implicit GEMM (TMA-fed, TMEM accumulators) */
-    DR_CONV_TENSOR_WINOGRAD = 5 /* F(2x2,3x3) with the 16 transform-domain GEMMs on the tcgen05 tensor cores (TF32 mode) */
+    DR_CONV_TENSOR_WINOGRAD = 5, /* F(2x2,3x3) with the 16 transform-domain GEMMs on the tcgen05 tensor cores (TF32 mode) */
+    DR_CONV_WINOGRAD4 = 6   /* F(4x4,3x3) in FP32: 36 transform-domain GEMMs, 4x fewer multiplications, error about 1e-5 of max|ref| */
 };
-#define DR_CONV_ALGOS 6
+#define DR_CONV_ALGOS 7
 typedef enum dR_ConvAlgo dR_ConvAlgo;
 
 struct dR_Conv2d_Data {

@@ -53,11 +53,41 @@ def test_conv_winograd_matches_oracle(name, n, cin, cout, h, w, k, stride, act, 
     assert rel_err(got, ref) <= TOL_FP32
 
 
+WINO4_DEEP = [
+    # name, n, cin, cout, h, w: depths and edge sizes of the VGG layers (tiles of 4x4 outputs: 14 and 30 leave ragged edges)
+    ("w4_64_30", 2, 64, 64, 30, 34),
+    ("w4_256_28", 2, 256, 256, 28, 28),
+    ("w4_512_14", 3, 512, 512, 14, 14),
+    ("w4_128to256_9", 1, 128, 256, 9, 11),
+]
+
+
+@pytest.mark.parametrize("name,n,cin,cout,h,w,k,stride", [c for c in CONV_SHAPES if c[6] == 3 and c[7] == 1])
+@pytest.mark.parametrize("act,bias", [(1, True), (0, False)])
+def test_conv_winograd4_matches_oracle(name, n, cin, cout, h, w, k, stride, act, bias):
+    """F(4x4,3x3): 6x6 tiles, 36 transform-domain GEMMs; same bound as every exact-FP32 kernel."""
+    x, wt, b = cases.conv_case(name, n, cin, cout, h, w, k, bias)
+    ref = oracle.conv2d(x, wt, b, (1, 1), act)
+    (got,) = run_graph(conv_build(wt, b, 1, act, algo="winograd4"), [x])
+    assert rel_err(got, ref) <= TOL_FP32
+
+
+@pytest.mark.parametrize("name,n,cin,cout,h,w", WINO4_DEEP)
+def test_conv_winograd4_deep_layers_stay_inside_the_fp32_bound(name, n, cin, cout, h, w):
+    x, wt, b = cases.conv_case(name, n, cin, cout, h, w, 3, True)
+    ref = oracle.conv2d(x, wt, b, (1, 1), 1)
+    (got,) = run_graph(conv_build(wt, b, 1, 1, algo="winograd4"), [x])
+    err = rel_err(got, ref)
+    print(f"{name}: F(4x4,3x3) error {err:.2e} of max|ref|")
+    assert err <= TOL_FP32
+
+
 @pytest.mark.parametrize("name", [n for n, (k, _) in cases.GOLDEN_CASES.items() if k in ("wino", "c1x1")])
 def test_conv_matches_reference_kernel_golden(name):
     kind, kw = cases.GOLDEN_CASES[name]
     x, wt, b = cases.make_inputs(name)
-    for algo in (None, "direct"):       # None: the static rule (3x3 -> Winograd, 1x1 -> 1x1 GEMM)
+    algos = (None, "direct", "winograd4") if kind == "wino" else (None, "direct")
+    for algo in algos:                  # None: the static rule (3x3 -> Winograd, 1x1 -> 1x1 GEMM)
         (got,) = run_graph(conv_build(wt, b, 1, kw["act"], algo=algo), [x])
         assert rel_err(got, GOLD[name]) <= TOL_FP32
 
@@ -71,10 +101,13 @@ def test_static_variant_rule_follows_the_reference():
         b = dr.Conv2d(a, [1, 1, 8, 8], [1, 1, 1, 1], "relu", z((1, 1, 8, 8), np.float32), None)
         c = dr.Conv2d(b, [3, 3, 8, 8], [1, 2, 2, 1], "relu", z((3, 3, 8, 8), np.float32), None)
         d = dr.Conv2d(c, [5, 5, 8, 8], [1, 1, 1, 1], "relu", z((5, 5, 8, 8), np.float32), None)
-        dr.mark_as_output(d)
+        e = dr.Conv2d(d, [3, 3, 8, 32], [1, 1, 1, 1], "relu", z((3, 3, 8, 32), np.float32), None)
+        h = dr.Conv2d(e, [3, 3, 32, 16], [1, 1, 1, 1], "relu", z((3, 3, 32, 16), np.float32), None)
+        dr.mark_as_output(h)
         dr.prepare(g)
-        assert [dr.lib.dR_getConvAlgo(n.ptr) for n in (a, b, c, d)] == [2, 3, 1, 1]
-        assert [dr.lib.dR_getConvTensor(n.ptr) for n in (a, b, c, d)] == [0, 0, 0, 0]
+        # the reference's rule; 3x3 stride-1 layers with >= 16 channels on both sides take the F(4x4,3x3) form of Winograd (6)
+        assert [dr.lib.dR_getConvAlgo(n.ptr) for n in (a, b, c, d, e, h)] == [2, 3, 1, 1, 2, 6]
+        assert [dr.lib.dR_getConvTensor(n.ptr) for n in (a, b, c, d, e, h)] == [0, 0, 0, 0, 0, 0]
 
 
 def test_autotuned_variants_keep_parity():
