@@ -228,22 +228,23 @@ __global__ void __launch_bounds__(256, BM == 128 ? (CONV ? 2 : 1) : 3) k_gemm_f3
  */
 #define AS_STAGES 4
 #define AS_APITCH (BK + 4)          /* floats per staged A row: 16 + 4 keeps rows 16-byte aligned and spreads banks */
-#define AS_BM 128
-#define AS_SMEM(NCH) (AS_STAGES * (AS_BM * AS_APITCH + BK * 64 * (NCH)) * 4)      /* NCH = 64-column chunks per CTA tile: BN = 64 or 128 */
+/* NCH = 64-column chunks per CTA tile (BN = 64 or 128), MR = 64-row groups (BM = 64 or 128; 64 for GEMMs of at most 64 rows: a
+   fully connected layer at batch 17..64) */
+#define AS_SMEM(NCH, MR) (AS_STAGES * (64 * (MR) * AS_APITCH + BK * 64 * (NCH)) * 4)
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, int bytes)
 {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
 
-template <bool CONV, int NCH>
+template <bool CONV, int NCH, int MR>
 __global__ void __launch_bounds__(256, 2) k_gemm_f32_async(const float *__restrict__ A, const float *__restrict__ B, const float *__restrict__ bias,
                                                            float *__restrict__ C, int M, int N, int K, int lda, int ldb, int ldc, int coff, int act,
                                                            size_t strideA, size_t strideB, size_t strideC, int vecC, drk_ConvGeom g)
 {
     extern __shared__ __align__(16) float smem_f[];
     float *As = smem_f;                                         /* [STAGES][BM][APITCH] */
-    constexpr int AS_BN = 64 * NCH;
+    constexpr int AS_BN = 64 * NCH, AS_BM = 64 * MR;
     float *Bs = smem_f + AS_STAGES * AS_BM * AS_APITCH;         /* [STAGES][BK][BN] */
     const uint32_t as_u = (uint32_t)__cvta_generic_to_shared(As), bs_u = (uint32_t)__cvta_generic_to_shared(Bs);
     const int tid = threadIdx.x;
@@ -257,11 +258,11 @@ __global__ void __launch_bounds__(256, 2) k_gemm_f32_async(const float *__restri
        all 16 rows when BN = 64), columns (tid%(BN/4))*4 */
     const int a_kseg = (tid & 3) * 4, a_row0 = tid >> 2;
     const int b_n = (tid % (AS_BN / 4)) * 4, b_k0 = tid / (AS_BN / 4);
-    bool a_ok[2];
-    size_t a_base[2];
-    int a_iy0[2], a_ix0[2];
+    bool a_ok[MR];
+    size_t a_base[MR];
+    int a_iy0[MR], a_ix0[MR];
 #pragma unroll
-    for (int i = 0; i < 2; i++) {
+    for (int i = 0; i < MR; i++) {
         const int m = m0 + a_row0 + 64 * i;
         a_ok[i] = m < M;
         a_base[i] = 0; a_iy0[i] = 0; a_ix0[i] = 0;
@@ -283,7 +284,7 @@ __global__ void __launch_bounds__(256, 2) k_gemm_f32_async(const float *__restri
     auto stage_load = [&](int kt, int slot) {
         const int k = kt * BK + a_kseg;
 #pragma unroll
-        for (int i = 0; i < 2; i++) {
+        for (int i = 0; i < MR; i++) {
             const float *src = A;
             int bytes = 0;
             if (a_ok[i] && k < K) {
@@ -309,9 +310,9 @@ __global__ void __launch_bounds__(256, 2) k_gemm_f32_async(const float *__restri
 
     /* accumulators as pairs of neighbouring columns: one packed FFMA2 (fma.rn.f32x2, two IEEE round-to-nearest FMAs, the same
        results as two scalar ones) per pair halves the instruction and register-port traffic of the 8 x 8 outer product */
-    float2 acc[8][2 * NCH];
+    float2 acc[4 * MR][2 * NCH];
 #pragma unroll
-    for (int i = 0; i < 8; i++)
+    for (int i = 0; i < 4 * MR; i++)
 #pragma unroll
         for (int j = 0; j < 2 * NCH; j++) acc[i][j] = make_float2(0.f, 0.f);
 
@@ -331,9 +332,9 @@ __global__ void __launch_bounds__(256, 2) k_gemm_f32_async(const float *__restri
         const float *bs = Bs + (size_t)slot * BK * AS_BN;
 #pragma unroll
         for (int kk = 0; kk < BK; kk += 4) {
-            float4 a4[8];
+            float4 a4[4 * MR];
 #pragma unroll
-            for (int r = 0; r < 2; r++)
+            for (int r = 0; r < MR; r++)
 #pragma unroll
                 for (int i = 0; i < 4; i++)
                     a4[r * 4 + i] = *reinterpret_cast<const float4 *>(as + (r * 64 + ty * 4 + i) * AS_APITCH + kk);
@@ -346,7 +347,7 @@ __global__ void __launch_bounds__(256, 2) k_gemm_f32_async(const float *__restri
                     b[c * 2 + 0] = make_float2(t.x, t.y); b[c * 2 + 1] = make_float2(t.z, t.w);
                 }
 #pragma unroll
-                for (int i = 0; i < 8; i++) {
+                for (int i = 0; i < 4 * MR; i++) {
                     const float av = k4 == 0 ? a4[i].x : k4 == 1 ? a4[i].y : k4 == 2 ? a4[i].z : a4[i].w;
                     const float2 a2 = make_float2(av, av);
 #pragma unroll
@@ -358,7 +359,7 @@ __global__ void __launch_bounds__(256, 2) k_gemm_f32_async(const float *__restri
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
 #pragma unroll
-    for (int r = 0; r < 2; r++)
+    for (int r = 0; r < MR; r++)
 #pragma unroll
         for (int i = 0; i < 4; i++) {
             const int m = m0 + r * 64 + ty * 4 + i;
@@ -385,7 +386,7 @@ __global__ void __launch_bounds__(256, 2) k_gemm_f32_async(const float *__restri
         }
 }
 
-template <bool CONV, int NCH>
+template <bool CONV, int NCH, int MR>
 static int launch_async(cudaStream_t st, dim3 grid, const float *A, const float *B, const float *bias, float *C, int M, int N, int K, int lda, int ldb,
                         int ldc, int coff, int act, size_t sA, size_t sB, size_t sC, int vecC, const drk_ConvGeom &g)
 {
@@ -394,11 +395,11 @@ static int launch_async(cudaStream_t st, dim3 grid, const float *A, const float 
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_gemm_f32_async<CONV, NCH>, cudaFuncAttributeMaxDynamicSharedMemorySize, AS_SMEM(NCH));
+        cudaError_t e = cudaFuncSetAttribute(k_gemm_f32_async<CONV, NCH, MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, AS_SMEM(NCH, MR));
         if (e != cudaSuccess) return (int)e;
         attr_done[dev] = true;
     }
-    k_gemm_f32_async<CONV, NCH><<<grid, 256, AS_SMEM(NCH), st>>>(A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g);
+    k_gemm_f32_async<CONV, NCH, MR><<<grid, 256, AS_SMEM(NCH, MR), st>>>(A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g);
     return 0;
 }
 
@@ -432,10 +433,20 @@ int drk_gemm_f32_launch(cudaStream_t st, const float *A, const float *B, const f
         const dim3 ga((N + 64 * nch - 1) / (64 * nch), (M + 127) / 128, batch);
         if ((long)ga.x * ga.y * ga.z >= 100 && ga.y <= 65535u && ga.z <= 65535u) {
             int rc;
-            if (nch == 2) rc = geom ? launch_async<true, 2>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g)
-                                    : launch_async<false, 2>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g);
-            else rc = geom ? launch_async<true, 1>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g)
-                           : launch_async<false, 1>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g);
+            if (nch == 2) rc = geom ? launch_async<true, 2, 2>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g)
+                                    : launch_async<false, 2, 2>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g);
+            else rc = geom ? launch_async<true, 1, 2>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g)
+                           : launch_async<false, 1, 2>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g);
+            if (rc) return rc;
+            DRK_COUNT_LAUNCH();
+            return DRK_LAUNCH_RESULT();
+        }
+    }
+    if (vecA && vecB && !geom && M > 16 && M <= 64 && N >= 128) {
+        /* a short, wide product (fully connected layer at batch 17..64, batched over K slices): 64 x 128 tiles */
+        const dim3 ga((N + 127) / 128, 1, batch);
+        if ((long)ga.x * ga.z >= 100 && ga.z <= 65535u) {
+            int rc = launch_async<false, 2, 1>(st, ga, A, B, bias, C, M, N, K, lda, ldb, ldc, coff, act, sA, sB, sC, vecC, g);
             if (rc) return rc;
             DRK_COUNT_LAUNCH();
             return DRK_LAUNCH_RESULT();
