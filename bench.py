@@ -235,6 +235,15 @@ def measure(ctx, net, math, batch, steps, warmup, overlap=True, cuda_graph=False
         if want_profile and ctx.rank == 0:
             lib.dR_synchronize(g.ptr)
             res["profile"] = per_node_profile(dr, lib, g)
+            if math == "fp32":
+                # the FP32 FMA rate this GPU reaches from registers (the library's own probe kernel): the measured
+                # denominator for the FFMA kernels' fractions
+                rate = {}
+                for name, packed in (("ffma2", 1), ("ffma", 0)):
+                    t = ctypes.c_double(0.0)
+                    if lib.dR_probeFfmaRate(g.ptr, packed, ctypes.byref(t)) and t.value > 0:
+                        rate[name] = t.value
+                res["ffma_rate"] = rate
         lib.dR_freePinned(pin_in)
         lib.dR_freePinned(pin_out)
     return res
@@ -455,7 +464,11 @@ def run_ours(args):
             line["fp32_exact"] = {"images_per_s": fp["images_per_s"], "ms_per_step": fp["ms_per_step"], "e2e_images_per_s": fp["e2e_images_per_s"],
                                   "steps": fp["steps"], "dtype": "f32", "conv_tflops_direct_equivalent": fagg, "conv_tflops_executed_ffma": real,
                                   "frac_of_ffma_peak_executed": (real / FFMA_PEAK_NOMINAL) if real else None, "ffma_peak": FFMA_PEAK_NOMINAL,
-                                  "ffma_peak_source": "nominal 148 SMs x 128 lanes x 2 x 1.965 GHz", "ms_per_layer": froof.get("ms_per_layer"),
+                                  "ffma_peak_source": "nominal 148 SMs x 128 lanes x 2 x 1.965 GHz",
+                                  "ffma_rate_measured": fp.get("ffma_rate"),
+                                  "frac_of_ffma_rate_measured_executed": (real / max(fp["ffma_rate"].values())) if real and fp.get("ffma_rate") else None,
+                                  "ffma_rate_source": "dR_probeFfmaRate: 8 x 8 register outer product per thread, no memory traffic, every SM filled; best of three launches",
+                                  "ms_per_layer": froof.get("ms_per_layer"),
                                   "conv_kernel_family_per_layer": families,
                                   "tolerance": "1e-4 x max|ref| per layer (FP32 FFMA arithmetic; F(4x4,3x3) layers measure about 2e-5, F(2x2,3x3) -- the reference's transform -- 1e-6)"}
         if "fp32x3" in extra:

@@ -80,6 +80,7 @@ _SIGS = {
     "dR_getConvTensor": (c_int, [c_void_p]),
     "dR_getConvTensorKernel": (c_int, [c_void_p, POINTER(c_int)]),
     "dR_probeBoundedWait": (c_int, [c_void_p, c_int, POINTER(c_int)]),
+    "dR_probeFfmaRate": (c_int, [c_void_p, c_int, POINTER(c_double)]),
     "dR_feedDataU8Async": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t]),
     "dR_getNodeGpuMs": (c_double, [c_void_p]),
     "dR_getLaunchCount": (c_int, [c_void_p]),

@@ -289,6 +289,22 @@ extern "C" gboolean dR_probeBoundedWait(dR_Graph *net, gint limitMicroseconds, g
     return ok;
 }
 
+extern "C" gboolean dR_probeFfmaRate(dR_Graph *net, gboolean packed, gdouble *tflops)
+{
+    *tflops = 0.0;
+    if (!net->prepared || net->config->dryRun) return FALSE;
+    if (!bindDevice(net)) return FALSE;
+    int sms = 0;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, (int)net->clConfig->clDeviceNumber);
+    const size_t n = (size_t)(sms > 0 ? sms : 256) * 1024;
+    cl_mem sink = NULL;
+    if (!dR_createFloatBufferL(net, &sink, n)) return FALSE;
+    const int rc = dRk_ffma_rate_probe(net->clConfig->clCommandQueue, (float *)sink, n, packed ? 1 : 0, 20000, tflops);
+    gboolean ok = check(net, (cudaError_t)rc, "FFMA rate probe") && dR_finish(net);
+    dR_clMemoryBufferCleanup(net, sink);
+    return ok;
+}
+
 /* --------------------------------------------------------------- double-buffered feeding */
 extern "C" gboolean dR_feedOverlapInit(dR_Graph *net, dR_Node *feed)
 {

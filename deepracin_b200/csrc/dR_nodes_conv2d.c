@@ -224,10 +224,10 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
     }
     c->chosenAlgo = want != DR_CONV_AUTO ? want : staticRule(net, layer);
     c->chosenTensor = (c->chosenAlgo == DR_CONV_TENSOR || c->chosenAlgo == DR_CONV_TENSOR_WINOGRAD) ? (x3Mode(net) ? 2 : 1) : 0;
-    /* conv -> 2x2/2 max pool with no other reader: the tensor kernel's epilogue stores the pooled tensor
-       directly into the pooling node's buffer and the pooling node launches nothing */
+    /* conv -> 2x2/2 max pool with no other reader: the tensor kernel's epilogue (or the F(4x4,3x3) output transform) stores the
+       pooled tensor directly into the pooling node's buffer and the pooling node launches nothing */
     dev(c)->fusedPool = 0;
-    if (c->chosenAlgo == DR_CONV_TENSOR && net->config->fuseGraph && is3x3s1(c) && !layer->output && !layer->elided && layer->next_layers->length == 1 &&
+    if ((c->chosenAlgo == DR_CONV_TENSOR || c->chosenAlgo == DR_CONV_WINOGRAD4) && net->config->fuseGraph && is3x3s1(c) && !layer->output && !layer->elided && layer->next_layers->length == 1 &&
         layer->oshape.s0 % 2 == 0 && layer->oshape.s1 % 2 == 0) {
         dR_Node *nx = (dR_Node *)layer->next_layers->first->element;
         if (nx->type == tPooling && nx->previous_layers->length == 1) {
@@ -235,7 +235,9 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
             const gint ptype = pl->poolingType == tMax ? 1 : pl->poolingType == tAverage ? 2 : 0;
             if (ptype && pl->shape.s1 == 2 && pl->shape.s2 == 2 && pl->shape.s3 == 1 &&
                 pl->stride.s1 == 2 && pl->stride.s2 == 2 && pl->stride.s3 == 1 &&
-                (x3Mode(net) ? ptype == 1 : dRk_tensor_conv_can_fuse_pool(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3, c->shape.s0, c->shape.s1, ptype))) {
+                (c->chosenAlgo == DR_CONV_WINOGRAD4 || x3Mode(net)
+                     ? ptype == 1
+                     : dRk_tensor_conv_can_fuse_pool(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3, c->shape.s0, c->shape.s1, ptype))) {
                 dev(c)->fusedPool = ptype;
                 pl->useLMEM = TRUE;                 /* marks "computed by the producer" for dR_pooling_compute */
                 layer->elided = TRUE;
@@ -415,7 +417,7 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
         break;
     case DR_CONV_WINOGRAD4:
         net->clConfig->clError = dRk_conv2d_winograd4_f32(s, src, (const float *)d->wbuf[DR_CONV_WINOGRAD4], bias, dst, (float *)net->scratch, n, W, H,
-                                                          c->shape.s2, c->shape.s3, act, in->act_cstride, layer->act_cstride, layer->act_coffset);
+                                                          c->shape.s2, c->shape.s3, act, in->act_cstride, layer->act_cstride, layer->act_coffset, d->fusedPool);
         break;
     case DR_CONV_TENSOR:
         if (d->plan && (d->planSrc != src || d->planDst != dst)) {

@@ -27,6 +27,7 @@ template <> struct WVec<1> {
     static __device__ __forceinline__ T add(T a, T b) { return a + b; }
     static __device__ __forceinline__ T sub(T a, T b) { return a - b; }
     static __device__ __forceinline__ T fma(T a, float s, T b) { return fmaf(a, s, b); }      /* a * s + b */
+    static __device__ __forceinline__ T max(T a, T b) { return fmaxf(a, b); }
     static __device__ __forceinline__ T bias_act(T v, const float *bias, int o, int act) { return drk_act(v + (bias ? bias[o] : 0.0f), act); }
 };
 template <> struct WVec<2> {
@@ -35,6 +36,7 @@ template <> struct WVec<2> {
     static __device__ __forceinline__ T add(T a, T b) { return make_float2(a.x + b.x, a.y + b.y); }
     static __device__ __forceinline__ T sub(T a, T b) { return make_float2(a.x - b.x, a.y - b.y); }
     static __device__ __forceinline__ T fma(T a, float s, T b) { return make_float2(fmaf(a.x, s, b.x), fmaf(a.y, s, b.y)); }
+    static __device__ __forceinline__ T max(T a, T b) { return make_float2(fmaxf(a.x, b.x), fmaxf(a.y, b.y)); }
     static __device__ __forceinline__ T bias_act(T v, const float *bias, int o, int act)
     {
         float2 b = bias ? *reinterpret_cast<const float2 *>(bias + o) : make_float2(0.f, 0.f);
@@ -47,6 +49,7 @@ template <> struct WVec<4> {
     static __device__ __forceinline__ T add(T a, T b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
     static __device__ __forceinline__ T sub(T a, T b) { return make_float4(a.x - b.x, a.y - b.y, a.z - b.z, a.w - b.w); }
     static __device__ __forceinline__ T fma(T a, float s, T b) { return make_float4(fmaf(a.x, s, b.x), fmaf(a.y, s, b.y), fmaf(a.z, s, b.z), fmaf(a.w, s, b.w)); }
+    static __device__ __forceinline__ T max(T a, T b) { return make_float4(fmaxf(a.x, b.x), fmaxf(a.y, b.y), fmaxf(a.z, b.z), fmaxf(a.w, b.w)); }
     static __device__ __forceinline__ T bias_act(T v, const float *bias, int o, int act)
     {
         float4 b = bias ? *reinterpret_cast<const float4 *>(bias + o) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -279,7 +282,9 @@ __global__ void __launch_bounds__(256) k_wino4_input(const float *__restrict__ i
     }
 }
 
-template <int VEC>
+/* POOL: the 4x4 outputs of a tile are reduced to their 2x2 block maxima after bias and activation, and stored into the
+   pooled tensor [H/2][W/2] (the 2x2/2 max pooling that follows the layer, evaluated here; W and H even) */
+template <int VEC, bool POOL>
 __global__ void __launch_bounds__(256) k_wino4_output(const float *__restrict__ Mt, const float *__restrict__ bias, float *__restrict__ out,
                                                       int W, int H, int O, int ldo, int coff, int tx, int ty, size_t T, size_t Ts, int act)
 {
@@ -307,21 +312,34 @@ __global__ void __launch_bounds__(256) k_wino4_output(const float *__restrict__ 
             s[r][2] = X::fma(p34, 4.0f, p12);
             s[r][3] = X::add(X::fma(q34, 8.0f, q12), m[5]);
         }
-        const int ox = tix * 4, oy = tiy * 4;
-        float *dst = out + (((size_t)b * H + oy) * W + ox) * ldo + coff + o;
+        vt y[4][4];                                                         /* A^T (.) : y[row][column], bias and activation applied */
 #pragma unroll
-        for (int cx = 0; cx < 4; cx++) {                                    /* A^T (.) : four rows per column */
-            if (ox + cx >= W) continue;
+        for (int cx = 0; cx < 4; cx++) {
             const vt p12 = X::add(s[1][cx], s[2][cx]), q12 = X::sub(s[1][cx], s[2][cx]);
             const vt p34 = X::add(s[3][cx], s[4][cx]), q34 = X::sub(s[3][cx], s[4][cx]);
-            vt y[4];
-            y[0] = X::add(X::add(s[0][cx], p12), p34);
-            y[1] = X::fma(q34, 2.0f, q12);
-            y[2] = X::fma(p34, 4.0f, p12);
-            y[3] = X::add(X::fma(q34, 8.0f, q12), s[5][cx]);
+            y[0][cx] = X::bias_act(X::add(X::add(s[0][cx], p12), p34), bias, o, act);
+            y[1][cx] = X::bias_act(X::fma(q34, 2.0f, q12), bias, o, act);
+            y[2][cx] = X::bias_act(X::fma(p34, 4.0f, p12), bias, o, act);
+            y[3][cx] = X::bias_act(X::add(X::fma(q34, 8.0f, q12), s[5][cx]), bias, o, act);
+        }
+        if (POOL) {
+            const int Wp = W >> 1, Hp = H >> 1, px = tix * 2, py = tiy * 2;
+            float *dst = out + (((size_t)b * Hp + py) * Wp + px) * ldo + coff + o;
+#pragma unroll
+            for (int cy = 0; cy < 2; cy++)
+#pragma unroll
+                for (int cx = 0; cx < 2; cx++)
+                    if (px + cx < Wp && py + cy < Hp)
+                        *reinterpret_cast<vt *>(dst + ((size_t)cy * Wp + cx) * ldo) =
+                            X::max(X::max(y[2 * cy][2 * cx], y[2 * cy][2 * cx + 1]), X::max(y[2 * cy + 1][2 * cx], y[2 * cy + 1][2 * cx + 1]));
+        } else {
+            const int ox = tix * 4, oy = tiy * 4;
+            float *dst = out + (((size_t)b * H + oy) * W + ox) * ldo + coff + o;
 #pragma unroll
             for (int cy = 0; cy < 4; cy++)
-                if (oy + cy < H) *reinterpret_cast<vt *>(dst + ((size_t)cy * W + cx) * ldo) = X::bias_act(y[cy], bias, o, act);
+#pragma unroll
+                for (int cx = 0; cx < 4; cx++)
+                    if (ox + cx < W && oy + cy < H) *reinterpret_cast<vt *>(dst + ((size_t)cy * W + cx) * ldo) = y[cy][cx];
         }
     }
 }
@@ -370,16 +388,19 @@ static void wino4_launch_in(cudaStream_t st, const float *in, float *V, int W, i
 
 template <int VEC>
 static void wino4_launch_out(cudaStream_t st, const float *Mt, const float *bias, float *out, int W, int H, int O, int ldo, int coff,
-                                  int tx, int ty, size_t T, int act)
+                             int tx, int ty, size_t T, int act, int pool)
 {
-    k_wino4_output<VEC><<<drk_blocks(T * (O / VEC), 256, 148u * 32u), 256, 0, st>>>(Mt, bias, out, W, H, O, ldo, coff, tx, ty, T, T, act);
+    const unsigned blocks = drk_blocks(T * (O / VEC), 256, 148u * 32u);
+    if (pool) k_wino4_output<VEC, true><<<blocks, 256, 0, st>>>(Mt, bias, out, W, H, O, ldo, coff, tx, ty, T, T, act);
+    else k_wino4_output<VEC, false><<<blocks, 256, 0, st>>>(Mt, bias, out, W, H, O, ldo, coff, tx, ty, T, T, act);
 }
 
 extern "C" int dRk_conv2d_winograd4_f32(dRk_stream stream, const float *in, const float *U, const float *bias, float *out,
-                                        float *scratch, int n, int W, int H, int Cin, int Cout, int act, int ldi, int ldo, int coff)
+                                        float *scratch, int n, int W, int H, int Cin, int Cout, int act, int ldi, int ldo, int coff, int pool)
 {
     if (n <= 0 || W <= 0 || H <= 0 || Cin <= 0 || Cout <= 0 || !scratch) return -1;
     if (ldi < Cin || ldo < coff + Cout) return -3;
+    if (pool && (pool != 1 || (W & 1) || (H & 1))) return -5;      /* only the 2x2/2 max pooling of an even plane is evaluated here */
     cudaStream_t st = drk_stream(stream);
     const int tx = (W + 3) / 4, ty = (H + 3) / 4;
     const int chunk = wino4_chunk(n, W, H, Cin, Cout);
@@ -392,7 +413,7 @@ extern "C" int dRk_conv2d_winograd4_f32(dRk_stream stream, const float *in, cons
         if (T > 0x7fffffffull) return -2;
         float *V = scratch, *Mt = scratch + 36 * T * Cin;
         const float *src = in + (size_t)b0 * H * W * ldi;
-        float *dst = out + (size_t)b0 * H * W * ldo;
+        float *dst = out + (size_t)b0 * (pool ? (H / 2) * (W / 2) : H * W) * ldo;
         if (vin) wino4_launch_in<2>(st, src, V, W, H, Cin, ldi, tx, ty, T);
         else wino4_launch_in<1>(st, src, V, W, H, Cin, ldi, tx, ty, T);
         DRK_COUNT_LAUNCH();
@@ -401,8 +422,8 @@ extern "C" int dRk_conv2d_winograd4_f32(dRk_stream stream, const float *in, cons
         rc = drk_gemm_f32_launch(st, V, U, NULL, Mt, (int)T, Cout, Cin, Cin, Cout, Cout, 0, 0, 36,
                                  T * Cin, (size_t)Cin * Cout, T * Cout, NULL);
         if (rc) return rc;
-        if (vout) wino4_launch_out<2>(st, Mt, bias, dst, W, H, Cout, ldo, coff, tx, ty, T, act);
-        else wino4_launch_out<1>(st, Mt, bias, dst, W, H, Cout, ldo, coff, tx, ty, T, act);
+        if (vout) wino4_launch_out<2>(st, Mt, bias, dst, W, H, Cout, ldo, coff, tx, ty, T, act, pool);
+        else wino4_launch_out<1>(st, Mt, bias, dst, W, H, Cout, ldo, coff, tx, ty, T, act, pool);
         DRK_COUNT_LAUNCH();
         rc = DRK_LAUNCH_RESULT();
         if (rc) return rc;

@@ -53,6 +53,9 @@ gint dR_getDeviceStatus(dR_Graph *net);
  * would (code 9 in the graph's status word, read by dR_getDeviceStatus) and returns.  result as dRk_bounded_wait_probe.
  * The graph must be prepared; blocks until the probe has finished. */
 gboolean dR_probeBoundedWait(dR_Graph *net, gint limitMicroseconds, gint result[3]);
+/* Measurement support: the FP32 FMA rate of the graph's GPU from registers (dRk_ffma_rate_probe; packed: FFMA2, else scalar
+ * FFMA), in TFLOP/s -- the yardstick for the FFMA kernels.  The graph must be prepared; blocks for a few milliseconds. */
+gboolean dR_probeFfmaRate(dR_Graph *net, gboolean packed, gdouble *tflops);
 /* Double-buffered feeding: dR_feedDataAsync copies on a second stream into the feed node's other interface
  * buffer while the previous batch is still being computed; the next dR_apply waits for that copy and reads it.
  * Before dR_prepare; not combined with CUDA-graph replay or caller-supplied feed buffers. */

@@ -52,12 +52,13 @@ int dRk_conv2d_winograd_f32(dRk_stream stream, const float *in, const float *U, 
  * 36 transform-domain GEMMs, 4x4 outputs per tile; 4x fewer multiplications than the direct sum (F(2x2,3x3): 2.25x) at an
  * error of about 1e-5 of max|ref| (inside the FP32 class bound of 1e-4, above F(2x2,3x3)'s 1e-6).  U = G g G^T as
  * [36][Cin][Cout] from dRk_winograd4_pack_weights (w is the reference's [Cin][Cout][3][3] filter array);
- * scratch must hold dRk_winograd4_scratch_floats() floats.
+ * scratch must hold dRk_winograd4_scratch_floats() floats.  pool = 1: the 2x2/2 max pooling that follows the layer
+ * (src/dR_nodes_pooling.c:138-183) is evaluated by the output transform and out is the pooled [n][H/2][W/2] tensor (W, H even).
  */
 size_t dRk_winograd4_scratch_floats(int n, int W, int H, int Cin, int Cout);
 int dRk_winograd4_pack_weights(const float *w, float *U, int Cin, int Cout);
 int dRk_conv2d_winograd4_f32(dRk_stream stream, const float *in, const float *U, const float *bias, float *out,
-                             float *scratch, int n, int W, int H, int Cin, int Cout, int act, int ldi, int ldo, int coff);
+                             float *scratch, int n, int W, int H, int Cin, int Cout, int act, int ldi, int ldo, int coff, int pool);
 
 /*
  * Fully connected layer out[b][o] = act(bias[o] + sum_k in[b][k] * w[k][o]); `in` is the
@@ -212,6 +213,12 @@ void dRk_tensor_fc_free(dRk_TensorFcPlan *plan);
  * whose wait ran out does, and returns.  result (device int[3]): [0] outcome of that wait (0 = ran out), [1] outcome of
  * a wait on a barrier that was arrived at (1), [2] how long the first wait took, in units of 1024 clocks. */
 int dRk_bounded_wait_probe(dRk_stream stream, int *status, long long limit_cycles, int *result);
+
+/* Measurement support: the FP32 FMA rate of this GPU from registers (an 8 x 8 outer product per thread, the inner step of the
+ * FFMA GEMM, no memory traffic; packed = 1: FFMA2, 0: scalar FFMA), best of three launches of `iters` iterations over every SM.
+ * The yardstick the FFMA kernels' fractions are quoted against; sink is device scratch of at least 1024 floats per SM.
+ * Synchronises the stream. */
+int dRk_ffma_rate_probe(dRk_stream stream, float *sink, size_t sink_floats, int packed, int iters, double *tflops);
 
 /* Debug switches of the library (environment variables DRK_NO_PAIR, DRK_NO_SWAP, DRK_NO_HALO, DRK_NO_INPUT_MAP,
  * DRK_NO_DEP_LAUNCH; read once per process): each takes one kernel variant or launch feature out of use so that two runs can

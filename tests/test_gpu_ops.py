@@ -82,6 +82,32 @@ def test_conv_winograd4_deep_layers_stay_inside_the_fp32_bound(name, n, cin, cou
     assert err <= TOL_FP32
 
 
+@pytest.mark.parametrize("n,cin,cout,h,w,act", [(2, 32, 32, 12, 16, 1), (3, 64, 128, 14, 14, 1), (1, 16, 48, 30, 26, 0), (2, 128, 64, 28, 28, 1)])
+def test_winograd4_with_fused_maxpool_matches_oracle(n, cin, cout, h, w, act):
+    """FP32 mode, conv3x3 followed by 2x2/2 max pooling: the F(4x4,3x3) output transform stores the pooled tensor (each 4x4 tile
+    holds four whole pooling windows) and the pooling node launches nothing; identical to the unfused pair bit for bit."""
+    x, wt, b = cases.conv_case("w4pool_%d_%d" % (cin, h), n, cin, cout, h, w, 3, True)
+    ref = oracle.pool(oracle.conv2d(x, wt, b, (1, 1), act), (2, 2, 1), (2, 2, 1), 0)
+    res = {}
+    for fuse in (True, False):
+        with dr.Environment() as env:
+            g = env.create_graph("CHW")
+            g.batch = n
+            g.fuse = fuse
+            f = dr.feed_node(g, [cin, h, w])
+            c = conv_build(wt, b, 1, act)(g, [f])
+            o = dr.Pooling(c, "max", [1, 2, 2, 1], [1, 2, 2, 1])
+            dr.mark_as_output(o)
+            dr.prepare(g)
+            assert dr.lib.dR_getConvAlgo(c.ptr) == dr.CONV_ALGO["winograd4"]
+            dr.feed_data(f, x)
+            res[fuse] = dr.apply(g)[0].reshape(ref.shape)
+            # feed layout, input transform, GEMM, output transform(+pool), [pool], output layout
+            assert dr.lib.dR_getLaunchCount(g.ptr) == (5 if fuse else 6)
+    assert rel_err(res[True], ref) <= TOL_FP32
+    assert np.array_equal(res[True], res[False])
+
+
 @pytest.mark.parametrize("name", [n for n, (k, _) in cases.GOLDEN_CASES.items() if k in ("wino", "c1x1")])
 def test_conv_matches_reference_kernel_golden(name):
     kind, kw = cases.GOLDEN_CASES[name]
