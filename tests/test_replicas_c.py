@@ -50,7 +50,9 @@ def test_replicas_classify_the_reference_images(tmp_path):
     exe = build_client(tmp_path)
     d = oracle.staged_squeezenet_dir()
     imgs = [os.path.join(d, n + "_224x224x3_rgb_hwc.f32") for n in ("tiger", "puzzle")]
-    r = subprocess.run([exe, d, "2", "0", "0"] + imgs, capture_output=True, text=True, timeout=600)
+    import torch
+    second = "1" if torch.cuda.device_count() >= 2 else "0"
+    r = subprocess.run([exe, d, "2", "0", second] + imgs, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout + r.stderr
     classes = [int(line.split()[1]) for line in r.stdout.splitlines() if line.startswith("class ")]
     assert classes == [292, 611, 292, 611]
@@ -58,7 +60,8 @@ def test_replicas_classify_the_reference_images(tmp_path):
 
 @pytest.mark.gpu
 def test_replicas_equal_one_graph_on_the_whole_batch(tmp_path):
-    """2 replicas x batch 2 (both on device 0) against one graph at batch 4 on the same saved model: identical outputs."""
+    """2 replicas x batch 2 (on devices 0 and 1 where the box has two GPUs, else both on device 0) against one graph at batch 4 on
+    the same saved model: identical outputs."""
     lib = dr.lib
     imgs = nets.synthetic_images("replicas_c", 4, 32)
     with dr.Environment() as env:
@@ -82,7 +85,9 @@ def test_replicas_equal_one_graph_on_the_whole_batch(tmp_path):
     lib.dR_replicasDestroy.argtypes = [ctypes.c_void_p]
     lib.dR_replicasInputFloatsPerImage.restype = ctypes.c_size_t
     lib.dR_replicasInputFloatsPerImage.argtypes = [ctypes.c_void_p]
-    ordinals = (ctypes.c_int * 2)(0, 0)
+    import torch
+    ordinals = (ctypes.c_int * 2)(0, 1 if torch.cuda.device_count() >= 2 else 0)
+    print("replica devices:", list(ordinals))
     r = lib.dR_replicasLoad(2, ordinals, 2, str(tmp_path / "dr_graph_export").encode(), 1, 1)
     assert r
     assert lib.dR_replicasInputFloatsPerImage(r) == 32 * 32 * 3
