@@ -105,7 +105,7 @@ gboolean dR_fc_allocateBuffers(dR_Graph *net, dR_Node *layer)
     dR_FC_Data *fc = (dR_FC_Data *)layer->layer;
     gboolean ret;
     if (!fc->hasVariables) { g_print("FullyConnected Layer %d has no weights (call dR_FullyConnected_setVariables)\n", layer->layerID); return FALSE; }
-    if (fc->chosenTensor) ret = dR_createFloatBufferL(net, &fc->weightsBufT, (size_t)fc->shape.s0 * fc->shape.s1);
+    if (fc->chosenTensor) ret = dR_createFloatBufferL(net, &fc->weightsBufT, dRk_tensor_fc_packed_floats(fc->shape.s0, fc->shape.s1));
     else ret = dR_createFloatBufferL(net, &fc->weightsBuf, (size_t)fc->shape.s0 * fc->shape.s1);
     if (fc->useBias) ret &= dR_createFloatBuffer(net, &fc->biasBuf, fc->shape.s1, CL_MEM_READ_ONLY);
     return ret;
@@ -116,13 +116,11 @@ gboolean dR_fc_fillBuffers(dR_Graph *net, dR_Node *layer)
     dR_FC_Data *fc = (dR_FC_Data *)layer->layer;
     gboolean ret;
     if (fc->chosenTensor) {
-        /* K-major packing [Nout][Nin] for the TMA-fed B operand */
-        const size_t nin = (size_t)fc->shape.s0, nout = (size_t)fc->shape.s1;
-        gfloat *t = (gfloat *)g_malloc(nin * nout * sizeof(gfloat));
-        for (size_t k0 = 0; k0 < nin; k0 += 64)
-            for (size_t o = 0; o < nout; o++)
-                for (size_t k = k0; k < nin && k < k0 + 64; k++) t[o * nin + k] = fc->weights[k * nout + o];
-        ret = dR_uploadArray(net, "", t, 0, nin * nout * sizeof(cl_float), fc->weightsBufT);
+        /* block-by-block packing for the TMA-fed B operand */
+        const size_t np = dRk_tensor_fc_packed_floats(fc->shape.s0, fc->shape.s1);
+        gfloat *t = (gfloat *)g_malloc(np * sizeof(gfloat));
+        ret = dRk_tensor_fc_pack_weights(fc->weights, t, fc->shape.s0, fc->shape.s1) == 0 &&
+              dR_uploadArray(net, "", t, 0, np * sizeof(cl_float), fc->weightsBufT);
         g_free(t);
     } else {
         ret = dR_uploadArray(net, "", fc->weights, 0, (size_t)fc->shape.s0 * fc->shape.s1 * sizeof(cl_float), fc->weightsBuf);

@@ -103,7 +103,8 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                 for (int tap = 0; tap < p.taps && pre < C::STAGES; tap++)
                     for (int ks = ks0; ks < ks1 && pre < C::STAGES; ks++, pre++) {
                         mbar_expect_tx(full_bar(pre), (uint32_t)p.stage_tx);
-                        tma_load_2d(base + pre * C::STAGE_BYTES + A_STAGE_BYTES, &mapB, tap * p.CinPad + ks * BK, brow, full_bar(pre));
+                        if (p.bpacked) tma_load_2d(base + pre * C::STAGE_BYTES + A_STAGE_BYTES, &mapB, 0, (nt * p.kslabs + ks) * BN, full_bar(pre));
+                        else tma_load_2d(base + pre * C::STAGE_BYTES + A_STAGE_BYTES, &mapB, tap * p.CinPad + ks * BK, brow, full_bar(pre));
                     }
             }
             drk_dep_wait();
@@ -133,7 +134,10 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                                 tma_load_4d(sa + q * sub_bytes, &mapA, ks * BK, txi * p.TW + kx - p.pad, tyi * p.TH + ky - p.pad, img, full_bar(stage));
                             }
                         }
-                        if (!armed) tma_load_2d(sb, &mapB, tap * p.CinPad + ks * BK, brow, full_bar(stage));
+                        if (!armed) {
+                            if (p.bpacked) tma_load_2d(sb, &mapB, 0, (nt * p.kslabs + ks) * BN, full_bar(stage));
+                            else tma_load_2d(sb, &mapB, tap * p.CinPad + ks * BK, brow, full_bar(stage));
+                        }
                         issued++;
                         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
                     }
@@ -1431,8 +1435,8 @@ extern "C" void dRk_tensor_conv_free(dRk_TensorConvPlan *pl) { free(pl); }
 
 /*
  * Fully connected layer on the tensor cores (TF32 mode, larger batches): the activations [n][Nin] are the
- * A operand of a flat GEMM (rows past the batch are TMA zero fill), the K-major weights [Nout][Nin] the
- * B operand with N = 256 per tile; K is split over enough CTAs to occupy every SM, the partial products
+ * A operand of a flat GEMM (rows past the batch are TMA zero fill), the weights the B operand with N = 256 per tile,
+ * stored block by block (256 output columns x 32 inputs = one TMA request = one contiguous 32 KiB run); K is split over enough CTAs to occupy every SM, the partial products
  * land in `scratch` ([ksplit][n][Nout]) and the reduce kernel of the FP32 path adds bias and activation.
  * Bound: HBM (weights read once).  Replaces matrixVectorMultFirst/Second (Kernels/dR_fcl.cl:59-120).
  */
@@ -1461,6 +1465,30 @@ extern "C" size_t dRk_tensor_fc_scratch_floats(int n, int Nin, int Nout)
     const int kslabs = Nin / BK;
     if (ksplit > kslabs / 8) ksplit = kslabs / 8 > 0 ? kslabs / 8 : 1;
     return (size_t)ksplit * n * Nout;
+}
+
+extern "C" size_t dRk_tensor_fc_packed_floats(int Nin, int Nout)
+{
+    if (Nin <= 0 || Nout <= 0 || Nin % BK != 0) return 0;
+    return (size_t)((Nout + 255) / 256) * 256 * (size_t)Nin;
+}
+
+/* [n tile][K slab][256 output columns][32 inputs]: block (nt, ks) holds w[ks*32 + e][nt*256 + r] at [r][e]; columns past Nout are zeros */
+extern "C" int dRk_tensor_fc_pack_weights(const float *w, float *wpacked, int Nin, int Nout)
+{
+    if (!w || !wpacked || Nin <= 0 || Nout <= 0 || Nin % BK != 0) return -1;
+    const int ntiles = (Nout + 255) / 256, kslabs = Nin / BK;
+    for (int nt = 0; nt < ntiles; nt++)
+        for (int ks = 0; ks < kslabs; ks++) {
+            float *blk = wpacked + ((size_t)nt * kslabs + ks) * 256 * BK;
+            for (int e = 0; e < BK; e++) {
+                const float *src = w + (size_t)(ks * BK + e) * Nout + (size_t)nt * 256;
+                const int valid = Nout - nt * 256 < 256 ? Nout - nt * 256 : 256;
+                for (int r = 0; r < valid; r++) blk[(size_t)r * BK + e] = src[r];
+                for (int r = valid; r < 256; r++) blk[(size_t)r * BK + e] = 0.0f;
+            }
+        }
+    return 0;
 }
 
 extern "C" dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wT, const float *bias, float *out, float *scratch,
@@ -1495,10 +1523,12 @@ extern "C" dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wT
     const cuuint32_t abox[2] = {BK, BM};
     CUresult r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)in, adims, astr, abox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    const cuuint64_t bdims[2] = {(cuuint64_t)Nin, (cuuint64_t)Nout};
+    /* the packed weights as a 32-wide matrix whose rows are the blocks' rows one after another */
+    p.bpacked = 1;
+    const cuuint64_t bdims[2] = {(cuuint64_t)BK, (cuuint64_t)p.n_tiles * p.kslabs * 256}, bstr[1] = {(cuuint64_t)BK * 4};
     const cuuint32_t bbox[2] = {BK, 256};
     if (r == CUDA_SUCCESS)
-        r = enc(&pl->mapB, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)wT, bdims, astr, bbox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        r = enc(&pl->mapB, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)wT, bdims, bstr, bbox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { fprintf(stderr, "tensor fc plan: tensor map rejected (%d)\n", (int)r); free(fp); return NULL; }
     const long long tiles = (long long)p.n_tiles * p.ksplit;

@@ -197,12 +197,16 @@ int dRk_tensor_winograd_run(dRk_stream stream, dRk_TensorWinogradPlan *plan);
 void dRk_tensor_winograd_free(dRk_TensorWinogradPlan *plan);
 
 /* Fully connected layer on the tensor cores (TF32 inputs, FP32 accumulate) for batches of 16..128 with
- * Nin % 32 == 0 and Nout % 4 == 0 (>= 64): split-K flat GEMM + the reduce step of dRk_fc_f32.  wT is [Nout][Nin]
- * (K contiguous); scratch holds dRk_tensor_fc_scratch_floats() floats.  Same reference kernels as dRk_fc_f32. */
+ * Nin % 32 == 0 and Nout % 4 == 0 (>= 64): split-K flat GEMM + the reduce step of dRk_fc_f32.  wpacked comes from
+ * dRk_tensor_fc_pack_weights (w is the reference's [Nin][Nout] matrix; dRk_tensor_fc_packed_floats() floats): every
+ * 256-column x 32-row block the kernel fetches in one TMA request is one contiguous 32 KiB run, so the weight stream reads
+ * DRAM sequentially.  scratch holds dRk_tensor_fc_scratch_floats() floats.  Same reference kernels as dRk_fc_f32. */
 typedef struct dRk_TensorFcPlan dRk_TensorFcPlan;
 int dRk_tensor_fc_supported(int n, int Nin, int Nout);
 size_t dRk_tensor_fc_scratch_floats(int n, int Nin, int Nout);
-dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wT, const float *bias, float *out, float *scratch,
+size_t dRk_tensor_fc_packed_floats(int Nin, int Nout);
+int dRk_tensor_fc_pack_weights(const float *w, float *wpacked, int Nin, int Nout);
+dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wpacked, const float *bias, float *out, float *scratch,
                                      int n, int Nin, int Nout, int act, int *status);
 int dRk_tensor_fc_run(dRk_stream stream, dRk_TensorFcPlan *plan);
 void dRk_tensor_fc_free(dRk_TensorFcPlan *plan);
