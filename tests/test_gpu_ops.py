@@ -157,6 +157,21 @@ def test_fc_matches_oracle(n, c, h, w, nout, act, bias):
     assert rel_err(got, ref) <= TOL_FP32
 
 
+@pytest.mark.parametrize("n", [2, 4, 5, 12, 16, 17, 24, 32, 33, 64])
+@pytest.mark.parametrize("c,h,w,nout", [(41, 10, 10, 132), (64, 8, 9, 1000)])
+def test_fc_streaming_kernels_on_ragged_shapes(n, c, h, w, nout):
+    """Every batch-size class of the weight-streaming path (2, 4, 8 and 16 rows per pass, passes of 16 with a shorter last one, the
+    K-sliced GEMM above 32 rows) on shapes whose K slices end inside an input stage (Nin = 4100, 4608) and whose last column block is
+    partly empty (Nout = 132, 1000)."""
+    x, wt, b = cases.fc_case("fcr%d_%d" % (c * h * w, nout), n, c, h, w, nout, True)
+    ref = oracle.fc(x, wt, b, 1)
+
+    def build(g, f):
+        return dr.Fully_Connected(f[0], [c * h * w, nout], "relu", wt, b)
+    (got,) = run_graph(build, [x])
+    assert rel_err(got, ref) <= TOL_FP32
+
+
 @pytest.mark.parametrize("name", ["fc_3x2x8_to_20", "fc_4x4x16_to_64_linear"])
 def test_fc_matches_reference_kernel_golden(name):
     kind, kw = cases.GOLDEN_CASES[name]
