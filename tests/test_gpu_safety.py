@@ -88,7 +88,9 @@ GUARD_CONVS = [
     ("g_1x1_odd", 3, 32, 72, 9, 7, 1, "tf32"),
     ("g_halo_13x17", 3, 64, 200, 17, 13, 3, "tf32"),
     ("g_first_c3", 3, 3, 48, 17, 13, 3, "tf32"),            # producer-gather first layer, pixel count not a multiple of its tile
-    ("g_wino_odd", 2, 16, 20, 11, 9, 3, "fp32"),            # FP32 Winograd with ragged 2x2 output tiles
+    ("g_wino_odd", 2, 8, 20, 11, 9, 3, "fp32"),             # FP32 Winograd F(2x2,3x3) with ragged 2x2 output tiles
+    ("g_wino4_odd", 2, 16, 20, 11, 9, 3, "fp32"),           # F(4x4,3x3): ragged 4x4 output tiles, Cout ends inside a warp
+    ("g_wino4_c17", 3, 17, 19, 14, 6, 3, "fp32"),           # odd channel counts: scalar transform path
     ("g_direct_5x5", 2, 6, 10, 9, 13, 5, "fp32"),
     ("g_1x1_fp32", 2, 24, 52, 7, 5, 1, "fp32"),
     ("g_first_fp32", 2, 3, 20, 9, 11, 3, "fp32"),
@@ -104,18 +106,21 @@ def test_convolution_stores_stay_inside_the_output_tensor(name, n, cin, cout, h,
     assert rel_err(out, ref) <= (TOL_TF32 if math == "tf32" else TOL_FP32)
 
 
-@pytest.mark.parametrize("name,n,cin,cout,h,w", [("gp_swap", 40, 8, 72, 30, 26), ("gp_pair", 6, 16, 64, 56, 56), ("gp_halo", 2, 32, 136, 12, 20), ("gp_first", 2, 3, 64, 18, 22)])
-def test_fused_pool_stores_stay_inside_the_output_tensor(name, n, cin, cout, h, w):
-    """conv3x3 + 2x2/2 max pool evaluated by the convolution's epilogue: the guarded buffer is the POOLING node's output."""
+@pytest.mark.parametrize("name,n,cin,cout,h,w,math", [("gp_swap", 40, 8, 72, 30, 26, "tf32"), ("gp_pair", 6, 16, 64, 56, 56, "tf32"),
+                                                       ("gp_halo", 2, 32, 136, 12, 20, "tf32"), ("gp_first", 2, 3, 64, 18, 22, "tf32"),
+                                                       ("gp_wino4", 3, 16, 36, 14, 10, "fp32"), ("gp_wino4_c17", 2, 17, 21, 6, 18, "fp32")])
+def test_fused_pool_stores_stay_inside_the_output_tensor(name, n, cin, cout, h, w, math):
+    """conv3x3 + 2x2/2 max pool evaluated by the convolution's epilogue (FP32 mode: by the F(4x4,3x3) output transform): the
+    guarded buffer is the POOLING node's output."""
     x, wt, b = cases.conv_case(name, n, cin, cout, h, w, 3, True)
     ref = oracle.pool(oracle.conv2d(x, wt, b, (1, 1), 1), (2, 2, 1), (2, 2, 1), 0)
 
     def build(lib, g, f):
         c = conv_node(wt, b)(lib, g, f)
         return lib.dR_Pooling(g, c, pointer(Shape4(1, 2, 2, 1)), pointer(Shape4(1, 2, 2, 1)), 0)
-    out, front, back = guarded_run(build, x, ref.shape, "tf32")
+    out, front, back = guarded_run(build, x, ref.shape, math)
     check_guards(out, front, back)
-    assert rel_err(out, ref) <= TOL_TF32
+    assert rel_err(out, ref) <= (TOL_TF32 if math == "tf32" else TOL_FP32)
 
 
 @pytest.mark.parametrize("math", ["fp32", "tf32"])
@@ -136,7 +141,8 @@ def test_channel_offset_stores_into_a_concat_buffer(math):
     assert rel_err(out, ref) <= (TOL_TF32 if math == "tf32" else TOL_FP32)
 
 
-@pytest.mark.parametrize("n,c,h,w,nout,math", [(3, 5, 3, 7, 37, "fp32"), (20, 64, 2, 2, 72, "tf32"), (17, 8, 4, 4, 1000, "fp32")])
+@pytest.mark.parametrize("n,c,h,w,nout,math", [(3, 5, 3, 7, 37, "fp32"), (20, 64, 2, 2, 72, "tf32"), (17, 8, 4, 4, 1000, "fp32"),
+                                               (5, 33, 4, 4, 132, "fp32"), (19, 33, 4, 4, 132, "fp32"), (40, 16, 4, 4, 200, "fp32")])
 def test_fully_connected_stores_stay_inside_the_output_tensor(n, c, h, w, nout, math):
     x, wt, b = cases.fc_case("gfc_%d" % nout, n, c, h, w, nout, True)
     ref = oracle.fc(x, wt, b, 1)
