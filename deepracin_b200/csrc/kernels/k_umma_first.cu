@@ -38,8 +38,12 @@
 template <int CIN, int G>
 struct FirstCfg {
     static constexpr int K = 9 * CIN;
-    static constexpr int KS = (K + BK - 1) / BK;                   /* 128-byte slabs per pixel patch */
-    static constexpr int NMMA = (K + 7) / 8;                       /* MMAs (K = 8) per group */
+    /* two more K columns carry the bias: every patch row holds 1.0 there and the filter row the bias split into a TF32 high part
+       and the TF32 of the remainder (exact to 2^-21 of the bias), so the accumulator leaves the MMA with the bias added and the
+       epilogue -- which is what bounds this kernel -- saves an addition per output.  They fit the zero padding of the last slab. */
+    static constexpr int KB = K + 2;
+    static constexpr int KS = (KB + BK - 1) / BK;                  /* 128-byte slabs per pixel patch */
+    static constexpr int NMMA = (KB + 7) / 8;                      /* MMAs (K = 8) per group */
     static constexpr int CP = BM / G;                              /* rows (channels) per group */
     static constexpr int SLABS = G * KS;
     static constexpr int A_BYTES = SLABS * BM * BK * 4;
@@ -83,17 +87,17 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-/* stores 32 consecutive pixels of one channel: bias, activation clamp, pixel stride ldo */
-__device__ __forceinline__ float *store32(float *optr, const uint32_t (&r)[32], float bv, float lo, float hi, size_t ldo, long long left, bool chok)
+/* stores 32 consecutive pixels of one channel: activation clamp (the bias came through the MMA), pixel stride ldo */
+__device__ __forceinline__ float *store32(float *optr, const uint32_t (&r)[32], float lo, float hi, size_t ldo, long long left, bool chok)
 {
     if (chok) {
         if (left >= 32) {
 #pragma unroll
-            for (int j = 0; j < 32; j++) optr[j * ldo] = fminf(fmaxf(__uint_as_float(r[j]) + bv, lo), hi);
+            for (int j = 0; j < 32; j++) optr[j * ldo] = fminf(fmaxf(__uint_as_float(r[j]), lo), hi);
         } else {
 #pragma unroll
             for (int j = 0; j < 32; j++)
-                if (j < left) optr[j * ldo] = fminf(fmaxf(__uint_as_float(r[j]) + bv, lo), hi);
+                if (j < left) optr[j * ldo] = fminf(fmaxf(__uint_as_float(r[j]), lo), hi);
         }
     }
     return optr + 32 * ldo;
@@ -156,7 +160,17 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
             const int k = ks * BK + chunk * 4 + e;
             int kw = k;                                             /* column of the packed filters this K position multiplies */
             if (MAPPED && k < C::K) { const int tap = k / CIN; kw = tap * CIN + map.inv[k - tap * CIN]; }
-            v[e] = (ch >= 0 && ch < Cout && k < C::K) ? to_tf32(__ldg(wT + (size_t)ch * C::K + kw)) : 0u;
+            float wv = 0.0f;
+            if (ch >= 0 && ch < Cout) {
+                if (k < C::K) wv = __ldg(wT + (size_t)ch * C::K + kw);
+                else if (k < C::KB && bias) {
+                    const float bfull = __ldg(bias + ch);
+                    const float bhi = __uint_as_float(to_tf32(bfull));
+                    wv = k == C::K ? bhi : bfull - bhi;
+                }
+            }
+            /* 2x2 average pooling: the 1/4 goes into the filters and the bias (a power of two: exact, and it commutes with the clamp) */
+            v[e] = to_tf32(pool == 2 ? 0.25f * wv : wv);
         }
         *reinterpret_cast<uint4 *>(gen + slab * (BM * BK * 4) + swz(row, chunk)) = make_uint4(v[0], v[1], v[2], v[3]);
     }
@@ -205,11 +219,9 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
         const int ch = pooled ? quarter * 16 + (lane & 15) : row - grp * C::CP;
         if ((pooled ? quarter * 16 : (quarter * 32) % C::CP) < Cout) {
             const bool chok = ch < Cout;
-            const float bv = (bias && chok) ? __ldg(bias + ch) : 0.0f;
-            const float lo = act ? 0.0f : -INFINITY, hi = act ? FLT_MAX : INFINITY;
+            const float lo = act ? 0.0f : -INFINITY, hi = act ? FLT_MAX : INFINITY;       /* the bias is already in the accumulator */
             int it = 0;
             if (pooled) {
-                const float inv = pool == 2 ? 0.25f : 1.0f;
                 for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, it++) {
                     const int acc = it & 1;
                     const uint32_t acc_phase = (uint32_t)(it >> 1) & 1u;
@@ -217,7 +229,10 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
                     tc_fence_after();
                     const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * FIRST_N + half * (FIRST_N / 2));
                     const long long f0 = (long long)t * FIRST_N + half * (FIRST_N / 2);
-                    /* pooled pixels are consecutive: (f0 + c0)/2 + k; lanes of group 0 store the even k, group 1 the odd k */
+                    /* pooled pixels are consecutive: (f0 + c0)/2 + k.  A lane holds the horizontal halves of its own row (group 0:
+                       row 2j, group 1: row 2j+1) for all 16 of them; of every two neighbours the lane of group 0 finishes the
+                       even one and the lane of group 1 the odd one, so ONE shuffle per two pixels hands each lane the half it
+                       lacks, and every lane stores only what it finished. */
                     float *optr = out + (size_t)((f0 >> 1) + grp) * ldo + coff + (chok ? ch : 0);
                     long long left = (total_f >> 1) - (f0 >> 1) - grp;
 #pragma unroll 1
@@ -225,12 +240,14 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
                         uint32_t r[32];
                         tmem_ld32(taddr + (uint32_t)c0, r);
 #pragma unroll
-                        for (int k = 0; k < 16; k++) {
-                            const float a = fminf(fmaxf(__uint_as_float(r[2 * k]) + bv, lo), hi), b = fminf(fmaxf(__uint_as_float(r[2 * k + 1]) + bv, lo), hi);
-                            float h = pool == 2 ? a + b : fmaxf(a, b);
-                            const float o = __shfl_xor_sync(0xffffffffu, h, 16);
-                            h = pool == 2 ? (h + o) * inv : fmaxf(h, o);
-                            if ((k & 1) == grp && chok && k < left + grp) optr[(size_t)(k - grp) * ldo] = h;
+                        for (int k = 0; k < 16; k += 2) {
+                            const float a0 = fminf(fmaxf(__uint_as_float(r[2 * k]), lo), hi), b0 = fminf(fmaxf(__uint_as_float(r[2 * k + 1]), lo), hi);
+                            const float a1 = fminf(fmaxf(__uint_as_float(r[2 * k + 2]), lo), hi), b1 = fminf(fmaxf(__uint_as_float(r[2 * k + 3]), lo), hi);
+                            const float h0 = pool == 2 ? a0 + b0 : fmaxf(a0, b0), h1 = pool == 2 ? a1 + b1 : fmaxf(a1, b1);
+                            const float got = __shfl_xor_sync(0xffffffffu, grp ? h0 : h1, 16);
+                            const float mine = grp ? h1 : h0;
+                            const float o = pool == 2 ? mine + got : fmaxf(mine, got);
+                            if (chok && k < left) optr[(size_t)k * ldo] = o;
                         }
                         optr += 16 * (size_t)ldo;
                         left -= 16;
@@ -253,18 +270,18 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
                 tmem_ld32_nowait(taddr, r0);
                 tmem_ld_wait();
                 tmem_ld32_nowait(taddr + 32u, r1);
-                optr = store32(optr, r0, bv, lo, hi, (size_t)ldo, total_px - g0, chok);
+                optr = store32(optr, r0, lo, hi, (size_t)ldo, total_px - g0, chok);
                 tmem_ld_wait();
                 tmem_ld32_nowait(taddr + 64u, r0);
-                optr = store32(optr, r1, bv, lo, hi, (size_t)ldo, total_px - g0 - 32, chok);
+                optr = store32(optr, r1, lo, hi, (size_t)ldo, total_px - g0 - 32, chok);
                 tmem_ld_wait();
                 tmem_ld32_nowait(taddr + 96u, r1);
-                optr = store32(optr, r0, bv, lo, hi, (size_t)ldo, total_px - g0 - 64, chok);
+                optr = store32(optr, r0, lo, hi, (size_t)ldo, total_px - g0 - 64, chok);
                 tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tempty_bar(acc));         /* the accumulator is in registers: the MMAs of the tile after next may start */
-                store32(optr, r1, bv, lo, hi, (size_t)ldo, total_px - g0 - 96, chok);
+                store32(optr, r1, lo, hi, (size_t)ldo, total_px - g0 - 96, chok);
             }
         }
     } else {
@@ -306,6 +323,7 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
                     }
                 }
                 if (inside) {
+                    v[grp][C::K] = v[grp][C::K + 1] = 0x3f800000u;           /* 1.0 in the two bias columns */
                     const float *pix = in + (size_t)g * ldi;                 /* the centre pixel */
 #pragma unroll
                     for (int ky = 0; ky < 3; ky++) {
@@ -332,7 +350,7 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
                 for (int ck = 0; ck < C::KS * 8; ck++) {
                     const int slab = grp * C::KS + (ck >> 3), chunk = ck & 7;
                     uint4 o;
-                    if (ck * 4 < C::K) o = make_uint4(to_tf32(__uint_as_float(v[grp][ck * 4])), to_tf32(__uint_as_float(v[grp][ck * 4 + 1])),
+                    if (ck * 4 < C::KB) o = make_uint4(to_tf32(__uint_as_float(v[grp][ck * 4])), to_tf32(__uint_as_float(v[grp][ck * 4 + 1])),
                                                       to_tf32(__uint_as_float(v[grp][ck * 4 + 2])), to_tf32(__uint_as_float(v[grp][ck * 4 + 3])));
                     else o = make_uint4(0u, 0u, 0u, 0u);
                     *reinterpret_cast<uint4 *>(stage + slab * (FIRST_N * BK * 4) + swz(col, chunk)) = o;
