@@ -303,12 +303,19 @@ k_umma_conv_first(const float *__restrict__ in, const float *__restrict__ wT, co
                 if (G == 2 && pool) {
                     const long long f = (long long)t * FIRST_N + col;
                     inside = f < total_f;
-                    const long long jq = f / W;
-                    x = (int)(f - jq * W);
                     const int hh = H >> 1;
-                    const long long img = jq / hh;
-                    y = 2 * (int)(jq - img * hh) + grp;
-                    g = (img * H + y) * W + x;
+                    if (small) {                                    /* 32-bit divisions: a 64-bit one costs as much as the rest of the gather */
+                        const unsigned fu = (unsigned)f, jq = fu / (unsigned)W, img = jq / (unsigned)hh;
+                        x = (int)(fu - jq * (unsigned)W);
+                        y = 2 * (int)(jq - img * (unsigned)hh) + grp;
+                        g = ((long long)img * H + y) * W + x;
+                    } else {
+                        const long long jq = f / W;
+                        x = (int)(f - jq * W);
+                        const long long img = jq / hh;
+                        y = 2 * (int)(jq - img * hh) + grp;
+                        g = (img * H + y) * W + x;
+                    }
                 } else {
                     g = (long long)t * TILE_PX + grp * FIRST_N + col;
                     inside = g < total_px;
