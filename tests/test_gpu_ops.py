@@ -82,6 +82,39 @@ def test_conv_winograd4_deep_layers_stay_inside_the_fp32_bound(name, n, cin, cou
     assert err <= TOL_FP32
 
 
+def _random_fp32_shapes(count, seed):
+    r = np.random.Generator(np.random.PCG64(seed))
+    out = []
+    for i in range(count):
+        k = int(r.choice([1, 3, 3, 3, 5]))
+        stride = 2 if (k == 3 and r.random() < 0.15) else 1
+        cin = int(r.integers(1, 6)) if r.random() < 0.2 else int(r.integers(8, 97))
+        cout = int(r.integers(4, 97))
+        h, w = int(r.integers(5, 41)), int(r.integers(5, 41))
+        if r.random() < 0.5:
+            h, w = h & ~1, w & ~1
+        pool = bool(k == 3 and stride == 1 and h % 2 == 0 and w % 2 == 0 and r.random() < 0.4)
+        out.append((i, int(r.integers(1, 4)), cin, cout, max(h, 4), max(w, 4), k, stride, pool))
+    return out
+
+
+@pytest.mark.parametrize("idx,n,cin,cout,h,w,k,stride,pool", _random_fp32_shapes(36, 4711))
+def test_random_layer_shapes_match_oracle_in_fp32_mode(idx, n, cin, cout, h, w, k, stride, pool):
+    """Seeded random layers under the FP32 mode's static rule -- F(4x4,3x3) from 16 channels up (with and without the fused 2x2 max
+    pool), F(2x2,3x3) below, the few-channel kernel, the 1x1 GEMM, direct for other filters and strides; odd channel counts take
+    the scalar transform paths."""
+    x, wt, b = cases.conv_case("rnd32_%d" % idx, n, cin, cout, h, w, k, True)
+    ref = oracle.conv2d(x, wt, b, (stride, stride), 1)
+    if pool:
+        ref = oracle.pool(ref, (2, 2, 1), (2, 2, 1), 0)
+
+    def build(g, f):
+        o = conv_build(wt, b, stride, 1)(g, f)
+        return dr.Pooling(o, "max", [1, 2, 2, 1], [1, 2, 2, 1]) if pool else o
+    (got,) = run_graph(build, [x])
+    assert rel_err(got.reshape(ref.shape), ref) <= TOL_FP32
+
+
 @pytest.mark.parametrize("n,cin,cout,h,w,act", [(2, 32, 32, 12, 16, 1), (3, 64, 128, 14, 14, 1), (1, 16, 48, 30, 26, 0), (2, 128, 64, 28, 28, 1)])
 def test_winograd4_with_fused_maxpool_matches_oracle(n, cin, cout, h, w, act):
     """FP32 mode, conv3x3 followed by 2x2/2 max pooling: the F(4x4,3x3) output transform stores the pooled tensor (each 4x4 tile
