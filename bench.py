@@ -474,11 +474,27 @@ def run_ours(args):
         if "fp32x3" in extra:
             x3 = extra["fp32x3"]
             xroof, xagg, _ = vgg_roofline("tf32", batch, x3["profile"], peaks, None) if "profile" in x3 else ({}, None, None)
+            # executed tensor-core work: three MMAs per product; a Winograd F(4x4,3x3) layer has 36 products per whole tile of 16 outputs
+            xexec, xfam = None, None
+            xconvs = [(t, algo) for kind, t, _, algo in x3["profile"] if kind == "conv" and t > 0] if "profile" in x3 else []
+            if xagg and len(xconvs) == len(VGG_CONVS):
+                ex, ms_t, xfam = 0.0, 0.0, []
+                for (ci, co, hw), (t, algo) in zip(VGG_CONVS, xconvs):
+                    if algo == 5:
+                        ex += 3 * 2.0 * 36 * ci * co * ((hw + 3) // 4) ** 2 * batch
+                        ms_t += t
+                    elif algo == 4:
+                        ex += 3 * 2.0 * 9 * ci * co * hw * hw * batch
+                        ms_t += t
+                    xfam.append({1: "FP32 direct (FFMA)", 4: "direct, 3 passes", 5: "winograd F(4x4,3x3), 3 passes", 6: "FP32 winograd F(4x4,3x3) (FFMA)"}.get(algo, str(algo)))
+                xexec = ex / (ms_t * 1e-3) / 1e12 if ms_t > 0 else None
             line["fp32_accurate_tensor"] = {"images_per_s": x3["images_per_s"], "ms_per_step": x3["ms_per_step"], "e2e_images_per_s": x3["e2e_images_per_s"],
                                             "steps": x3["steps"], "dtype": "3xtf32", "conv_tflops_direct_equivalent": xagg,
-                                            "conv_tflops_executed_tf32": (3.0 * xagg) if xagg else None, "ms_per_layer": xroof.get("ms_per_layer"),
-                                            "what": "math mode fp32x3: 3x3 layers with >= 8 input channels evaluate x*w as hi*hi + hi*lo + lo*hi in three TF32 "
-                                                    "tensor-core passes (FP32-class error bound 1e-4 x max|ref| per layer); first layer, FC, pooling, softmax on the FP32 kernels"}
+                                            "conv_tflops_executed_tf32_tensor_layers": xexec, "conv_kernel_family_per_layer": xfam,
+                                            "ms_per_layer": xroof.get("ms_per_layer"),
+                                            "what": "math mode fp32x3: 3x3 layers with >= 8 input channels evaluate every product as hi*hi + hi*lo + lo*hi in three TF32 "
+                                                    "tensor-core passes (FP32-class error bound 1e-4 x max|ref| per layer) -- the deep layers as Winograd F(4x4,3x3) "
+                                                    "with its 36 transform-domain products on the tensor cores, the others directly; first layer, FC, pooling, softmax on the FP32 kernels"}
         if "squeezenet_b64" in extra:
             sq = extra["squeezenet_b64"]
             line["squeezenet"] = {"batch64": {"images_per_s": sq["images_per_s"], "ms_per_step": sq["ms_per_step"], "e2e_images_per_s": sq["e2e_images_per_s"],

@@ -186,7 +186,10 @@ static gboolean algoLegal(dR_Graph *net, dR_Node *layer, gint algo)
     case DR_CONV_ONEBYONE: return is1x1s1(c);
     case DR_CONV_TENSOR: return tensorLegal(net, layer);
     case DR_CONV_TENSOR_WINOGRAD:
-        return is3x3s1(c) && !x3Mode(net) && tensorLegal(net, layer) && dRk_tensor_winograd_supported(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
+        if (x3Mode(net))        /* FP32-accurate mode: F(4x4,3x3) with three-pass products */
+            return is3x3s1(c) && dR_firstInput(layer)->act_cstride == dR_firstInput(layer)->oshape.s2 &&
+                   dRk_tensor_winograd4_x3_supported(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
+        return is3x3s1(c) && tensorLegal(net, layer) && dRk_tensor_winograd_supported(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
     }
     return FALSE;
 }
@@ -200,6 +203,12 @@ static gboolean algoLegal(dR_Graph *net, dR_Node *layer, gint algo)
 static gint staticRule(dR_Graph *net, dR_Node *layer)
 {
     dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
+    /* FP32-accurate tensor mode: Winograd F(4x4,3x3) with three-pass products (0.75 MMA per direct multiplication) beats the direct
+       three-pass kernel (3 MMAs) where a tile's product outweighs moving its operands through memory, Cin*Cout against 2*Cin + Cout
+       floats per tile and transform position: measured on the VGG-16 shapes at batch 64, 128->256 and deeper win (1.2-2.2x),
+       128->128 and shallower lose */
+    if (x3Mode(net) && (glong)c->shape.s2 * c->shape.s3 >= 56 * (2 * (glong)c->shape.s2 + c->shape.s3) &&
+        algoLegal(net, layer, DR_CONV_TENSOR_WINOGRAD)) return DR_CONV_TENSOR_WINOGRAD;
     if (net->config->mathMode != DR_MATH_FP32 && tensorLegal(net, layer)) return DR_CONV_TENSOR;
     /* a handful of input channels (RGB first layer): bound by writing the output, a direct kernel wins */
     if (is3x3s1(c) && c->shape.s2 <= 4) return DR_CONV_DIRECT;
@@ -227,7 +236,8 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
     /* conv -> 2x2/2 max pool with no other reader: the tensor kernel's epilogue (or the F(4x4,3x3) output transform) stores the
        pooled tensor directly into the pooling node's buffer and the pooling node launches nothing */
     dev(c)->fusedPool = 0;
-    if ((c->chosenAlgo == DR_CONV_TENSOR || c->chosenAlgo == DR_CONV_WINOGRAD4) && net->config->fuseGraph && is3x3s1(c) && !layer->output && !layer->elided && layer->next_layers->length == 1 &&
+    if ((c->chosenAlgo == DR_CONV_TENSOR || c->chosenAlgo == DR_CONV_WINOGRAD4 || (c->chosenAlgo == DR_CONV_TENSOR_WINOGRAD && x3Mode(net))) &&
+        net->config->fuseGraph && is3x3s1(c) && !layer->output && !layer->elided && layer->next_layers->length == 1 &&
         layer->oshape.s0 % 2 == 0 && layer->oshape.s1 % 2 == 0) {
         dR_Node *nx = (dR_Node *)layer->next_layers->first->element;
         if (nx->type == tPooling && nx->previous_layers->length == 1) {
@@ -235,7 +245,7 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
             const gint ptype = pl->poolingType == tMax ? 1 : pl->poolingType == tAverage ? 2 : 0;
             if (ptype && pl->shape.s1 == 2 && pl->shape.s2 == 2 && pl->shape.s3 == 1 &&
                 pl->stride.s1 == 2 && pl->stride.s2 == 2 && pl->stride.s3 == 1 &&
-                (c->chosenAlgo == DR_CONV_WINOGRAD4 || x3Mode(net)
+                (c->chosenAlgo == DR_CONV_WINOGRAD4 || x3Mode(net)     /* the F(4x4,3x3) output transform and the three-pass kernel: max only */
                      ? ptype == 1
                      : dRk_tensor_conv_can_fuse_pool(c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3, c->shape.s0, c->shape.s1, ptype))) {
                 dev(c)->fusedPool = ptype;
@@ -295,8 +305,9 @@ gboolean dR_conv2d_createKernel(dR_Graph *net, dR_Node *layer)
         if (s > layer->scratchFloats) layer->scratchFloats = s;
     }
     if (c->chosenAlgo == DR_CONV_TENSOR_WINOGRAD ||
-        (net->config->autotune && net->config->mathMode == DR_MATH_TF32 && algoLegal(net, layer, DR_CONV_TENSOR_WINOGRAD))) {
-        const size_t s = dRk_tensor_winograd_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
+        (net->config->autotune && net->config->mathMode != DR_MATH_FP32 && algoLegal(net, layer, DR_CONV_TENSOR_WINOGRAD))) {
+        const size_t s = x3Mode(net) ? dRk_tensor_winograd4_x3_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3)
+                                     : dRk_tensor_winograd_scratch_floats(net->config->batchSize, c->ishape.s0, c->ishape.s1, c->shape.s2, c->shape.s3);
         if (s > layer->scratchFloats) layer->scratchFloats = s;
     }
     return TRUE;
@@ -340,7 +351,7 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
     if (algo == DR_CONV_WINOGRAD) n = (size_t)16 * I * O;
     if (algo == DR_CONV_WINOGRAD4) n = (size_t)36 * I * O;
     if (algo == DR_CONV_TENSOR) n = x3Mode(net) ? dRk_tensor_conv_x3_packed_floats(I, O) : dRk_tensor_conv_packed_floats(c->ishape.s0, c->ishape.s1, I, O, kw, kh);
-    if (algo == DR_CONV_TENSOR_WINOGRAD) n = dRk_tensor_winograd_packed_floats(I, O);
+    if (algo == DR_CONV_TENSOR_WINOGRAD) n = x3Mode(net) ? dRk_tensor_winograd4_x3_packed_floats(I, O) : dRk_tensor_winograd_packed_floats(I, O);
     if (n == 0) return FALSE;
     gfloat *p = (gfloat *)g_malloc0(n * sizeof(gfloat));
     if (algo == DR_CONV_DIRECT) {
@@ -354,7 +365,7 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
         if ((x3Mode(net) ? dRk_tensor_conv_x3_pack_weights(c->weights, p, I, O)
                          : dRk_tensor_conv_pack_weights(c->weights, p, c->ishape.s0, c->ishape.s1, I, O, kw, kh)) != 0) { g_free(p); return FALSE; }
     } else if (algo == DR_CONV_TENSOR_WINOGRAD) {
-        if (dRk_tensor_winograd_pack_weights(c->weights, p, I, O) != 0) { g_free(p); return FALSE; }
+        if ((x3Mode(net) ? dRk_tensor_winograd4_x3_pack_weights(c->weights, p, I, O) : dRk_tensor_winograd_pack_weights(c->weights, p, I, O)) != 0) { g_free(p); return FALSE; }
     } else if (algo == DR_CONV_WINOGRAD4) {
         if (dRk_winograd4_pack_weights(c->weights, p, I, O) != 0) { g_free(p); return FALSE; }
     } else {
@@ -453,8 +464,12 @@ gboolean dR_conv2d_runVariant(dR_Graph *net, dR_Node *layer, gint algo, gint ten
         if (d->wplan && (d->wplanSrc != src || d->wplanDst != dst || d->wplanScratch != (float *)net->scratch)) { dRk_tensor_winograd_free(d->wplan); d->wplan = NULL; }
         if (!d->wplan) {
             d->wplanSrc = src; d->wplanDst = dst; d->wplanScratch = (float *)net->scratch;
-            d->wplan = dRk_tensor_winograd_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR_WINOGRAD], bias, dst, (float *)net->scratch, n, W, H,
-                                                c->shape.s2, c->shape.s3, act, in->act_cstride, layer->act_cstride, layer->act_coffset, (int *)net->statusWord);
+            d->wplan = x3Mode(net)
+                ? dRk_tensor_winograd4_x3_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR_WINOGRAD], bias, dst, (float *)net->scratch, n, W, H,
+                                               c->shape.s2, c->shape.s3, act, in->act_cstride, layer->act_cstride, layer->act_coffset, d->fusedPool,
+                                               (int *)net->statusWord)
+                : dRk_tensor_winograd_plan(src, (const float *)d->wbuf[DR_CONV_TENSOR_WINOGRAD], bias, dst, (float *)net->scratch, n, W, H,
+                                           c->shape.s2, c->shape.s3, act, in->act_cstride, layer->act_cstride, layer->act_coffset, (int *)net->statusWord);
             if (!d->wplan) { g_print("Conv2d Layer %d: tensor-core Winograd plan could not be built\n", layer->layerID); return FALSE; }
         }
         net->clConfig->clError = dRk_tensor_winograd_run(s, d->wplan);

@@ -25,3 +25,8 @@ int drk_conv3x3_smallcin_launch(cudaStream_t st, const float *in, const float *w
 int drk_wino_input_launch(cudaStream_t st, const float *in, float *V, int nimg, int W, int H, int C, int ldi, size_t T, size_t Ts);
 int drk_wino_output_launch(cudaStream_t st, const float *Mt, const float *bias, float *out, int W, int H, int O, int ldo, int coff,
                            size_t T, size_t Ts, int act);
+
+/* Winograd F(4x4,3x3) transforms (k_winograd.cu): V[k][t][c], k = 0..35; split = rows of 2C floats, TF32 high parts then remainders */
+int drk_wino4_input_launch(cudaStream_t st, const float *in, float *V, int W, int H, int C, int ldi, size_t T, size_t Ts, int split);
+int drk_wino4_output_launch(cudaStream_t st, const float *Mt, const float *bias, float *out, int W, int H, int O, int ldo, int coff,
+                            size_t T, size_t Ts, int act, int pool);

@@ -31,6 +31,8 @@ struct UmmaParams {
     long long split_stride;         /* floats between the partial outputs of consecutive K parts */
     int *status;
     int P, ncols;                   /* transposed kernel: pixel pitch of a block row (16 or 32) and MMA columns per tile = P * TH */
+    int x3cat;                      /* flat mode, FP32-accurate three-pass product over operands stored as (high | low) halves along K: kslabs = 3 * x3cat
+                                       K slabs; slab ks is pass ks / x3cat (0: hi x hi, 1: hi x lo, 2: lo x hi) of slab ks % x3cat; 0 = plain K loop */
     int bpacked;                    /* flat mode: the B operand is stored block by block ([n tile][K slab][BN rows][32]); a block is rows (nt * kslabs + ks) * BN.. of a 32-wide map */
     int bgroup_tiles, bgroup_rows;  /* flat mode, batched GEMMs stacked on M: every bgroup_tiles M tiles the B operand moves on by bgroup_rows rows (0: one B) */
 };

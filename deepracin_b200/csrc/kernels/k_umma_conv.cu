@@ -93,6 +93,10 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                before it (programmatic dependent launch), so that only the activation loads remain on the critical path.
                Only this thread reads memory the previous kernel writes, and every store of this kernel follows, through the
                barrier chain, from a load issued after the wait. */
+            /* K slab -> x coordinate of the A and B maps (three-pass mode: the high halves of both, then A high x B low, then
+               A low x B high; the low halves sit x3cat slabs to the right of the high ones) */
+            auto a_slab = [&](int ks) { return p.x3cat ? (ks >= 2 * p.x3cat ? ks - p.x3cat : (ks >= p.x3cat ? ks - p.x3cat : ks)) : ks; };
+            auto b_slab = [&](int ks) { return p.x3cat ? (ks >= 2 * p.x3cat ? ks - 2 * p.x3cat : ks) : ks; };
             int pre = 0;
             if ((int)blockIdx.x < total_tiles) {
                 const int t = blockIdx.x;
@@ -104,7 +108,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                     for (int ks = ks0; ks < ks1 && pre < C::STAGES; ks++, pre++) {
                         mbar_expect_tx(full_bar(pre), (uint32_t)p.stage_tx);
                         if (p.bpacked) tma_load_2d(base + pre * C::STAGE_BYTES + A_STAGE_BYTES, &mapB, 0, (nt * p.kslabs + ks) * BN, full_bar(pre));
-                        else tma_load_2d(base + pre * C::STAGE_BYTES + A_STAGE_BYTES, &mapB, tap * p.CinPad + ks * BK, brow, full_bar(pre));
+                        else tma_load_2d(base + pre * C::STAGE_BYTES + A_STAGE_BYTES, &mapB, tap * p.CinPad + b_slab(ks) * BK, brow, full_bar(pre));
                     }
             }
             drk_dep_wait();
@@ -121,7 +125,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                         const uint32_t sa = base + stage * C::STAGE_BYTES, sb = sa + A_STAGE_BYTES;
                         if (!armed) mbar_expect_tx(full_bar(stage), (uint32_t)p.stage_tx);
                         if (p.S == 0) {
-                            tma_load_2d(sa, &mapA, ks * BK, mt * BM, full_bar(stage));
+                            tma_load_2d(sa, &mapA, a_slab(ks) * BK, mt * BM, full_bar(stage));
                         } else {
                             const int per = p.tiles_x * p.tiles_y;
                             const int sub_bytes = p.TW * p.TH * BK * 4;
@@ -136,7 +140,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                         }
                         if (!armed) {
                             if (p.bpacked) tma_load_2d(sb, &mapB, 0, (nt * p.kslabs + ks) * BN, full_bar(stage));
-                            else tma_load_2d(sb, &mapB, tap * p.CinPad + ks * BK, brow, full_bar(stage));
+                            else tma_load_2d(sb, &mapB, tap * p.CinPad + b_slab(ks) * BK, brow, full_bar(stage));
                         }
                         issued++;
                         if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -1569,6 +1573,8 @@ struct dRk_TensorWinogradPlan {
     const float *in, *bias;
     float *out, *V, *M;
     int n, W, H, Cin, Cout, act, ldi, ldo, coff;
+    int f4x3;                                   /* 0: F(2x2,3x3) with TF32 products; 1: F(4x4,3x3) with three-pass (FP32-accurate) products */
+    int pool;                                   /* F(4x4): the output transform evaluates a following 2x2/2 max pooling */
 };
 
 static size_t twino_tiles(int W, int H) { return (size_t)((W + 1) / 2) * ((H + 1) / 2); }
@@ -1614,8 +1620,10 @@ extern "C" int dRk_tensor_winograd_pack_weights(const float *w, float *dst, int 
     return 0;
 }
 
-/* the flat GEMM of one chunk: A = V [16*Tp][Cin], B = U [16*Cout][Cin], D = M [16*Tp][Cout] */
-static int twino_gemm_plan(dRk_TensorConvPlan *pl, const float *V, const float *U, float *M, size_t Tp, int Cin, int Cout, int *status, int sms)
+/* the flat GEMM of one chunk: A = V [P*Tp][Kw], B = U [P*Cout][Kw], D = M [P*Tp][Cout]; P transform positions stacked on M.
+ * x3: rows are Kw = 2*Cin wide, (high | low) halves, and the K loop makes the three passes hi x hi, hi x lo, lo x hi */
+static int twino_gemm_plan(dRk_TensorConvPlan *pl, const float *V, const float *U, float *M, size_t Tp, int P, int x3, int Cin, int Cout,
+                           int *status, int sms)
 {
     PFN_encodeTiled enc = get_encode();
     if (!enc) return -1;
@@ -1623,10 +1631,12 @@ static int twino_gemm_plan(dRk_TensorConvPlan *pl, const float *V, const float *
     UmmaParams &p = pl->p;
     p.n = 1; p.W = 1; p.H = 1; p.Cin = Cin; p.Cout = Cout;
     p.CinPad = (Cin + BK - 1) / BK * BK;
-    p.taps = 1; p.kw = 1; p.pad = 0; p.kslabs = p.CinPad / BK;
+    p.taps = 1; p.kw = 1; p.pad = 0;
+    p.x3cat = x3 ? Cin / BK : 0;
+    p.kslabs = x3 ? 3 * p.x3cat : p.CinPad / BK;
     p.S = 0; p.TW = BM; p.TH = 1; p.tiles_x = p.tiles_y = 1;
-    p.total_sub = (long long)(16 * Tp);
-    p.m_tiles = (int)(16 * Tp / BM);
+    p.total_sub = (long long)((size_t)P * Tp);
+    p.m_tiles = (int)((size_t)P * Tp / BM);
     p.bias = NULL; p.out = M; p.ldo = Cout; p.coff = 0; p.act = 0; p.pool = 0; p.status = status;
     p.ksplit = 1; p.kper = p.kslabs; p.split_stride = 0;
     p.bgroup_tiles = (int)(Tp / BM); p.bgroup_rows = Cout;
@@ -1634,15 +1644,17 @@ static int twino_gemm_plan(dRk_TensorConvPlan *pl, const float *V, const float *
     pl->BN = pick_bn(Cout, p.m_tiles, sms);
     p.n_tiles = (Cout + pl->BN - 1) / pl->BN;
     p.stage_tx = A_STAGE_BYTES + pl->BN * BK * 4;
+    const cuuint64_t Kw = (cuuint64_t)(x3 ? 2 * Cin : Cin);
+    const CUtensorMapDataType dt = x3 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32;   /* the halves are used bit for bit */
     const cuuint32_t ones[2] = {1, 1};
-    const cuuint64_t adims[2] = {(cuuint64_t)Cin, (cuuint64_t)(16 * Tp)}, str[1] = {(cuuint64_t)Cin * 4};
+    const cuuint64_t adims[2] = {Kw, (cuuint64_t)P * Tp}, str[1] = {Kw * 4};
     const cuuint32_t abox[2] = {BK, BM};
-    CUresult r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)V, adims, str, abox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    CUresult r = enc(&pl->mapA, dt, 2, (void *)V, adims, str, abox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    const cuuint64_t bdims[2] = {(cuuint64_t)Cin, (cuuint64_t)16 * Cout};
+    const cuuint64_t bdims[2] = {Kw, (cuuint64_t)P * Cout};
     const cuuint32_t bbox[2] = {BK, (cuuint32_t)pl->BN};
     if (r == CUDA_SUCCESS)
-        r = enc(&pl->mapB, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)U, bdims, str, bbox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        r = enc(&pl->mapB, dt, 2, (void *)U, bdims, str, bbox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { fprintf(stderr, "tensor winograd plan: tensor map rejected (%d)\n", (int)r); return -1; }
     const long long tiles = (long long)p.m_tiles * p.n_tiles;
@@ -1670,7 +1682,95 @@ extern "C" dRk_TensorWinogradPlan *dRk_tensor_winograd_plan(const float *in, con
         if (wp->imgs[i] == 0) continue;
         wp->T[i] = twino_tiles(W, H) * wp->imgs[i];
         wp->Tp[i] = twino_pad(wp->T[i]);
-        if (twino_gemm_plan(&wp->gemm[i], wp->V, U, wp->M, wp->Tp[i], Cin, Cout, status, sms) != 0) { free(wp); return NULL; }
+        if (twino_gemm_plan(&wp->gemm[i], wp->V, U, wp->M, wp->Tp[i], 16, 0, Cin, Cout, status, sms) != 0) { free(wp); return NULL; }
+    }
+    return wp;
+}
+
+/*
+ * Winograd F(4x4,3x3) with FP32-accurate products on the tensor cores: the transforms of k_winograd.cu in FP32 around ONE launch of
+ * the flat GEMM over the 36 transform positions, every product evaluated as hi x hi + hi x lo + lo x hi of TF32 halves (the input
+ * transform writes V as (high | low) rows, the filters are packed the same way).  A quarter of the direct sum's multiplications,
+ * three MMAs each: 0.75 MMA per direct multiplication where the direct three-pass kernel spends 3.  The algorithm of
+ * conv2dwinograd2 (Kernels/dR_winograd2.cl:23-254) at the larger tile size, in the FP32 class's error bound.
+ */
+static size_t twino4_tiles(int W, int H) { return (size_t)((W + 3) / 4) * ((H + 3) / 4); }
+static int twino4_chunk(int n, int W, int H, int Cin, int Cout)
+{
+    const size_t per = 36 * twino4_tiles(W, H) * (size_t)(2 * Cin + Cout);
+    size_t c = (TWINO_SCRATCH_CAP - 36 * (size_t)BM * (2 * Cin + Cout)) / per;
+    if (c < 1) c = 1;
+    if (c > (size_t)n) c = (size_t)n;
+    return (int)c;
+}
+
+extern "C" int dRk_tensor_winograd4_x3_supported(int W, int H, int Cin, int Cout)
+{
+    return dRk_tensor_conv_supported(W, H, Cin, Cout, 3, 3) && Cin >= BK && Cin % BK == 0 && Cin <= 1024 &&
+           twino_pad(twino4_tiles(W, H)) * 36 <= 0x7fffffffull / 2;
+}
+
+extern "C" size_t dRk_tensor_winograd4_x3_scratch_floats(int n, int W, int H, int Cin, int Cout)
+{
+    if (n <= 0 || !dRk_tensor_winograd4_x3_supported(W, H, Cin, Cout)) return 0;
+    return 36 * twino_pad(twino4_tiles(W, H) * twino4_chunk(n, W, H, Cin, Cout)) * (size_t)(2 * Cin + Cout);
+}
+
+extern "C" size_t dRk_tensor_winograd4_x3_packed_floats(int Cin, int Cout) { return (size_t)36 * Cout * 2 * Cin; }
+
+/* U = G g G^T in double (G of F(4x4,3x3)), stored [36][Cout][2*Cin]: the upper 19 bits of the FP32 value, then what is left of the
+ * double value.  w is the reference's [Cin][Cout][3][3] filter array. */
+extern "C" int dRk_tensor_winograd4_x3_pack_weights(const float *w, float *dst, int Cin, int Cout)
+{
+    if (!w || !dst || Cin <= 0 || Cout <= 0) return -1;
+    static const double G[6][3] = {{1.0 / 4, 0, 0}, {-1.0 / 6, -1.0 / 6, -1.0 / 6}, {-1.0 / 6, 1.0 / 6, -1.0 / 6},
+                                   {1.0 / 24, 1.0 / 12, 1.0 / 6}, {1.0 / 24, -1.0 / 12, 1.0 / 6}, {0, 0, 1}};
+    for (int c = 0; c < Cin; c++)
+        for (int o = 0; o < Cout; o++) {
+            const float *g = w + ((size_t)c * Cout + o) * 9;
+            double t[6][3];
+            for (int i = 0; i < 6; i++)
+                for (int j = 0; j < 3; j++) t[i][j] = G[i][0] * g[0 * 3 + j] + G[i][1] * g[1 * 3 + j] + G[i][2] * g[2 * 3 + j];
+            for (int i = 0; i < 6; i++)
+                for (int j = 0; j < 6; j++) {
+                    const double u = t[i][0] * G[j][0] + t[i][1] * G[j][1] + t[i][2] * G[j][2];
+                    const float uf = (float)u;
+                    uint32_t bits;
+                    memcpy(&bits, &uf, 4);
+                    bits &= 0xffffe000u;
+                    float hi;
+                    memcpy(&hi, &bits, 4);
+                    float *row = dst + ((size_t)(i * 6 + j) * Cout + o) * (2 * (size_t)Cin);
+                    row[c] = hi;
+                    row[Cin + c] = (float)(u - (double)hi);
+                }
+        }
+    return 0;
+}
+
+extern "C" dRk_TensorWinogradPlan *dRk_tensor_winograd4_x3_plan(const float *in, const float *U2, const float *bias, float *out, float *scratch,
+                                                                int n, int W, int H, int Cin, int Cout, int act, int ldi, int ldo, int coff,
+                                                                int pool, int *status)
+{
+    if (n <= 0 || !scratch || !dRk_tensor_winograd4_x3_supported(W, H, Cin, Cout)) return NULL;
+    if (ldi < Cin || ldo < coff + Cout || ((uintptr_t)scratch % 16) || ((uintptr_t)U2 % 16)) return NULL;
+    if (pool && (pool != 1 || (W & 1) || (H & 1))) return NULL;
+    int dev = 0, sms = 148;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    dRk_TensorWinogradPlan *wp = (dRk_TensorWinogradPlan *)calloc(1, sizeof(dRk_TensorWinogradPlan));
+    if (!wp) return NULL;
+    wp->in = in; wp->bias = bias; wp->out = out; wp->n = n; wp->W = W; wp->H = H; wp->Cin = Cin; wp->Cout = Cout;
+    wp->act = act; wp->ldi = ldi; wp->ldo = ldo; wp->coff = coff; wp->f4x3 = 1; wp->pool = pool;
+    const int chunk = twino4_chunk(n, W, H, Cin, Cout);
+    wp->imgs[0] = chunk; wp->nfull = n / chunk; wp->imgs[1] = n - wp->nfull * chunk;
+    wp->V = scratch;
+    wp->M = scratch + 36 * twino_pad(twino4_tiles(W, H) * chunk) * (size_t)(2 * Cin);
+    for (int i = 0; i < 2; i++) {
+        if (wp->imgs[i] == 0) continue;
+        wp->T[i] = twino4_tiles(W, H) * wp->imgs[i];
+        wp->Tp[i] = twino_pad(wp->T[i]);
+        if (twino_gemm_plan(&wp->gemm[i], wp->V, U2, wp->M, wp->Tp[i], 36, 1, Cin, Cout, status, sms) != 0) { free(wp); return NULL; }
     }
     return wp;
 }
@@ -1683,8 +1783,9 @@ extern "C" int dRk_tensor_winograd_run(dRk_stream stream, dRk_TensorWinogradPlan
     for (int c = 0; c < wp->nfull + (wp->imgs[1] ? 1 : 0); c++) {
         const int i = c < wp->nfull ? 0 : 1;
         const float *src = wp->in + (size_t)b0 * wp->H * wp->W * wp->ldi;
-        float *dst = wp->out + (size_t)b0 * wp->H * wp->W * wp->ldo;
-        int rc = drk_wino_input_launch(st, src, wp->V, wp->imgs[i], wp->W, wp->H, wp->Cin, wp->ldi, wp->T[i], wp->Tp[i]);
+        float *dst = wp->out + (size_t)b0 * (wp->pool ? (wp->H / 2) * (wp->W / 2) : wp->H * wp->W) * wp->ldo;
+        int rc = wp->f4x3 ? drk_wino4_input_launch(st, src, wp->V, wp->W, wp->H, wp->Cin, wp->ldi, wp->T[i], wp->Tp[i], 1)
+                          : drk_wino_input_launch(st, src, wp->V, wp->imgs[i], wp->W, wp->H, wp->Cin, wp->ldi, wp->T[i], wp->Tp[i]);
         if (rc) return rc;
         dRk_TensorConvPlan *g = &wp->gemm[i];
         switch (g->BN) {
@@ -1693,7 +1794,8 @@ extern "C" int dRk_tensor_winograd_run(dRk_stream stream, dRk_TensorWinogradPlan
         default: rc = launch_umma<64>(st, g); break;
         }
         if (rc) return rc;
-        rc = drk_wino_output_launch(st, wp->M, wp->bias, dst, wp->W, wp->H, wp->Cout, wp->ldo, wp->coff, wp->T[i], wp->Tp[i], wp->act);
+        rc = wp->f4x3 ? drk_wino4_output_launch(st, wp->M, wp->bias, dst, wp->W, wp->H, wp->Cout, wp->ldo, wp->coff, wp->T[i], wp->Tp[i], wp->act, wp->pool)
+                      : drk_wino_output_launch(st, wp->M, wp->bias, dst, wp->W, wp->H, wp->Cout, wp->ldo, wp->coff, wp->T[i], wp->Tp[i], wp->act);
         if (rc) return rc;
         b0 += wp->imgs[i];
     }

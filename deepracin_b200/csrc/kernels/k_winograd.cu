@@ -28,6 +28,7 @@ template <> struct WVec<1> {
     static __device__ __forceinline__ T sub(T a, T b) { return a - b; }
     static __device__ __forceinline__ T fma(T a, float s, T b) { return fmaf(a, s, b); }      /* a * s + b */
     static __device__ __forceinline__ T max(T a, T b) { return fmaxf(a, b); }
+    static __device__ __forceinline__ T hi(T a) { return __uint_as_float(__float_as_uint(a) & 0xffffe000u); }     /* the 19 bits a TF32 operand keeps */
     static __device__ __forceinline__ T bias_act(T v, const float *bias, int o, int act) { return drk_act(v + (bias ? bias[o] : 0.0f), act); }
 };
 template <> struct WVec<2> {
@@ -37,6 +38,7 @@ template <> struct WVec<2> {
     static __device__ __forceinline__ T sub(T a, T b) { return make_float2(a.x - b.x, a.y - b.y); }
     static __device__ __forceinline__ T fma(T a, float s, T b) { return make_float2(fmaf(a.x, s, b.x), fmaf(a.y, s, b.y)); }
     static __device__ __forceinline__ T max(T a, T b) { return make_float2(fmaxf(a.x, b.x), fmaxf(a.y, b.y)); }
+    static __device__ __forceinline__ T hi(T a) { return make_float2(WVec<1>::hi(a.x), WVec<1>::hi(a.y)); }
     static __device__ __forceinline__ T bias_act(T v, const float *bias, int o, int act)
     {
         float2 b = bias ? *reinterpret_cast<const float2 *>(bias + o) : make_float2(0.f, 0.f);
@@ -50,6 +52,7 @@ template <> struct WVec<4> {
     static __device__ __forceinline__ T sub(T a, T b) { return make_float4(a.x - b.x, a.y - b.y, a.z - b.z, a.w - b.w); }
     static __device__ __forceinline__ T fma(T a, float s, T b) { return make_float4(fmaf(a.x, s, b.x), fmaf(a.y, s, b.y), fmaf(a.z, s, b.z), fmaf(a.w, s, b.w)); }
     static __device__ __forceinline__ T max(T a, T b) { return make_float4(fmaxf(a.x, b.x), fmaxf(a.y, b.y), fmaxf(a.z, b.z), fmaxf(a.w, b.w)); }
+    static __device__ __forceinline__ T hi(T a) { return make_float4(WVec<1>::hi(a.x), WVec<1>::hi(a.y), WVec<1>::hi(a.z), WVec<1>::hi(a.w)); }
     static __device__ __forceinline__ T bias_act(T v, const float *bias, int o, int act)
     {
         float4 b = bias ? *reinterpret_cast<const float4 *>(bias + o) : make_float4(0.f, 0.f, 0.f, 0.f);
@@ -244,8 +247,9 @@ static __device__ __forceinline__ void wino4_bt(vt &d0, vt &d1, vt &d2, vt &d3, 
     d5 = t5;
 }
 
-/* V[k][t][c], k = 0..35 */
-template <int VEC>
+/* V[k][t][c], k = 0..35.  SPLIT: rows are 2C wide, the value's TF32 high part (upper 19 bits) at [c] and the remainder at [C + c]:
+   the operand layout of the FP32-accurate three-pass tensor-core product */
+template <int VEC, bool SPLIT>
 __global__ void __launch_bounds__(256) k_wino4_input(const float *__restrict__ in, float *__restrict__ V, int W, int H, int C, int ldi,
                                                      int tx, int ty, size_t T, size_t Ts)
 {
@@ -277,7 +281,16 @@ __global__ void __launch_bounds__(256) k_wino4_input(const float *__restrict__ i
         for (int r = 0; r < 6; r++) {                                                                           /* (.) B */
             wino4_bt<X, vt>(d[r][0], d[r][1], d[r][2], d[r][3], d[r][4], d[r][5]);
 #pragma unroll
-            for (int s = 0; s < 6; s++) *reinterpret_cast<vt *>(V + ((size_t)(r * 6 + s) * Ts + t) * C + c) = d[r][s];
+            for (int s = 0; s < 6; s++) {
+                if (SPLIT) {
+                    float *row = V + ((size_t)(r * 6 + s) * Ts + t) * (2 * (size_t)C) + c;
+                    const vt h = X::hi(d[r][s]);
+                    *reinterpret_cast<vt *>(row) = h;
+                    *reinterpret_cast<vt *>(row + C) = X::sub(d[r][s], h);
+                } else {
+                    *reinterpret_cast<vt *>(V + ((size_t)(r * 6 + s) * Ts + t) * C + c) = d[r][s];
+                }
+            }
         }
     }
 }
@@ -381,18 +394,42 @@ extern "C" int dRk_winograd4_pack_weights(const float *w, float *U, int Cin, int
 }
 
 template <int VEC>
-static void wino4_launch_in(cudaStream_t st, const float *in, float *V, int W, int H, int C, int ldi, int tx, int ty, size_t T)
+static void wino4_launch_in(cudaStream_t st, const float *in, float *V, int W, int H, int C, int ldi, int tx, int ty, size_t T, size_t Ts, int split)
 {
-    k_wino4_input<VEC><<<drk_blocks(T * (C / VEC), 256, 148u * 32u), 256, 0, st>>>(in, V, W, H, C, ldi, tx, ty, T, T);
+    const unsigned blocks = drk_blocks(T * (C / VEC), 256, 148u * 32u);
+    if (split) k_wino4_input<VEC, true><<<blocks, 256, 0, st>>>(in, V, W, H, C, ldi, tx, ty, T, Ts);
+    else k_wino4_input<VEC, false><<<blocks, 256, 0, st>>>(in, V, W, H, C, ldi, tx, ty, T, Ts);
 }
 
 template <int VEC>
 static void wino4_launch_out(cudaStream_t st, const float *Mt, const float *bias, float *out, int W, int H, int O, int ldo, int coff,
-                             int tx, int ty, size_t T, int act, int pool)
+                             int tx, int ty, size_t T, size_t Ts, int act, int pool)
 {
     const unsigned blocks = drk_blocks(T * (O / VEC), 256, 148u * 32u);
-    if (pool) k_wino4_output<VEC, true><<<blocks, 256, 0, st>>>(Mt, bias, out, W, H, O, ldo, coff, tx, ty, T, T, act);
-    else k_wino4_output<VEC, false><<<blocks, 256, 0, st>>>(Mt, bias, out, W, H, O, ldo, coff, tx, ty, T, T, act);
+    if (pool) k_wino4_output<VEC, true><<<blocks, 256, 0, st>>>(Mt, bias, out, W, H, O, ldo, coff, tx, ty, T, Ts, act);
+    else k_wino4_output<VEC, false><<<blocks, 256, 0, st>>>(Mt, bias, out, W, H, O, ldo, coff, tx, ty, T, Ts, act);
+}
+
+/* F(4x4,3x3) transform launches shared with the tensor-core path (k_umma_conv.cu): Ts = row stride between the 36 transform
+ * positions (Ts >= T), split = (high | low) operand rows for the three-pass product, pool = fused 2x2/2 max pooling */
+int drk_wino4_input_launch(cudaStream_t st, const float *in, float *V, int W, int H, int C, int ldi, size_t T, size_t Ts, int split)
+{
+    const int tx = (W + 3) / 4, ty = (H + 3) / 4;
+    if (C % 2 == 0 && ldi % 2 == 0 && ((uintptr_t)in % 8) == 0 && ((uintptr_t)V % 16) == 0) wino4_launch_in<2>(st, in, V, W, H, C, ldi, tx, ty, T, Ts, split);
+    else wino4_launch_in<1>(st, in, V, W, H, C, ldi, tx, ty, T, Ts, split);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
+}
+
+int drk_wino4_output_launch(cudaStream_t st, const float *Mt, const float *bias, float *out, int W, int H, int O, int ldo, int coff,
+                            size_t T, size_t Ts, int act, int pool)
+{
+    const int tx = (W + 3) / 4, ty = (H + 3) / 4;
+    if (O % 2 == 0 && ldo % 2 == 0 && coff % 2 == 0 && ((uintptr_t)out % 8) == 0 && ((uintptr_t)Mt % 16) == 0 && (!bias || ((uintptr_t)bias % 8) == 0))
+        wino4_launch_out<2>(st, Mt, bias, out, W, H, O, ldo, coff, tx, ty, T, Ts, act, pool);
+    else wino4_launch_out<1>(st, Mt, bias, out, W, H, O, ldo, coff, tx, ty, T, Ts, act, pool);
+    DRK_COUNT_LAUNCH();
+    return DRK_LAUNCH_RESULT();
 }
 
 extern "C" int dRk_conv2d_winograd4_f32(dRk_stream stream, const float *in, const float *U, const float *bias, float *out,
@@ -404,9 +441,6 @@ extern "C" int dRk_conv2d_winograd4_f32(dRk_stream stream, const float *in, cons
     cudaStream_t st = drk_stream(stream);
     const int tx = (W + 3) / 4, ty = (H + 3) / 4;
     const int chunk = wino4_chunk(n, W, H, Cin, Cout);
-    const bool vin = Cin % 2 == 0 && ldi % 2 == 0 && ((uintptr_t)in % 8) == 0 && ((uintptr_t)scratch % 16) == 0;
-    const bool vout = Cout % 2 == 0 && ldo % 2 == 0 && coff % 2 == 0 && ((uintptr_t)out % 8) == 0 && ((uintptr_t)scratch % 16) == 0 &&
-                      (!bias || ((uintptr_t)bias % 8) == 0);
     for (int b0 = 0; b0 < n; b0 += chunk) {
         const int nb = n - b0 < chunk ? n - b0 : chunk;
         const size_t T = (size_t)nb * tx * ty;
@@ -414,18 +448,12 @@ extern "C" int dRk_conv2d_winograd4_f32(dRk_stream stream, const float *in, cons
         float *V = scratch, *Mt = scratch + 36 * T * Cin;
         const float *src = in + (size_t)b0 * H * W * ldi;
         float *dst = out + (size_t)b0 * (pool ? (H / 2) * (W / 2) : H * W) * ldo;
-        if (vin) wino4_launch_in<2>(st, src, V, W, H, Cin, ldi, tx, ty, T);
-        else wino4_launch_in<1>(st, src, V, W, H, Cin, ldi, tx, ty, T);
-        DRK_COUNT_LAUNCH();
-        int rc = DRK_LAUNCH_RESULT();
+        int rc = drk_wino4_input_launch(st, src, V, W, H, Cin, ldi, T, T, 0);
         if (rc) return rc;
         rc = drk_gemm_f32_launch(st, V, U, NULL, Mt, (int)T, Cout, Cin, Cin, Cout, Cout, 0, 0, 36,
                                  T * Cin, (size_t)Cin * Cout, T * Cout, NULL);
         if (rc) return rc;
-        if (vout) wino4_launch_out<2>(st, Mt, bias, dst, W, H, Cout, ldo, coff, tx, ty, T, act, pool);
-        else wino4_launch_out<1>(st, Mt, bias, dst, W, H, Cout, ldo, coff, tx, ty, T, act, pool);
-        DRK_COUNT_LAUNCH();
-        rc = DRK_LAUNCH_RESULT();
+        rc = drk_wino4_output_launch(st, Mt, bias, dst, W, H, Cout, ldo, coff, T, T, act, pool);
         if (rc) return rc;
     }
     return 0;

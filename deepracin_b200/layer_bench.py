@@ -140,7 +140,7 @@ def sweep(iters, warmup):
 def vgg_layers(batch, iters, warmup):
     out = []
     for cin, cout, hw in ((64, 64, 224), (64, 128, 112), (128, 128, 112), (128, 256, 56), (256, 256, 56), (256, 512, 28), (512, 512, 28), (512, 512, 14)):
-        for math, algo in (("tf32", "tensor"), ("tf32", "tensor_winograd"), ("fp32", "winograd"), ("fp32", "winograd4"), ("fp32", "direct")):
+        for math, algo in (("tf32", "tensor"), ("tf32", "tensor_winograd"), ("fp32x3", "tensor"), ("fp32x3", "tensor_winograd"), ("fp32", "winograd"), ("fp32", "winograd4"), ("fp32", "direct")):
             out.append(conv_layer(cin, cout, hw, batch, 3, math, algo, iters, warmup))
     return out
 

@@ -193,6 +193,17 @@ size_t dRk_tensor_winograd_packed_floats(int Cin, int Cout);
 int dRk_tensor_winograd_pack_weights(const float *w, float *dst, int Cin, int Cout);
 dRk_TensorWinogradPlan *dRk_tensor_winograd_plan(const float *in, const float *U, const float *bias, float *out, float *scratch,
                                                  int n, int W, int H, int Cin, int Cout, int act, int ldi, int ldo, int coff, int *status);
+/* The same algorithm as Winograd F(4x4,3x3) with FP32-accurate products: 36 transform positions, every product as three TF32 MMAs
+ * (hi x hi, hi x lo, lo x hi) over operands stored as (high | low) halves; FP32-class error bound (1e-4 of max|ref|).  Cin a
+ * multiple of 32; U2 from dRk_tensor_winograd4_x3_pack_weights ([36][Cout][2*Cin]); pool = 1 evaluates a following 2x2/2 max pooling
+ * in the output transform (out is then the pooled tensor).  Run and free with dRk_tensor_winograd_run / _free. */
+int dRk_tensor_winograd4_x3_supported(int W, int H, int Cin, int Cout);
+size_t dRk_tensor_winograd4_x3_scratch_floats(int n, int W, int H, int Cin, int Cout);
+size_t dRk_tensor_winograd4_x3_packed_floats(int Cin, int Cout);
+int dRk_tensor_winograd4_x3_pack_weights(const float *w, float *dst, int Cin, int Cout);
+dRk_TensorWinogradPlan *dRk_tensor_winograd4_x3_plan(const float *in, const float *U2, const float *bias, float *out, float *scratch,
+                                                     int n, int W, int H, int Cin, int Cout, int act, int ldi, int ldo, int coff,
+                                                     int pool, int *status);
 int dRk_tensor_winograd_run(dRk_stream stream, dRk_TensorWinogradPlan *plan);
 void dRk_tensor_winograd_free(dRk_TensorWinogradPlan *plan);
 

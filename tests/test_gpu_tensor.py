@@ -349,7 +349,7 @@ def test_fp32_accurate_tensor_conv_matches_oracle_at_the_fp32_bound(name, n, cin
         g.batch = n
         g.math = "fp32x3"
         f = dr.feed_node(g, [cin, h, w])
-        c = conv_build(wt, b, 1, 1)(g, [f])
+        c = conv_build(wt, b, 1, 1, algo="tensor")(g, [f])     # the direct three-pass kernel (from 64 channels up the rule prefers Winograd)
         o = dr.Pooling(c, "max", [1, 2, 2, 1], [1, 2, 2, 1]) if pool else c
         dr.mark_as_output(o)
         dr.prepare(g)
@@ -371,6 +371,51 @@ def test_fp32_accurate_tensor_conv_matches_oracle_at_the_fp32_bound(name, n, cin
     # What is left is the tensor core's accumulator rounding (it truncates), which grows with the number of MMAs per output:
     # ~5e-6 at K = 9 * 32, ~5e-5 at K = 9 * 512.  An operand split that is off would show as ~1e-3 (the TF32 class's error).
     assert worst <= 6e-5
+
+
+X3_WINOGRAD_SHAPES = [
+    # name, n, cin, cout, h, w, pool, forced (None: the mode's static rule picks it)
+    ("x3w_64_64_30x34", 2, 64, 64, 30, 34, False, "tensor_winograd"),        # shallower than the rule's threshold: forced
+    ("x3w_64_192_13x17", 3, 64, 192, 17, 13, False, "tensor_winograd"),      # ragged 4x4 tiles
+    ("x3w_128_256_pool", 2, 128, 256, 28, 28, True, None),
+    ("x3w_32_48", 2, 32, 48, 20, 22, False, "tensor_winograd"),
+    ("x3w_conv3_2", 40, 256, 256, 56, 56, False, None),              # the benchmark's layers at full depth
+    ("x3w_conv4_pool", 16, 512, 512, 28, 28, True, None),
+    ("x3w_conv5_pool", 64, 512, 512, 14, 14, True, None),
+    ("x3w_conv1_2", 4, 64, 64, 224, 224, True, "tensor_winograd"),
+]
+
+
+@pytest.mark.parametrize("name,n,cin,cout,h,w,pool,forced", X3_WINOGRAD_SHAPES)
+def test_fp32_accurate_tensor_winograd_matches_oracle_at_the_fp32_bound(name, n, cin, cout, h, w, pool, forced):
+    """math = 'fp32x3', Winograd F(4x4,3x3) with its 36 products on the tensor cores as three TF32 passes each (operands stored as
+    high | low halves): a quarter of the direct multiplications, FP32-class error bound."""
+    x, wt, b = cases.conv_case(name, n, cin, cout, h, w, 3, True)
+    with dr.Environment() as env:
+        g = env.create_graph("CHW")
+        g.batch = n
+        g.math = "fp32x3"
+        f = dr.feed_node(g, [cin, h, w])
+        c = conv_build(wt, b, 1, 1, algo=forced)(g, [f])
+        o = dr.Pooling(c, "max", [1, 2, 2, 1], [1, 2, 2, 1]) if pool else c
+        dr.mark_as_output(o)
+        dr.prepare(g)
+        assert dr.lib.dR_getConvAlgo(c.ptr) == dr.CONV_ALGO["tensor_winograd"] and dr.lib.dR_getConvTensor(c.ptr) == 2
+        dr.feed_data(f, x)
+        got = dr.apply(g)[0]
+        launches = dr.lib.dR_getLaunchCount(g.ptr)
+        assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    ho, wo = (h // 2, w // 2) if pool else (h, w)
+    got = got.reshape(n, cout, ho, wo)
+    assert launches % 3 == 2 and launches >= 5          # feed layout, (input transform, GEMM, output transform) per image chunk, output layout
+    worst = 0.0
+    for i in sorted({0, n // 2, n - 1}):
+        ref = oracle.conv2d(x[i:i + 1], wt, b, (1, 1), 1)
+        if pool:
+            ref = oracle.pool(ref, (2, 2, 1), (2, 2, 1), 0)
+        worst = max(worst, rel_err(got[i:i + 1], ref))
+    print("fp32x3 winograd %s: max rel err %.2e" % (name, worst))
+    assert worst <= 1e-4
 
 
 def test_fp32_accurate_tensor_mode_on_a_whole_network():
