@@ -1585,6 +1585,8 @@ static int twino_chunk(int n, int W, int H, int Cin, int Cout)
     size_t c = (TWINO_SCRATCH_CAP - 16 * (size_t)BM * (Cin + Cout)) / per;     /* room for the padding rows */
     if (c < 1) c = 1;
     if (c > (size_t)n) c = (size_t)n;
+    const size_t chunks = ((size_t)n + c - 1) / c;          /* equal chunks rather than full ones and a short last one */
+    c = ((size_t)n + chunks - 1) / chunks;
     return (int)c;
 }
 
@@ -1701,6 +1703,8 @@ static int twino4_chunk(int n, int W, int H, int Cin, int Cout)
     size_t c = (TWINO_SCRATCH_CAP - 36 * (size_t)BM * (2 * Cin + Cout)) / per;
     if (c < 1) c = 1;
     if (c > (size_t)n) c = (size_t)n;
+    const size_t chunks = ((size_t)n + c - 1) / c;          /* equal chunks rather than full ones and a short last one */
+    c = ((size_t)n + chunks - 1) / chunks;
     return (int)c;
 }
 

@@ -179,6 +179,8 @@ static int wino_chunk(int n, int W, int H, int Cin, int Cout)
     size_t c = WINO_SCRATCH_CAP / per;
     if (c < 1) c = 1;
     if (c > (size_t)n) c = (size_t)n;
+    const size_t chunks = ((size_t)n + c - 1) / c;          /* equal chunks rather than full ones and a short last one */
+    c = ((size_t)n + chunks - 1) / chunks;
     return (int)c;
 }
 
@@ -365,6 +367,8 @@ static int wino4_chunk(int n, int W, int H, int Cin, int Cout)
     size_t c = WINO4_SCRATCH_CAP / per;
     if (c < 1) c = 1;
     if (c > (size_t)n) c = (size_t)n;
+    const size_t chunks = ((size_t)n + c - 1) / c;          /* equal chunks rather than full ones and a short last one */
+    c = ((size_t)n + chunks - 1) / chunks;
     return (int)c;
 }
 
