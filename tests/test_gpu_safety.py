@@ -91,6 +91,8 @@ GUARD_CONVS = [
     ("g_wino_odd", 2, 8, 20, 11, 9, 3, "fp32"),             # FP32 Winograd F(2x2,3x3) with ragged 2x2 output tiles
     ("g_wino4_odd", 2, 16, 20, 11, 9, 3, "fp32"),           # F(4x4,3x3): ragged 4x4 output tiles, Cout ends inside a warp
     ("g_wino4_c17", 3, 17, 19, 14, 6, 3, "fp32"),           # odd channel counts: scalar transform path
+    ("g_x3w_odd", 2, 128, 264, 13, 11, 3, "fp32x3"),        # F(4x4,3x3) with three-pass tensor products: ragged tiles, padded GEMM rows
+    ("g_x3_direct", 3, 32, 40, 15, 18, 3, "fp32x3"),        # the direct three-pass kernel
     ("g_direct_5x5", 2, 6, 10, 9, 13, 5, "fp32"),
     ("g_1x1_fp32", 2, 24, 52, 7, 5, 1, "fp32"),
     ("g_first_fp32", 2, 3, 20, 9, 11, 3, "fp32"),
@@ -108,7 +110,8 @@ def test_convolution_stores_stay_inside_the_output_tensor(name, n, cin, cout, h,
 
 @pytest.mark.parametrize("name,n,cin,cout,h,w,math", [("gp_swap", 40, 8, 72, 30, 26, "tf32"), ("gp_pair", 6, 16, 64, 56, 56, "tf32"),
                                                        ("gp_halo", 2, 32, 136, 12, 20, "tf32"), ("gp_first", 2, 3, 64, 18, 22, "tf32"),
-                                                       ("gp_wino4", 3, 16, 36, 14, 10, "fp32"), ("gp_wino4_c17", 2, 17, 21, 6, 18, "fp32")])
+                                                       ("gp_wino4", 3, 16, 36, 14, 10, "fp32"), ("gp_wino4_c17", 2, 17, 21, 6, 18, "fp32"),
+                                                       ("gp_x3w", 2, 128, 256, 12, 20, "fp32x3")])
 def test_fused_pool_stores_stay_inside_the_output_tensor(name, n, cin, cout, h, w, math):
     """conv3x3 + 2x2/2 max pool evaluated by the convolution's epilogue (FP32 mode: by the F(4x4,3x3) output transform): the
     guarded buffer is the POOLING node's output."""
