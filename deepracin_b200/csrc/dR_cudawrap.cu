@@ -7,7 +7,9 @@
  * every kernel in the library is built for sm_100a ahead of time.
  */
 #include <cuda_runtime.h>
+#include <pthread.h>
 #include <stdio.h>
+#include <string.h>
 #include "dR_core.h"
 #include "dR_b200.h"
 #include "dR_kernels.h"
@@ -96,6 +98,46 @@ extern "C" gboolean dR_createFloatBuffer(dR_Graph *net, cl_mem *mem, gint size, 
     return dR_createFloatBufferL(net, mem, (size_t)size);
 }
 
+/*
+ * Blocking upload from pageable host memory, the reference's clEnqueueWriteBuffer(CL_TRUE) (src/dR_clwrap.c:1079-1131).  A plain
+ * copy from pageable memory runs at a third of the link's rate, and for a caller that feeds float images through dR_feedData that
+ * copy is 40 % of a VGG-16 step.  Large sources therefore go through a pinned staging window: a few host threads copy disjoint
+ * chunks into it and each enqueues its chunk's DMA as soon as it is there, so the host copy and the DMA overlap; the call still
+ * returns only when the data is on the device.  Sources that are already pinned, and small ones, take the direct copy.
+ */
+#define UPLOAD_STAGE_MIN ((size_t)2 << 20)          /* smaller uploads: direct */
+#define UPLOAD_STAGE_WINDOW ((size_t)64 << 20)      /* pinned window; larger uploads go through it in rounds */
+#define UPLOAD_CHUNK ((size_t)1 << 20)
+#define UPLOAD_THREADS 4                            /* measured on a 16-core host: 1 / 2 / 4 / 8 threads feed 38.5 MB in 3.0 / 2.5 / 1.5 / 2.0 ms (plain pageable copy: 2.0) */
+
+typedef struct {
+    const char *src;
+    char *stage, *dst;
+    size_t bytes;
+    int first, dev;
+    cudaStream_t stream;
+    cudaError_t err;
+} dR_UploadJob;
+
+static void *uploadWorker(void *arg)
+{
+    dR_UploadJob *j = (dR_UploadJob *)arg;
+    j->err = cudaSetDevice(j->dev);
+    for (size_t off = (size_t)j->first * UPLOAD_CHUNK; off < j->bytes && j->err == cudaSuccess; off += (size_t)UPLOAD_THREADS * UPLOAD_CHUNK) {
+        const size_t len = j->bytes - off < UPLOAD_CHUNK ? j->bytes - off : UPLOAD_CHUNK;
+        memcpy(j->stage + off, j->src + off, len);
+        j->err = cudaMemcpyAsync(j->dst + off, j->stage + off, len, cudaMemcpyHostToDevice, j->stream);
+    }
+    return NULL;
+}
+
+static gboolean sourceIsPinned(const void *p)
+{
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { (void)cudaGetLastError(); return FALSE; }
+    return a.type == cudaMemoryTypeHost || a.type == cudaMemoryTypeManaged;
+}
+
 extern "C" gboolean dR_uploadArray(dR_Graph *net, gchar *name, void *src, size_t offset, size_t numBytes, cl_mem dst)
 {
     (void)name;
@@ -103,6 +145,38 @@ extern "C" gboolean dR_uploadArray(dR_Graph *net, gchar *name, void *src, size_t
     if (!dst || !src) { g_print("dR_uploadArray: NULL buffer\n"); return FALSE; }
     if (!bindDevice(net)) return FALSE;
     cudaStream_t s = streamOf(net);
+    dR_ClConfig *c = net->clConfig;
+    if (numBytes >= UPLOAD_STAGE_MIN && !sourceIsPinned(src)) {
+        const size_t window = numBytes < UPLOAD_STAGE_WINDOW ? numBytes : UPLOAD_STAGE_WINDOW;
+        if (c->uploadStageBytes < window) {
+            if (c->uploadStage) { cudaFreeHost(c->uploadStage); c->uploadStage = NULL; c->uploadStageBytes = 0; }
+            if (cudaMallocHost(&c->uploadStage, window) == cudaSuccess) c->uploadStageBytes = window;
+            else { (void)cudaGetLastError(); c->uploadStage = NULL; }
+        }
+        if (c->uploadStage) {
+            for (size_t done = 0; done < numBytes; done += window) {
+                const size_t part = numBytes - done < window ? numBytes - done : window;
+                dR_UploadJob jobs[UPLOAD_THREADS];
+                pthread_t th[UPLOAD_THREADS];
+                gboolean started[UPLOAD_THREADS];
+                for (int i = 0; i < UPLOAD_THREADS; i++) {
+                    jobs[i].src = (const char *)src + done; jobs[i].stage = (char *)c->uploadStage; jobs[i].dst = (char *)dst + offset + done;
+                    jobs[i].bytes = part; jobs[i].first = i; jobs[i].dev = (int)c->clDeviceNumber; jobs[i].stream = s; jobs[i].err = cudaSuccess;
+                    started[i] = i > 0 && (size_t)i * UPLOAD_CHUNK < part && pthread_create(&th[i], NULL, uploadWorker, &jobs[i]) == 0;
+                }
+                uploadWorker(&jobs[0]);
+                for (int i = 1; i < UPLOAD_THREADS; i++) {
+                    if (started[i]) pthread_join(th[i], NULL);
+                    else if ((size_t)i * UPLOAD_CHUNK < part) uploadWorker(&jobs[i]);       /* no thread to be had: this one does the share */
+                }
+                for (int i = 0; i < UPLOAD_THREADS; i++)
+                    if (jobs[i].err != cudaSuccess) return check(net, jobs[i].err, "cudaMemcpyAsync H2D (staged)");
+                /* the window is written again by the next round (or the next call): wait for its DMAs */
+                if (!check(net, cudaStreamSynchronize(s), "upload synchronize")) return FALSE;
+            }
+            return TRUE;
+        }
+    }
     if (!check(net, cudaMemcpyAsync((char *)dst + offset, src, numBytes, cudaMemcpyHostToDevice, s), "cudaMemcpyAsync H2D")) return FALSE;
     return check(net, cudaStreamSynchronize(s), "upload synchronize");
 }
@@ -202,6 +276,7 @@ extern "C" gboolean dR_cleanupCL(dR_Graph *net)
     if (net->config->dryRun) { c->cleanupDone = TRUE; return TRUE; }
     if (c->evStart) { cudaEventDestroy((cudaEvent_t)c->evStart); cudaEventDestroy((cudaEvent_t)c->evStop); c->evStart = c->evStop = NULL; }
     if (c->copyStream) { cudaStreamDestroy((cudaStream_t)c->copyStream); c->copyStream = NULL; }
+    if (c->uploadStage) { cudaFreeHost(c->uploadStage); c->uploadStage = NULL; c->uploadStageBytes = 0; }
     if (c->ownsStream && c->clCommandQueue) cudaStreamDestroy(streamOf(net));
     c->clCommandQueue = NULL;
     g_free(c->clDeviceName);

@@ -168,6 +168,8 @@ struct dR_ClConfig {
     void *copyStream;                  /* second stream for overlapped feeds */
     gint smCount;
     size_t smemPerBlockOptin;
+    void *uploadStage;                 /* pinned staging buffer of the blocking upload (pageable sources), allocated at the first large upload */
+    size_t uploadStageBytes;
 };
 
 struct dR_Config {
