@@ -134,7 +134,7 @@ gchar *dR_conv2d_printLayer(dR_Node *layer)
     dR_Conv2d_Data *c = (dR_Conv2d_Data *)layer->layer;
     static const char *acts[] = {"Linear", "ReLU", "Sigmoid", "Tan"};
     static const char *algos[DR_CONV_ALGOS] = {"auto", "direct (FP32 implicit GEMM)", "Winograd F(2x2,3x3)", "1x1 GEMM", "tcgen05 TF32 implicit GEMM",
-                                               "Winograd F(2x2,3x3), tcgen05 TF32 products", "Winograd F(4x4,3x3)"};
+                                               "Winograd, tcgen05 products (F(2x2,3x3) TF32 / F(4x4,3x3) three-pass)", "Winograd F(4x4,3x3)"};
     return g_strdup_printf("Conv2d Layer: %d\n Filter dimensions: %dx%d\n Input channels: %d\n Output channels: %d\n Activation: %s\n"
                            " Stride: %d, %d, %d, %d\n Use bias: %s\n Kernel family: %s\n",
                            layer->layerID, c->shape.s0, c->shape.s1, c->shape.s2, c->shape.s3, acts[c->activation & 3],

@@ -16,7 +16,8 @@ enum dR_ConvAlgo {
     DR_CONV_WINOGRAD = 2,   /* F(2x2,3x3): transform, 16 transform-domain GEMMs, inverse transform */
     DR_CONV_ONEBYONE = 3,   /* 1x1 stride 1 as one GEMM over pixels */
     DR_CONV_TENSOR = 4,     /* tcgen05 TF32 implicit GEMM (TMA-fed, TMEM accumulators) */
-    DR_CONV_TENSOR_WINOGRAD = 5, /* F(2x2,3x3) with the 16 transform-domain GEMMs on the tcgen05 tensor cores (TF32 mode) */
+    DR_CONV_TENSOR_WINOGRAD = 5, /* Winograd with the transform-domain GEMMs on the tcgen05 tensor cores: F(2x2,3x3) with TF32 products in TF32 mode,
+                                    F(4x4,3x3) with three-pass (FP32-accurate) products in DR_MATH_FP32_TENSOR mode */
     DR_CONV_WINOGRAD4 = 6   /* F(4x4,3x3) in FP32: 36 transform-domain GEMMs, 4x fewer multiplications, error about 1e-5 of max|ref| */
 };
 #define DR_CONV_ALGOS 7
