@@ -494,7 +494,7 @@ def run_ours(args):
                                             "ms_per_layer": xroof.get("ms_per_layer"),
                                             "what": "math mode fp32x3: 3x3 layers with >= 8 input channels evaluate every product as hi*hi + hi*lo + lo*hi in three TF32 "
                                                     "tensor-core passes (FP32-class error bound 1e-4 x max|ref| per layer) -- the deep layers as Winograd F(4x4,3x3) "
-                                                    "with its 36 transform-domain products on the tensor cores, the others directly; first layer, FC, pooling, softmax on the FP32 kernels"}
+                                                    "with its 36 transform-domain products on the tensor cores, the others directly, FC as a three-pass split-K GEMM; first layer, pooling, softmax on the FP32 kernels"}
         if "squeezenet_b64" in extra:
             sq = extra["squeezenet_b64"]
             line["squeezenet"] = {"batch64": {"images_per_s": sq["images_per_s"], "ms_per_step": sq["ms_per_step"], "e2e_images_per_s": sq["e2e_images_per_s"],

@@ -93,9 +93,13 @@ gint32 dR_fc_getRequiredOutputBufferSize(dR_Node *layer) { return layer->oshape.
 gboolean dR_fc_createKernel(dR_Graph *net, dR_Node *layer)
 {
     dR_FC_Data *fc = (dR_FC_Data *)layer->layer;
-    /* TF32 mode, batches of 16..128: split-K GEMM on the tensor cores; otherwise the FP32 weight-streaming kernels */
-    fc->chosenTensor = net->config->mathMode == DR_MATH_TF32 && dRk_tensor_fc_supported(net->config->batchSize, fc->shape.s0, fc->shape.s1);
-    layer->scratchFloats = fc->chosenTensor ? dRk_tensor_fc_scratch_floats(net->config->batchSize, fc->shape.s0, fc->shape.s1)
+    /* tensor modes, batches of 16..128: split-K GEMM on the tensor cores (2: with three-pass, FP32-accurate products); otherwise
+       the FP32 weight-streaming kernels */
+    fc->chosenTensor = 0;
+    if (net->config->mathMode != DR_MATH_FP32 && dRk_tensor_fc_supported(net->config->batchSize, fc->shape.s0, fc->shape.s1))
+        fc->chosenTensor = net->config->mathMode == DR_MATH_FP32_TENSOR ? 2 : 1;
+    layer->scratchFloats = fc->chosenTensor == 2 ? dRk_tensor_fc_x3_scratch_floats(net->config->batchSize, fc->shape.s0, fc->shape.s1)
+                         : fc->chosenTensor ? dRk_tensor_fc_scratch_floats(net->config->batchSize, fc->shape.s0, fc->shape.s1)
                                             : dRk_fc_scratch_floats(net->config->batchSize, fc->shape.s0, fc->shape.s1);
     return TRUE;
 }
@@ -105,7 +109,7 @@ gboolean dR_fc_allocateBuffers(dR_Graph *net, dR_Node *layer)
     dR_FC_Data *fc = (dR_FC_Data *)layer->layer;
     gboolean ret;
     if (!fc->hasVariables) { g_print("FullyConnected Layer %d has no weights (call dR_FullyConnected_setVariables)\n", layer->layerID); return FALSE; }
-    if (fc->chosenTensor) ret = dR_createFloatBufferL(net, &fc->weightsBufT, dRk_tensor_fc_packed_floats(fc->shape.s0, fc->shape.s1));
+    if (fc->chosenTensor) ret = dR_createFloatBufferL(net, &fc->weightsBufT, (fc->chosenTensor == 2 ? 2 : 1) * dRk_tensor_fc_packed_floats(fc->shape.s0, fc->shape.s1));
     else ret = dR_createFloatBufferL(net, &fc->weightsBuf, (size_t)fc->shape.s0 * fc->shape.s1);
     if (fc->useBias) ret &= dR_createFloatBuffer(net, &fc->biasBuf, fc->shape.s1, CL_MEM_READ_ONLY);
     return ret;
@@ -117,9 +121,10 @@ gboolean dR_fc_fillBuffers(dR_Graph *net, dR_Node *layer)
     gboolean ret;
     if (fc->chosenTensor) {
         /* block-by-block packing for the TMA-fed B operand */
-        const size_t np = dRk_tensor_fc_packed_floats(fc->shape.s0, fc->shape.s1);
+        const size_t np = (fc->chosenTensor == 2 ? 2 : 1) * dRk_tensor_fc_packed_floats(fc->shape.s0, fc->shape.s1);
         gfloat *t = (gfloat *)g_malloc(np * sizeof(gfloat));
-        ret = dRk_tensor_fc_pack_weights(fc->weights, t, fc->shape.s0, fc->shape.s1) == 0 &&
+        ret = (fc->chosenTensor == 2 ? dRk_tensor_fc_x3_pack_weights(fc->weights, t, fc->shape.s0, fc->shape.s1)
+                                     : dRk_tensor_fc_pack_weights(fc->weights, t, fc->shape.s0, fc->shape.s1)) == 0 &&
               dR_uploadArray(net, "", t, 0, np * sizeof(cl_float), fc->weightsBufT);
         g_free(t);
     } else {
@@ -138,9 +143,9 @@ gboolean dR_fc_compute(dR_Graph *net, dR_Node *layer)
     dR_beginCLKernel(net);
     if (fc->chosenTensor) {
         if (!fc->tmaDescs) {
-            fc->tmaDescs = dRk_tensor_fc_plan(dR_actPtr(in), (const float *)fc->weightsBufT, fc->useBias ? (const float *)fc->biasBuf : NULL,
-                                              dR_actPtr(layer), (float *)net->scratch, net->config->batchSize, fc->shape.s0, fc->shape.s1,
-                                              fc->activation == tReLU ? 1 : 0, (int *)net->statusWord);
+            fc->tmaDescs = (fc->chosenTensor == 2 ? dRk_tensor_fc_x3_plan : dRk_tensor_fc_plan)(
+                dR_actPtr(in), (const float *)fc->weightsBufT, fc->useBias ? (const float *)fc->biasBuf : NULL, dR_actPtr(layer),
+                (float *)net->scratch, net->config->batchSize, fc->shape.s0, fc->shape.s1, fc->activation == tReLU ? 1 : 0, (int *)net->statusWord);
             if (!fc->tmaDescs) { g_print("FullyConnected Layer %d: tensor-core plan could not be built\n", layer->layerID); return FALSE; }
         }
         net->clConfig->clError = dRk_tensor_fc_run(net->clConfig->clCommandQueue, (dRk_TensorFcPlan *)fc->tmaDescs);

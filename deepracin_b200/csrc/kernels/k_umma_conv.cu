@@ -107,7 +107,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                 for (int tap = 0; tap < p.taps && pre < C::STAGES; tap++)
                     for (int ks = ks0; ks < ks1 && pre < C::STAGES; ks++, pre++) {
                         mbar_expect_tx(full_bar(pre), (uint32_t)p.stage_tx);
-                        if (p.bpacked) tma_load_2d(base + pre * C::STAGE_BYTES + A_STAGE_BYTES, &mapB, 0, (nt * p.kslabs + ks) * BN, full_bar(pre));
+                        if (p.bpacked) tma_load_2d(base + pre * C::STAGE_BYTES + A_STAGE_BYTES, &mapB, 0, (nt * (p.x3cat ? 2 * p.x3cat : p.kslabs) + b_slab(ks)) * BN, full_bar(pre));
                         else tma_load_2d(base + pre * C::STAGE_BYTES + A_STAGE_BYTES, &mapB, tap * p.CinPad + b_slab(ks) * BK, brow, full_bar(pre));
                     }
             }
@@ -139,7 +139,7 @@ k_umma_conv(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CU
                             }
                         }
                         if (!armed) {
-                            if (p.bpacked) tma_load_2d(sb, &mapB, 0, (nt * p.kslabs + ks) * BN, full_bar(stage));
+                            if (p.bpacked) tma_load_2d(sb, &mapB, 0, (nt * (p.x3cat ? 2 * p.x3cat : p.kslabs) + b_slab(ks)) * BN, full_bar(stage));
                             else tma_load_2d(sb, &mapB, tap * p.CinPad + b_slab(ks) * BK, brow, full_bar(stage));
                         }
                         issued++;
@@ -1448,9 +1448,10 @@ int drk_fc_reduce_launch(cudaStream_t st, const float *partial, const float *bia
 
 struct dRk_TensorFcPlan {
     dRk_TensorConvPlan conv;
-    const float *bias;
-    float *out, *scratch;
-    int n, Nout, act;
+    const float *bias, *in;
+    float *out, *scratch;       /* split-K partial sums */
+    float *in2;                 /* three-pass mode: the activations as (high | low) rows [n][2*Nin], rewritten by every run */
+    int n, Nin, Nout, act;
 };
 
 extern "C" int dRk_tensor_fc_supported(int n, int Nin, int Nout)
@@ -1495,11 +1496,20 @@ extern "C" int dRk_tensor_fc_pack_weights(const float *w, float *wpacked, int Ni
     return 0;
 }
 
-extern "C" dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wT, const float *bias, float *out, float *scratch,
-                                                int n, int Nin, int Nout, int act, int *status)
+static int tensor_fc_ksplit(int Nin, int Nout, int x3, int sms)
+{
+    const int kslabs = (x3 ? 3 : 1) * (Nin / BK);
+    int ksplit = sms / ((Nout + 255) / 256);
+    if (ksplit < 1) ksplit = 1;
+    if (ksplit > kslabs / 8) ksplit = kslabs / 8 > 0 ? kslabs / 8 : 1;
+    return ksplit;
+}
+
+static dRk_TensorFcPlan *tensor_fc_plan(const float *in, const float *wpacked, const float *bias, float *out, float *scratch,
+                                        int n, int Nin, int Nout, int act, int x3, int *status)
 {
     if (!dRk_tensor_fc_supported(n, Nin, Nout) || !scratch) return NULL;
-    if (((uintptr_t)in % 16) || ((uintptr_t)wT % 16) || ((uintptr_t)scratch % 16)) return NULL;
+    if (((uintptr_t)in % 16) || ((uintptr_t)wpacked % 16) || ((uintptr_t)scratch % 16)) return NULL;
     PFN_encodeTiled enc = get_encode();
     if (!enc) return NULL;
     int dev = 0, sms = 148;
@@ -1509,41 +1519,120 @@ extern "C" dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wT
     if (!fp) return NULL;
     dRk_TensorConvPlan *pl = &fp->conv;
     UmmaParams &p = pl->p;
+    /* three-pass mode: the head of the scratch holds the (high | low) activations, the partial sums follow */
+    float *in2 = x3 ? scratch : NULL;
+    float *partial = x3 ? scratch + (((size_t)n * 2 * Nin + 3) & ~(size_t)3) : scratch;
     p.n = n; p.W = 1; p.H = 1; p.Cin = Nin; p.CinPad = Nin; p.Cout = Nout;
-    p.taps = 1; p.kw = 1; p.pad = 0; p.kslabs = Nin / BK;
+    p.taps = 1; p.kw = 1; p.pad = 0;
+    p.x3cat = x3 ? Nin / BK : 0;
+    p.kslabs = (x3 ? 3 : 1) * (Nin / BK);
     p.S = 0; p.TW = BM; p.TH = 1; p.tiles_x = p.tiles_y = 1;
     p.total_sub = n; p.m_tiles = 1; p.n_tiles = (Nout + 255) / 256;
-    p.bias = NULL; p.out = scratch; p.ldo = Nout; p.coff = 0; p.act = 0; p.pool = 0; p.status = status;
-    p.ksplit = sms / p.n_tiles;
-    if (p.ksplit < 1) p.ksplit = 1;
-    if (p.ksplit > p.kslabs / 8) p.ksplit = p.kslabs / 8 > 0 ? p.kslabs / 8 : 1;
+    p.bias = NULL; p.out = partial; p.ldo = Nout; p.coff = 0; p.act = 0; p.pool = 0; p.status = status;
+    p.ksplit = tensor_fc_ksplit(Nin, Nout, x3, sms);
     p.kper = (p.kslabs + p.ksplit - 1) / p.ksplit;
     p.ksplit = (p.kslabs + p.kper - 1) / p.kper;          /* no empty parts */
     p.split_stride = (long long)n * Nout;
     pl->BN = 256;
     p.stage_tx = A_STAGE_BYTES + 256 * BK * 4;
+    const CUtensorMapDataType dt = x3 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_TFLOAT32;
+    const cuuint64_t Kw = (cuuint64_t)(x3 ? 2 * Nin : Nin);
     const cuuint32_t ones[2] = {1, 1};
-    const cuuint64_t adims[2] = {(cuuint64_t)Nin, (cuuint64_t)n}, astr[1] = {(cuuint64_t)Nin * 4};
+    const cuuint64_t adims[2] = {Kw, (cuuint64_t)n}, astr[1] = {Kw * 4};
     const cuuint32_t abox[2] = {BK, BM};
-    CUresult r = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)in, adims, astr, abox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+    CUresult r = enc(&pl->mapA, dt, 2, (void *)(x3 ? in2 : in), adims, astr, abox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     /* the packed weights as a 32-wide matrix whose rows are the blocks' rows one after another */
     p.bpacked = 1;
-    const cuuint64_t bdims[2] = {(cuuint64_t)BK, (cuuint64_t)p.n_tiles * p.kslabs * 256}, bstr[1] = {(cuuint64_t)BK * 4};
+    const cuuint64_t bdims[2] = {(cuuint64_t)BK, (cuuint64_t)p.n_tiles * (x3 ? 2 : 1) * (Nin / BK) * 256}, bstr[1] = {(cuuint64_t)BK * 4};
     const cuuint32_t bbox[2] = {BK, 256};
     if (r == CUDA_SUCCESS)
-        r = enc(&pl->mapB, CU_TENSOR_MAP_DATA_TYPE_TFLOAT32, 2, (void *)wT, bdims, bstr, bbox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
+        r = enc(&pl->mapB, dt, 2, (void *)wpacked, bdims, bstr, bbox, ones, CU_TENSOR_MAP_INTERLEAVE_NONE,
                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { fprintf(stderr, "tensor fc plan: tensor map rejected (%d)\n", (int)r); free(fp); return NULL; }
     const long long tiles = (long long)p.n_tiles * p.ksplit;
     pl->grid = (int)(tiles < sms ? tiles : sms);
-    fp->bias = bias; fp->out = out; fp->scratch = scratch; fp->n = n; fp->Nout = Nout; fp->act = act;
+    fp->bias = bias; fp->in = in; fp->out = out; fp->scratch = partial; fp->in2 = in2; fp->n = n; fp->Nin = Nin; fp->Nout = Nout; fp->act = act;
     return fp;
+}
+
+extern "C" dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wpacked, const float *bias, float *out, float *scratch,
+                                                int n, int Nin, int Nout, int act, int *status)
+{
+    return tensor_fc_plan(in, wpacked, bias, out, scratch, n, Nin, Nout, act, 0, status);
+}
+
+/* FP32-accurate variant: every product as hi x hi + hi x lo + lo x hi of TF32 halves (three passes of the K loop); the weights
+ * are packed as high and low blocks, the activations are split into (high | low) rows at the head of `scratch` by every run */
+extern "C" size_t dRk_tensor_fc_x3_packed_floats(int Nin, int Nout) { return 2 * dRk_tensor_fc_packed_floats(Nin, Nout); }
+
+extern "C" size_t dRk_tensor_fc_x3_scratch_floats(int n, int Nin, int Nout)
+{
+    if (!dRk_tensor_fc_supported(n, Nin, Nout)) return 0;
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return (((size_t)n * 2 * Nin + 3) & ~(size_t)3) + (size_t)tensor_fc_ksplit(Nin, Nout, 1, sms) * n * Nout;
+}
+
+/* [n tile][2 * K slabs][256][32]: the slabs of the high parts (upper 19 bits of the weight), then those of the remainders */
+extern "C" int dRk_tensor_fc_x3_pack_weights(const float *w, float *wpacked, int Nin, int Nout)
+{
+    if (!w || !wpacked || Nin <= 0 || Nout <= 0 || Nin % BK != 0) return -1;
+    const int ntiles = (Nout + 255) / 256, kslabs = Nin / BK;
+    for (int nt = 0; nt < ntiles; nt++)
+        for (int ks = 0; ks < kslabs; ks++) {
+            float *hi = wpacked + ((size_t)nt * 2 * kslabs + ks) * 256 * BK, *lo = hi + (size_t)kslabs * 256 * BK;
+            const int valid = Nout - nt * 256 < 256 ? Nout - nt * 256 : 256;
+            for (int e = 0; e < BK; e++) {
+                const float *src = w + (size_t)(ks * BK + e) * Nout + (size_t)nt * 256;
+                for (int r = 0; r < 256; r++) {
+                    float h = 0.0f, l = 0.0f;
+                    if (r < valid) {
+                        uint32_t bits;
+                        memcpy(&bits, &src[r], 4);
+                        bits &= 0xffffe000u;
+                        memcpy(&h, &bits, 4);
+                        l = src[r] - h;
+                    }
+                    hi[(size_t)r * BK + e] = h;
+                    lo[(size_t)r * BK + e] = l;
+                }
+            }
+        }
+    return 0;
+}
+
+extern "C" dRk_TensorFcPlan *dRk_tensor_fc_x3_plan(const float *in, const float *wpacked2, const float *bias, float *out, float *scratch,
+                                                   int n, int Nin, int Nout, int act, int *status)
+{
+    return tensor_fc_plan(in, wpacked2, bias, out, scratch, n, Nin, Nout, act, 1, status);
+}
+
+/* rows of (high | low) halves: out[r][c] = upper 19 bits of in[r][c], out[r][K + c] = the remainder (exact) */
+__global__ void k_split_hi_lo(const float *__restrict__ in, float *__restrict__ out, int rows, int K)
+{
+    drk_dep_trigger();
+    drk_dep_wait();
+    const size_t total = (size_t)rows * K;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / K, c = i - r * K;
+        const float v = in[i];
+        const float h = __uint_as_float(__float_as_uint(v) & 0xffffe000u);
+        out[r * 2 * K + c] = h;
+        out[r * 2 * K + K + c] = v - h;
+    }
 }
 
 extern "C" int dRk_tensor_fc_run(dRk_stream stream, dRk_TensorFcPlan *fp)
 {
     if (!fp) return -1;
+    if (fp->in2) {
+        const size_t total = (size_t)fp->n * fp->Nin;
+        drk_launch_dep(k_split_hi_lo, dim3(drk_blocks(total, 256, 148u * 8u)), dim3(256), 0, drk_stream(stream), fp->in, fp->in2, fp->n, fp->Nin);
+        DRK_COUNT_LAUNCH();
+        const int rc0 = DRK_LAUNCH_RESULT();
+        if (rc0) return rc0;
+    }
     int rc = launch_umma<256>(drk_stream(stream), &fp->conv);
     if (rc) return rc;
     return drk_fc_reduce_launch(drk_stream(stream), fp->scratch, fp->bias, fp->out, fp->n * fp->Nout, fp->Nout, fp->conv.p.ksplit, fp->act);

@@ -219,6 +219,14 @@ size_t dRk_tensor_fc_packed_floats(int Nin, int Nout);
 int dRk_tensor_fc_pack_weights(const float *w, float *wpacked, int Nin, int Nout);
 dRk_TensorFcPlan *dRk_tensor_fc_plan(const float *in, const float *wpacked, const float *bias, float *out, float *scratch,
                                      int n, int Nin, int Nout, int act, int *status);
+/* The same with FP32-accurate products (three TF32 passes over high and low halves; DR_MATH_FP32_TENSOR mode): weights from
+ * dRk_tensor_fc_x3_pack_weights (twice the floats), scratch of dRk_tensor_fc_x3_scratch_floats() floats (its head holds the
+ * activations split into halves by every run).  Run and free as below. */
+size_t dRk_tensor_fc_x3_packed_floats(int Nin, int Nout);
+size_t dRk_tensor_fc_x3_scratch_floats(int n, int Nin, int Nout);
+int dRk_tensor_fc_x3_pack_weights(const float *w, float *wpacked2, int Nin, int Nout);
+dRk_TensorFcPlan *dRk_tensor_fc_x3_plan(const float *in, const float *wpacked2, const float *bias, float *out, float *scratch,
+                                        int n, int Nin, int Nout, int act, int *status);
 int dRk_tensor_fc_run(dRk_stream stream, dRk_TensorFcPlan *plan);
 void dRk_tensor_fc_free(dRk_TensorFcPlan *plan);
 

@@ -219,6 +219,12 @@ def test_tensor_fc_matches_oracle(n, c, h, w, nout, act):
     (exact,) = run_graph(lambda g, f: dr.Fully_Connected(f[0], [c * h * w, nout], "relu" if act else "linear", wt, b), [x], math="fp32")
     assert rel_err(exact, ref) <= 1e-4
     assert not np.array_equal(got, exact)       # the two arithmetic classes really are different kernels
+    # the FP32-accurate tensor mode: the same GEMM with three-pass products, at the FP32 class's bound
+    (x3,) = run_graph(lambda g, f: dr.Fully_Connected(f[0], [c * h * w, nout], "relu" if act else "linear", wt, b), [x], math="fp32x3")
+    err = rel_err(x3, ref)
+    print("fp32x3 fc %d->%d batch %d: %.2e" % (c * h * w, nout, n, err))
+    assert err <= 2e-5
+    assert not np.array_equal(x3, exact) and not np.array_equal(x3, got)
 
 
 def _random_shapes(count, seed):
