@@ -264,6 +264,30 @@ def test_tensor_planner_picks_the_expected_kernels_and_geometries():
     assert describe(2, 20, 20, 64, 64, 5, 0)[0] == 0                                 # 5x5 filters stay on the FP32 kernels
 
 
+def test_static_rule_per_math_mode_on_the_vgg16_channel_plan():
+    """Which kernel family the planner's static rule gives every VGG-16 convolution in the three arithmetic modes (planning only, no
+    device): FP32 -> the few-channel direct kernel, then Winograd F(4x4,3x3); TF32 -> the tensor kernels; FP32-accurate tensor mode ->
+    FFMA for the RGB layer, the direct three-pass kernel up to 128 -> 128, Winograd F(4x4,3x3) with three-pass products from 128 -> 256 on."""
+    plan = [(3, 64), (64, 64), (64, 128), (128, 128), (128, 256), (256, 256), (256, 256), (256, 512), (512, 512), (512, 512), (512, 512), (512, 512), (512, 512)]
+    expected = {"fp32": [1] + [6] * 12, "tf32": [4] * 13, "fp32x3": [1, 4, 4, 4] + [5] * 9}
+    tensor = {"fp32": [0] * 13, "tf32": [1] * 13, "fp32x3": [0] + [2] * 12}
+    for math in ("fp32", "tf32", "fp32x3"):
+        with dr.Environment() as env:
+            g = env.create_graph("HWC")
+            g.batch = 64
+            g.math = math
+            node = dr.feed_node(g, [16, 16, 3])
+            convs = []
+            for cin, cout in plan:
+                node = dr.Conv2d(node, [3, 3, cin, cout], [1, 1, 1, 1], "relu", np.zeros((3, 3, cin, cout), np.float32), np.zeros(cout, np.float32))
+                convs.append(node)
+            dr.mark_as_output(node)
+            dr.lib.dR_setMathMode(g.ptr, dr.MATH[math])
+            dry_prepare(g)
+            assert [dr.lib.dR_getConvAlgo(c.ptr) for c in convs] == expected[math], math
+            assert [dr.lib.dR_getConvTensor(c.ptr) for c in convs] == tensor[math], math
+
+
 def test_tensor_planner_geometries_respect_the_kernels_limits():
     """Every geometry the planner can hand to the transposed and row-pair kernels stays inside what those kernels were
     written for: N a multiple of 16 and at most 256, whole 32-column epilogue chunks at the 16-pixel pitch, an even row
