@@ -1015,6 +1015,15 @@ static double swap_fill(int W, int H)
     return swap_geometry(W, H, 1, &P, &TW, &TH);
 }
 
+/* the geometry and the tile count of a launch of n images */
+static double swap_geometry_for(int n, int W, int H, int Cout, int pool, int sms, int *P, int *TW, int *TH, long long *tiles)
+{
+    (void)sms;
+    const double fill = swap_geometry(W, H, pool, P, TW, TH);
+    *tiles = fill > 0.0 ? (long long)n * ((W + *TW - 1) / *TW) * ((H + *TH - 1) / *TH) * ((Cout + BM - 1) / BM) : 0;
+    return fill;
+}
+
 /* which kernel evaluates a layer shape; the packed-filter layout depends on it, so packing and planning both ask here.
  * The debug switches (dRk_debug_switches) exist for A/B comparisons of the variants when profiling. */
 enum { VAR_NONE = 0, VAR_FLAT, VAR_PLAIN, VAR_HALO, VAR_SWAP, VAR_PAIR, VAR_FIRST };
@@ -1091,11 +1100,16 @@ extern "C" int dRk_tensor_conv_pack_weights(const float *w, float *dst, int W, i
 static int use_swap_kernel(int variant, int n, int W, int H, int Cout, int pool, int sms)
 {
     int P, TW, TH;
+    long long tiles;
     if (dRk_debug_switches()->no_swap) return 0;
-    const double fill = swap_geometry(W, H, pool ? 1 : 0, &P, &TW, &TH);
+    const double fill = swap_geometry_for(n, W, H, Cout, pool ? 1 : 0, sms, &P, &TW, &TH, &tiles);
     if (fill <= 0.0) return 0;
-    const long long tiles = (long long)n * ((W + TW - 1) / TW) * ((H + TH - 1) / TH) * ((Cout + BM - 1) / BM);
     if (tiles >= sms) return variant == VAR_SWAP || fill >= halo_fill(W, H) - 0.01;
+    /* from about half a tile per SM the transposed kernel still wins (128 -> 128 @28x28 at batch 32, 128 tiles: 17 against 27 us;
+       512 -> 512 @14x14 at batch 32: 48 against 54 us; at 64 tiles the two are level).  Halving the tile rows to double the tile
+       count was measured and loses: an MMA of N = 128 columns issues at 104 clocks, barely faster than N = 224 (256 -> 256 @14x14
+       at batch 64: 45 against 27 us). */
+    if (2 * tiles >= sms) return 1;
     const double tx = (W + HALO_TW - 1) / HALO_TW, ty = (H + 15) / 16;
     return Cout <= BM && (double)W * H / (tx * ty * SWAP_N) >= 0.8;
 }
@@ -1162,7 +1176,8 @@ extern "C" int dRk_tensor_conv_describe(int n, int W, int H, int Cin, int Cout, 
     } else if (v == VAR_SWAP || v == VAR_HALO) {
         if (use_swap_kernel(v, n, W, H, Cout, fuse_pool2, sms)) {
             v = VAR_SWAP;
-            swap_geometry(W, H, fuse_pool2 ? 1 : 0, P, TW, TH);
+            long long tiles;
+            swap_geometry_for(n, W, H, Cout, fuse_pool2 ? 1 : 0, sms, P, TW, TH, &tiles);
             *ncols = *P * *TH;
         } else if (halo_fill(W, H) >= 0.55 && !dRk_debug_switches()->no_halo) {
             v = VAR_HALO;
@@ -1235,7 +1250,8 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float
     } else if ((variant == VAR_SWAP || variant == VAR_HALO) && use_swap_kernel(variant, n, W, H, Cout, fuse_pool2, sms)) {
         pl->swap = 1;
         p.S = 1;
-        swap_geometry(W, H, fuse_pool2 ? 1 : 0, &p.P, &p.TW, &p.TH);
+        long long geo_tiles;
+        swap_geometry_for(n, W, H, Cout, fuse_pool2 ? 1 : 0, sms, &p.P, &p.TW, &p.TH, &geo_tiles);
         p.ncols = p.P * p.TH;
         p.tiles_x = (W + p.TW - 1) / p.TW; p.tiles_y = (H + p.TH - 1) / p.TH;
         p.total_sub = (long long)n * p.tiles_x * p.tiles_y;
@@ -1341,7 +1357,8 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_x3_plan(const float *in, const fl
     p.taps = 9; p.kw = 3; p.pad = 1; p.kslabs = p.CinPad / BK;
     p.bias = bias; p.out = out; p.ldo = ldo; p.coff = coff; p.act = act; p.status = status; p.pool = fuse_pool2 ? 1 : 0;
     p.ksplit = 1; p.kper = p.kslabs; p.S = 1;
-    swap_geometry(W, H, fuse_pool2 ? 1 : 0, &p.P, &p.TW, &p.TH);
+    long long geo_tiles;
+    swap_geometry_for(n, W, H, Cout, fuse_pool2 ? 1 : 0, sms, &p.P, &p.TW, &p.TH, &geo_tiles);
     p.ncols = p.P * p.TH;
     p.tiles_x = (W + p.TW - 1) / p.TW; p.tiles_y = (H + p.TH - 1) / p.TH;
     p.total_sub = (long long)n * p.tiles_x * p.tiles_y;

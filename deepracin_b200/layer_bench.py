@@ -34,10 +34,12 @@ def time_graph(g, iters, warmup):
     for _ in range(warmup):
         lib.dR_apply(g.ptr)
     lib.dR_synchronize(g.ptr)
-    lib.dR_timerStart(g.ptr)
-    for _ in range(iters):
-        lib.dR_apply(g.ptr)
-    return lib.dR_timerStopMs(g.ptr) / iters
+    # the timed loop runs inside the library (dR_applyTimed): a Python-side loop adds several microseconds of host time per launch,
+    # which a layer of 10-20 us cannot hide
+    ms = lib.dR_applyTimed(g.ptr, iters)
+    if ms <= 0:
+        raise RuntimeError("dR_applyTimed failed")
+    return ms / iters
 
 
 def conv_layer(cin, cout, hw, batch, k=3, math="tf32", algo="auto", iters=20, warmup=5, act="relu"):
@@ -127,7 +129,7 @@ def membound(iters, warmup):
 def sweep(iters, warmup):
     out = []
     for cin, hw in ((64, 56), (128, 28), (256, 14)):
-        for math, algo in (("fp32", "direct"), ("fp32", "winograd"), ("tf32", "auto")):
+        for math, algo in (("fp32", "direct"), ("fp32", "winograd"), ("fp32", "winograd4"), ("tf32", "auto")):
             out.append(conv_layer(cin, cin, hw, 32, 3, math, algo, iters, warmup))
     for math in ("fp32", "tf32"):
         out.append(conv_layer(256, 512, 28, 64, 1, math, "auto", iters, warmup))
