@@ -14,7 +14,7 @@ of its class probabilities inside the timed region.  The same line carries, as o
   fp32_exact   VGG-16 batch 64 in the reference's own arithmetic (FP32 FFMA kernels, tolerance 1e-4 per layer)
   fp32_accurate_tensor  VGG-16 batch 64 in math mode fp32x3: FP32-class error bound from three TF32 tensor-core passes per product
   e2e_u8       the headline's end-to-end loop fed with 8-bit image samples (dR_feedDataU8Async: a quarter of the host-link bytes)
-  squeezenet   SqueezeNet v1.1 (the reference's example graph) at batch 64 (every N) and batch 1 (N = 1)
+  squeezenet   SqueezeNet v1.1 (the reference's example graph) at batch 64 in the headline's class and in FP32 mode (every N), and at batch 1 (N = 1)
   sustained    >= 3 s of back-to-back dR_apply with the clock sampler running (N = 1)
   e2e_dropin   the reference-shaped blocking calls: dR_feedData ([C][H][W], pageable host memory) + dR_apply +
                dR_downloadArray, as examples/vgg16/vgg_deployed.c:141-166 makes them (N = 1)
@@ -392,6 +392,8 @@ def run_ours(args):
         sq = measure(ctx, "squeezenet", args.math, batch, max(args.steps, 20), 3)
         extra["fp32_exact"], extra["squeezenet_b64"] = fp, sq
         extra["fp32x3"] = measure(ctx, "vgg16", "fp32x3", batch, k2, 3, want_profile=True)
+        if args.math != "fp32":
+            extra["squeezenet_b64_fp32"] = measure(ctx, "squeezenet", "fp32", batch, k2, 3)
         if ctx.world == 1:
             extra["squeezenet_b1"] = measure(ctx, "squeezenet", args.math, 1, max(args.steps, 50), 5, cuda_graph=True)
             single = measure_dropin(ctx, k2, 3, batch, args.math)
@@ -502,6 +504,11 @@ def run_ours(args):
                                               "h2d_bytes_per_step": sq["h2d_bytes_per_step"]},
                                   "graph": "reference example graph (conv1 3x3 stride 1 + 2x2 average pool, 8 Fire modules, conv10, global average pool, softmax)",
                                   "math": args.math}
+            if "squeezenet_b64_fp32" in extra:
+                sf = extra["squeezenet_b64_fp32"]
+                line["squeezenet"]["batch64_fp32_mode"] = {"images_per_s": sf["images_per_s"], "ms_per_step": sf["ms_per_step"], "e2e_images_per_s": sf["e2e_images_per_s"],
+                                                           "launches_per_apply": sf["launches_per_apply"], "dtype": "f32",
+                                                           "conv_tflops": SQUEEZENET_CONV_FLOPS * sf["images_per_s"] / 1e12 / ctx.world}
             if "squeezenet_b1" in extra:
                 s1 = extra["squeezenet_b1"]
                 line["squeezenet"]["batch1"] = {"images_per_s": s1["images_per_s"], "ms_per_image": s1["ms_per_step"], "e2e_images_per_s": s1["e2e_images_per_s"],
