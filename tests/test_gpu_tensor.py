@@ -312,23 +312,31 @@ def test_tensor_core_winograd_matches_oracle(name, n, cin, cout, h, w):
     assert num / float(np.max(np.abs(res["fp32"]))) <= TOL_TF32
 
 
-def test_autotuner_may_choose_among_the_tensor_variants():
-    """TF32 mode with autotuning: direct tensor kernel and tensor-core Winograd are both timed; whichever wins, the result holds."""
+@pytest.mark.parametrize("math,tol", [("tf32", TOL_TF32), ("fp32x3", 1e-4)])
+def test_autotuner_may_choose_among_the_tensor_variants(math, tol):
+    """Tensor modes with autotuning: every family that can evaluate the layer in the mode's error class is timed (TF32: the direct
+    tensor kernel and tensor-core Winograd; FP32-accurate mode: the direct three-pass kernel, Winograd F(4x4,3x3) with three-pass
+    products and the FFMA kernels); whichever wins, the result holds at the mode's bound."""
     x, wt, b = cases.conv_case("tw_autotune", 8, 128, 128, 28, 28, 3, True)
     ref = oracle.conv2d(x[:1], wt, b, (1, 1), 1)
     with dr.Environment() as env:
         g = env.create_graph("CHW")
         g.batch = 8
-        g.math = "tf32"
+        g.math = math
         g.autotune = True
         f = dr.feed_node(g, [128, 28, 28])
         o = conv_build(wt, b, 1, 1)(g, [f])
         dr.mark_as_output(o)
         dr.prepare(g)
-        assert dr.lib.dR_getConvAlgo(o.ptr) in (dr.CONV_ALGO["tensor"], dr.CONV_ALGO["tensor_winograd"])
+        chosen = dr.lib.dR_getConvAlgo(o.ptr)
+        if math == "tf32":
+            assert chosen in (dr.CONV_ALGO["tensor"], dr.CONV_ALGO["tensor_winograd"])
+        else:
+            assert chosen in (dr.CONV_ALGO["tensor"], dr.CONV_ALGO["tensor_winograd"], dr.CONV_ALGO["winograd4"], dr.CONV_ALGO["winograd"], dr.CONV_ALGO["direct"])
         dr.feed_data(f, x)
         got = dr.apply(g)[0].reshape(8, 128, 28, 28)
-    assert rel_err(got[:1], ref) <= TOL_TF32
+        assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+    assert rel_err(got[:1], ref) <= tol
 
 
 X3_SHAPES = [
