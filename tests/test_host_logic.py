@@ -288,6 +288,53 @@ def test_static_rule_per_math_mode_on_the_vgg16_channel_plan():
             assert [dr.lib.dR_getConvTensor(c.ptr) for c in convs] == tensor[math], math
 
 
+def test_host_side_weight_packings():
+    """The host-side packers of the Winograd F(4x4,3x3) and tensor-FC kernels against their definitions in NumPy (no device)."""
+    import ctypes
+    lib = dr.lib
+    FP = ctypes.POINTER(ctypes.c_float)
+    rng = np.random.default_rng(7)
+    cin, cout = 32, 12
+    w = rng.standard_normal((cin, cout, 3, 3)).astype(np.float32)           # the reference's [Cin][Cout][kh][kw]
+    G = np.array([[1 / 4, 0, 0], [-1 / 6, -1 / 6, -1 / 6], [-1 / 6, 1 / 6, -1 / 6], [1 / 24, 1 / 12, 1 / 6], [1 / 24, -1 / 12, 1 / 6], [0, 0, 1]])
+    U = np.einsum("ij,cojk,lk->ilco", G, w.astype(np.float64), G)           # [6][6][Cin][Cout]
+    # FFMA path: [36][Cin][Cout] in float
+    lib.dRk_winograd4_pack_weights.argtypes = [FP, FP, ctypes.c_int, ctypes.c_int]
+    out = np.zeros((36, cin, cout), np.float32)
+    assert lib.dRk_winograd4_pack_weights(w.ctypes.data_as(FP), out.ctypes.data_as(FP), cin, cout) == 0
+    assert np.allclose(out, U.reshape(36, cin, cout), rtol=2e-7, atol=1e-9)     # double arithmetic, rounded to float once
+    # three-pass tensor path: [36][Cout][2*Cin], upper 19 bits of the float value, then the remainder of the double value
+    lib.dRk_tensor_winograd4_x3_packed_floats.restype = ctypes.c_size_t
+    lib.dRk_tensor_winograd4_x3_packed_floats.argtypes = [ctypes.c_int, ctypes.c_int]
+    assert lib.dRk_tensor_winograd4_x3_packed_floats(cin, cout) == 36 * cout * 2 * cin
+    lib.dRk_tensor_winograd4_x3_pack_weights.argtypes = [FP, FP, ctypes.c_int, ctypes.c_int]
+    out2 = np.zeros((36, cout, 2 * cin), np.float32)
+    assert lib.dRk_tensor_winograd4_x3_pack_weights(w.ctypes.data_as(FP), out2.ctypes.data_as(FP), cin, cout) == 0
+    Ut = U.reshape(36, cin, cout).transpose(0, 2, 1)                        # [36][Cout][Cin]
+    hi, lo = out2[:, :, :cin], out2[:, :, cin:]
+    assert not np.any(hi.view(np.uint32) & np.uint32(0x1FFF))               # a TF32 operand: the low 13 mantissa bits are zero
+    assert np.all(np.abs(lo) <= np.abs(hi) * 2.0 ** -10 + 1e-30)            # the remainder sits below the kept bits
+    assert np.max(np.abs(hi.astype(np.float64) + lo - Ut)) <= 2.0 ** -30 * np.max(np.abs(Ut))   # high + low carry the double value to ~2^-34
+    # tensor FC: [n tile][K slab][256][32], zeros past Nout; the three-pass packing is the high blocks followed by the low blocks
+    nin, nout = 64, 300
+    wf = rng.standard_normal((nin, nout)).astype(np.float32)
+    lib.dRk_tensor_fc_packed_floats.restype = ctypes.c_size_t
+    lib.dRk_tensor_fc_packed_floats.argtypes = [ctypes.c_int, ctypes.c_int]
+    assert lib.dRk_tensor_fc_packed_floats(nin, nout) == 2 * 256 * nin
+    lib.dRk_tensor_fc_pack_weights.argtypes = [FP, FP, ctypes.c_int, ctypes.c_int]
+    pk = np.full((2, nin // 32, 256, 32), 7.0, np.float32)
+    assert lib.dRk_tensor_fc_pack_weights(wf.ctypes.data_as(FP), pk.ctypes.data_as(FP), nin, nout) == 0
+    padded = np.zeros((nin, 512), np.float32)
+    padded[:, :nout] = wf
+    expect = padded.reshape(nin // 32, 32, 2, 256).transpose(2, 0, 3, 1)    # [tile][slab][row][e]
+    assert np.array_equal(pk, expect)
+    lib.dRk_tensor_fc_x3_pack_weights.argtypes = [FP, FP, ctypes.c_int, ctypes.c_int]
+    pk2 = np.full((2, 2, nin // 32, 256, 32), 7.0, np.float32)
+    assert lib.dRk_tensor_fc_x3_pack_weights(wf.ctypes.data_as(FP), pk2.ctypes.data_as(FP), nin, nout) == 0
+    ehi = (expect.view(np.uint32) & np.uint32(0xFFFFE000)).view(np.float32)
+    assert np.array_equal(pk2[:, 0], ehi) and np.array_equal(pk2[:, 1], expect - ehi)
+
+
 def test_tensor_planner_geometries_respect_the_kernels_limits():
     """Every geometry the planner can hand to the transposed and row-pair kernels stays inside what those kernels were
     written for: N a multiple of 16 and at most 256, whole 32-column epilogue chunks at the 16-pixel pitch, an even row
