@@ -89,6 +89,19 @@ def test_small_vgg_matches_oracle(tmp_path):
     assert np.array_equal(got.reshape(3, -1).argmax(1), ref.reshape(3, -1).argmax(1))
 
 
+@pytest.mark.parametrize("math,bound", [("fp32", 3e-4), ("fp32x3", 3e-4), ("tf32", 2e-2)])
+def test_mid_size_vgg_at_batch_16_in_every_math_mode(tmp_path, math, bound):
+    """A VGG-16 of half width at batch 16 against the oracle running the saved folder: in FP32 mode the 3x3 layers are Winograd
+    F(4x4,3x3) with its fused pooling, in the FP32-accurate tensor mode the deep layers are Winograd on the tensor cores and the
+    FC layers three-pass split-K GEMMs, in TF32 mode everything dense is a tensor kernel.  Logits, 16 layers deep."""
+    imgs = nets.synthetic_images("vgg_mid", 16, 32)
+    got, ref = run_vs_oracle(lambda g: nets.vgg16(g, size=32, width_div=2, fc_dims=(512, 512, 100), softmax=False), imgs, tmp_path, math=math)
+    got = got.reshape(ref.shape)
+    assert np.all(np.isfinite(ref))
+    assert rel_err(got, ref) <= bound
+    assert np.array_equal(got.reshape(16, -1).argmax(1), ref.reshape(16, -1).argmax(1))
+
+
 def test_small_vgg_logits_match_oracle_per_layer_bound(tmp_path):
     imgs = nets.synthetic_images("vgg_img2", 2, 32)
     got, ref = run_vs_oracle(lambda g: nets.vgg16(g, size=32, width_div=8, fc_dims=(512, 512, 100), softmax=False), imgs, tmp_path)
