@@ -350,7 +350,7 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
     size_t n = (size_t)kw * kh * I * O;
     if (algo == DR_CONV_WINOGRAD) n = (size_t)16 * I * O;
     if (algo == DR_CONV_WINOGRAD4) n = (size_t)36 * I * O;
-    if (algo == DR_CONV_TENSOR) n = x3Mode(net) ? dRk_tensor_conv_x3_packed_floats(I, O) : dRk_tensor_conv_packed_floats(c->ishape.s0, c->ishape.s1, I, O, kw, kh);
+    if (algo == DR_CONV_TENSOR) n = x3Mode(net) ? dRk_tensor_conv_x3_packed_floats(c->ishape.s0, c->ishape.s1, I, O) : dRk_tensor_conv_packed_floats(c->ishape.s0, c->ishape.s1, I, O, kw, kh);
     if (algo == DR_CONV_TENSOR_WINOGRAD) n = x3Mode(net) ? dRk_tensor_winograd4_x3_packed_floats(I, O) : dRk_tensor_winograd_packed_floats(I, O);
     if (n == 0) return FALSE;
     gfloat *p = (gfloat *)g_malloc0(n * sizeof(gfloat));
@@ -362,7 +362,7 @@ static gboolean ensurePacked(dR_Graph *net, dR_Node *layer, gint algo)
                     p[((size_t)t * I + i) * O + o] = c->weights[((size_t)i * O + o) * kh * kw + t];
     } else if (algo == DR_CONV_TENSOR) {
         /* K-major rows per output channel; the exact layout belongs to the tensor kernel picked for this shape */
-        if ((x3Mode(net) ? dRk_tensor_conv_x3_pack_weights(c->weights, p, I, O)
+        if ((x3Mode(net) ? dRk_tensor_conv_x3_pack_weights(c->weights, p, c->ishape.s0, c->ishape.s1, I, O)
                          : dRk_tensor_conv_pack_weights(c->weights, p, c->ishape.s0, c->ishape.s1, I, O, kw, kh)) != 0) { g_free(p); return FALSE; }
     } else if (algo == DR_CONV_TENSOR_WINOGRAD) {
         if ((x3Mode(net) ? dRk_tensor_winograd4_x3_pack_weights(c->weights, p, I, O) : dRk_tensor_winograd_pack_weights(c->weights, p, I, O)) != 0) { g_free(p); return FALSE; }

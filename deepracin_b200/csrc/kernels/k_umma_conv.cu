@@ -910,8 +910,9 @@ struct dRk_TensorConvPlan {
     int swap;           /* 1: k_umma_conv_swap (channels on M, 256 pixels on N) for Cout <= 128 */
     int first;          /* 1: k_umma_conv_first (Cin <= 4: patches gathered by producer warps, no tensor maps) */
     int pair;           /* 1: k_umma_conv_pair (Cout <= 64: two output rows stacked on M); mapA = odd input rows, mapA2 = even */
-    int x3;             /* 1: k_umma_conv_swap<true>, FP32-accurate three-pass evaluation; mapA2 = the filters' low parts */
-    CUtensorMap mapA2;
+    int x3;             /* 1: FP32-accurate three-pass evaluation: k_umma_conv_swap<true> (mapA2 = the filters' low parts) or, with pair,
+                           k_umma_conv_pair<true> (mapB2 = the filters' low parts) */
+    CUtensorMap mapA2, mapB2;
     const float *in, *wT;
     int sms;
     int ldi;            /* first-layer kernel: pixel stride of `in` and the optional affine channel map of its gather */
@@ -921,7 +922,8 @@ struct dRk_TensorConvPlan {
 
 double drk_umma_pair_fill(int W, int H);
 double drk_umma_pair_geometry(int W, int H, int *P, int *TW, int *TJ);
-int drk_umma_pair_launch(cudaStream_t st, const CUtensorMap *mapO, const CUtensorMap *mapE, const CUtensorMap *mapW, const UmmaParams *p, int grid);
+int drk_umma_pair_launch(cudaStream_t st, const CUtensorMap *mapO, const CUtensorMap *mapE, const CUtensorMap *mapW, const CUtensorMap *mapWlo,
+                         const UmmaParams *p, int grid, int x3);
 int drk_umma_first_supported(int Cin, int Cout, int kw, int kh);
 int drk_umma_first_can_pool(int W, int H, int Cin, int Cout);
 int drk_umma_first_launch(cudaStream_t st, const float *in, const float *wT, const float *bias, float *out, int n, int W, int H, int Cin,
@@ -1315,12 +1317,25 @@ extern "C" int dRk_tensor_conv_x3_supported(int W, int H, int Cin, int Cout)
     return dRk_tensor_conv_supported(W, H, Cin, Cout, 3, 3) && Cin >= 8 && Cin <= 768 && swap_geometry(W, H, 0, &P, &TW, &TH) > 0.0;
 }
 
-extern "C" size_t dRk_tensor_conv_x3_packed_floats(int Cin, int Cout) { return (size_t)2 * Cout * 9 * ((Cin + BK - 1) / BK * BK); }
+/* layers of at most 64 output channels whose image suits the row-pair blocks run k_umma_conv_pair<true>, all others k_umma_conv_swap<true> */
+static bool x3_uses_pair(int W, int H, int Cout)
+{
+    const drk_DebugSwitches *sw = dRk_debug_switches();
+    return Cout <= 64 && H >= 2 && drk_umma_pair_fill(W, H) >= 0.5 && !sw->no_pair && !sw->no_halo;
+}
 
-extern "C" int dRk_tensor_conv_x3_pack_weights(const float *w, float *dst, int Cin, int Cout)
+extern "C" size_t dRk_tensor_conv_x3_packed_floats(int W, int H, int Cin, int Cout)
+{
+    const size_t cp = (size_t)(Cin + BK - 1) / BK * BK;
+    return x3_uses_pair(W, H, Cout) ? (size_t)2 * BM * 12 * cp : (size_t)2 * Cout * 9 * cp;
+}
+
+extern "C" int dRk_tensor_conv_x3_pack_weights(const float *w, float *dst, int W, int H, int Cin, int Cout)
 {
     if (!w || !dst || Cin <= 0 || Cout <= 0) return -1;
-    const size_t cp = (size_t)(Cin + BK - 1) / BK * BK, half = (size_t)Cout * 9 * cp;
+    const size_t cp = (size_t)(Cin + BK - 1) / BK * BK;
+    const bool pair = x3_uses_pair(W, H, Cout);
+    const size_t half = pair ? (size_t)BM * 12 * cp : (size_t)Cout * 9 * cp;
     memset(dst, 0, 2 * half * sizeof(float));
     for (int c = 0; c < Cin; c++)
         for (int o = 0; o < Cout; o++)
@@ -1331,8 +1346,18 @@ extern "C" int dRk_tensor_conv_x3_pack_weights(const float *w, float *dst, int C
                 bits &= 0xffffe000u;                        /* what a kind::tf32 MMA reads of v */
                 float hi;
                 memcpy(&hi, &bits, 4);
-                dst[(size_t)o * 9 * cp + (size_t)t * cp + c] = v;
-                dst[half + (size_t)o * 9 * cp + (size_t)t * cp + c] = v - hi;
+                if (!pair) {
+                    dst[(size_t)o * 9 * cp + (size_t)t * cp + c] = v;
+                    dst[half + (size_t)o * 9 * cp + (size_t)t * cp + c] = v - hi;
+                } else {
+                    /* the row-pair layout of dRk_tensor_conv_pack_weights: row o holds tap (ky, kx) at i = ky, row 64 + o at i = ky + 1 */
+                    const int ky = t / 3, kx = t - ky * 3;
+                    for (int lower = 0; lower < 2; lower++) {
+                        const size_t at = (size_t)(lower * 64 + o) * 12 * cp + (size_t)((ky + lower) * 3 + kx) * cp + c;
+                        dst[at] = v;
+                        dst[half + at] = v - hi;
+                    }
+                }
             }
     return 0;
 }
@@ -1351,12 +1376,46 @@ extern "C" dRk_TensorConvPlan *dRk_tensor_conv_x3_plan(const float *in, const fl
     dRk_TensorConvPlan *pl = (dRk_TensorConvPlan *)calloc(1, sizeof(dRk_TensorConvPlan));
     if (!pl) return NULL;
     UmmaParams &p = pl->p;
-    pl->in = in; pl->wT = wT2; pl->sms = sms; pl->swap = 1; pl->x3 = 1; pl->BN = BM;
+    pl->in = in; pl->wT = wT2; pl->sms = sms; pl->x3 = 1; pl->BN = BM;
     p.n = n; p.W = W; p.H = H; p.Cin = Cin; p.Cout = Cout;
     p.CinPad = (Cin + BK - 1) / BK * BK;
     p.taps = 9; p.kw = 3; p.pad = 1; p.kslabs = p.CinPad / BK;
     p.bias = bias; p.out = out; p.ldo = ldo; p.coff = coff; p.act = act; p.status = status; p.pool = fuse_pool2 ? 1 : 0;
     p.ksplit = 1; p.kper = p.kslabs; p.S = 1;
+    if (x3_uses_pair(W, H, Cout)) {
+        /* the row-pair kernel in three-pass mode: planes and filters exactly as in dRk_tensor_conv_plan, FLOAT32 maps, one more map for the filters' low parts */
+        pl->pair = 1;
+        drk_umma_pair_geometry(W, H, &p.P, &p.TW, &p.TH);
+        p.ncols = p.P * p.TH;
+        p.tiles_x = (W + p.TW - 1) / p.TW; p.tiles_y = (H + 2 * p.TH - 1) / (2 * p.TH);
+        p.total_sub = (long long)n * p.tiles_x * p.tiles_y;
+        p.m_tiles = (int)p.total_sub;
+        p.n_tiles = 1;
+        const cuuint32_t ones4[4] = {1, 1, 1, 1};
+        const cuuint32_t pbox[4] = {BK, (cuuint32_t)p.P, (cuuint32_t)(p.TH + 1), 1};
+        const cuuint64_t pstr[3] = {(cuuint64_t)Cin * 4, (cuuint64_t)2 * W * Cin * 4, (cuuint64_t)H * W * Cin * 4};
+        const cuuint64_t dimsE[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)((H + 1) / 2), (cuuint64_t)n};
+        const cuuint64_t dimsO[4] = {(cuuint64_t)Cin, (cuuint64_t)W, (cuuint64_t)(H / 2), (cuuint64_t)n};
+        CUresult rp = enc(&pl->mapA2, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void *)in, dimsE, pstr, pbox, ones4, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rp == CUDA_SUCCESS)
+            rp = enc(&pl->mapA, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (void *)(in + (size_t)W * Cin), dimsO, pstr, pbox, ones4, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        const cuuint64_t Kp = (cuuint64_t)12 * p.CinPad;
+        const cuuint64_t fdims[2] = {Kp, (cuuint64_t)BM}, fstr[1] = {Kp * 4};
+        const cuuint32_t fbox[2] = {BK, BM};
+        if (rp == CUDA_SUCCESS)
+            rp = enc(&pl->mapB, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)wT2, fdims, fstr, fbox, ones4, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rp == CUDA_SUCCESS)
+            rp = enc(&pl->mapB2, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)(wT2 + (size_t)BM * Kp), fdims, fstr, fbox, ones4, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                     CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (rp != CUDA_SUCCESS) { fprintf(stderr, "tensor conv x3 plan: tensor map rejected (%d)\n", (int)rp); free(pl); return NULL; }
+        p.stage_tx = p.TW * p.TH * BK * 4 + BM * BK * 4;
+        pl->grid = (int)(p.m_tiles < sms ? p.m_tiles : sms);
+        return pl;
+    }
+    pl->swap = 1;
     long long geo_tiles;
     swap_geometry_for(n, W, H, Cout, fuse_pool2 ? 1 : 0, sms, &p.P, &p.TW, &p.TH, &geo_tiles);
     p.ncols = p.P * p.TH;
@@ -1421,7 +1480,7 @@ extern "C" int dRk_tensor_conv_run(dRk_stream stream, dRk_TensorConvPlan *pl)
         return drk_umma_first_launch(st, pl->in, pl->wT, pl->p.bias, pl->p.out, pl->p.n, pl->p.W, pl->p.H, pl->p.Cin, pl->p.Cout, pl->p.act,
                                      pl->ldi, pl->p.ldo, pl->p.coff, pl->p.pool, pl->p.status, pl->sms, pl->mapped ? pl->map_ch : NULL,
                                      pl->map_scale, pl->map_shift);
-    if (pl->pair) return drk_umma_pair_launch(st, &pl->mapA, &pl->mapA2, &pl->mapB, &pl->p, pl->grid);
+    if (pl->pair) return drk_umma_pair_launch(st, &pl->mapA, &pl->mapA2, &pl->mapB, pl->x3 ? &pl->mapB2 : &pl->mapB, &pl->p, pl->grid, pl->x3);
     if (pl->swap) {
         static bool attr_done[DRK_MAX_DEVICES];
         const int dev = current_device();

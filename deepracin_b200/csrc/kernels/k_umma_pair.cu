@@ -23,28 +23,38 @@
  * horizontal maxima to the upper-row warp of the same channels through a small double-buffered
  * shared-memory exchange guarded by mbarriers.  Every wait is bounded; on expiry the CTA flags an abort,
  * reports a code through `status`, drains its in-flight copies, frees TMEM and returns.
+ *
+ * X3 = true: FP32-accurate evaluation ("3xTF32", as k_umma_conv_swap<true>): every plane is multiplied three times into the
+ * same accumulator -- by the filter tiles as loaded (the MMA reads their upper 19 bits), by the tiles of the filters' low
+ * parts (mapWlo), and, with the plane's own low part x - hi(x) as the other operand, by the filter tiles again.  Four extra
+ * warps write that low part into a buffer of its own while the first two passes run; the plane ring is one slot shorter to
+ * make room for it.  Tensor maps are plain FLOAT32 in this mode.
  */
 #include <stdio.h>
 #include "k_common.cuh"
 #include "k_umma.cuh"
 
-#define PAIR_THREADS 192
+#define PAIR_SPLIT_WARPS 4                              /* X3 mode only */
+#define PAIR_THREADS(X3) (192 + ((X3) ? PAIR_SPLIT_WARPS * 32 : 0))
 /* Two block geometries, chosen per layer (UmmaParams P, TW, TH = row pairs per tile, ncols = P * TH):
  *   P = 16, 14 valid pixels, 16 row pairs: N = 256, 14 x 32 output pixels per tile (0.875 of the columns are pixels);
  *   P = 30, 28 valid pixels,  8 row pairs: N = 240, 28 x 16 output pixels per tile (0.933). */
 #define PAIR_N 256
 #define PAIR_PLANE_SLOT (35 * 1024)                     /* 280 rows: (TH + 1) * P <= 272 loaded, taps of idle columns read a few rows further */
-#define PAIR_NH 3                                       /* ring of plane slots: odd and even planes of a slab are separate stages */
+#define PAIR_NH 3                                       /* ring of plane slots: odd and even planes of a slab are separate stages (X3: two, the third slot holds the low part) */
 #define PAIR_W_BYTES (BM * BK * 4)
 #define PAIR_NW 7
 #define PAIR_X_FLOATS (2 * 7 * 32)                      /* one exchange buffer: 2 pooled rows x 7 pooled pixels x 32 lanes */
 #define PAIR_X_BYTES (2 * 2 * PAIR_X_FLOATS * 4)        /* two warp pairs x two buffers */
 #define PAIR_SMEM (PAIR_NH * PAIR_PLANE_SLOT + PAIR_NW * PAIR_W_BYTES + PAIR_X_BYTES + 1024 + 512)
 
-__global__ void __launch_bounds__(PAIR_THREADS, 1)
+template <bool X3>
+__global__ void __launch_bounds__(PAIR_THREADS(X3), 1)
 k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant__ CUtensorMap mapE, const __grid_constant__ CUtensorMap mapW,
-                 const UmmaParams p)
+                 const __grid_constant__ CUtensorMap mapWlo, const UmmaParams p)
 {
+    constexpr int NH = X3 ? PAIR_NH - 1 : PAIR_NH;      /* plane slots in the ring */
+    constexpr int PASSES = X3 ? 3 : 1;
     extern __shared__ uint8_t smem_raw[];
     drk_dep_trigger();
     const uint32_t raw = smem_u32(smem_raw);
@@ -54,7 +64,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
     const uint32_t x_off = PAIR_NH * PAIR_PLANE_SLOT + PAIR_NW * PAIR_W_BYTES;
     float *xbuf = reinterpret_cast<float *>(gen + x_off);
     const uint32_t bars = base + x_off + PAIR_X_BYTES;
-    constexpr int NBARS = 2 * PAIR_NH + 2 * PAIR_NW + 4 + 8 + 1;
+    constexpr int NBARS = 2 * PAIR_NH + 2 * PAIR_NW + 4 + 8 + 1 + 2;
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(gen + x_off + PAIR_X_BYTES + 8 * NBARS);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     auto hfull = [&](int s) { return bars + 8u * s; };
@@ -66,6 +76,9 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
     auto xfull = [&](int pr, int b) { return bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + 4 + pr * 4 + b); };
     auto xempty = [&](int pr, int b) { return bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + 4 + pr * 4 + 2 + b); };
     const uint32_t drain_bar = bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + 4 + 8);
+    const uint32_t xlo_full = bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + 4 + 8 + 1);     /* X3: the low-part buffer holds the current plane's low parts */
+    const uint32_t xlo_free = bars + 8u * (2 * PAIR_NH + 2 * PAIR_NW + 4 + 8 + 2);     /* X3: pass 3 of the previous plane has read it */
+    const uint32_t xlo_base = h_base + NH * PAIR_PLANE_SLOT;                            /* X3: the ring's last slot */
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int total_tiles = p.m_tiles;
@@ -80,6 +93,8 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
         for (int pr = 0; pr < 2; pr++)
             for (int b = 0; b < 2; b++) { mbar_init(xfull(pr, b), 1); mbar_init(xempty(pr, b), 1); }
         mbar_init(drain_bar, 1);
+        mbar_init(xlo_full, PAIR_SPLIT_WARPS);
+        mbar_init(xlo_free, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -95,6 +110,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
             asm volatile("prefetch.tensormap [%0];" ::"l"(&mapO) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&mapE) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&mapW) : "memory");
+            if (X3) asm volatile("prefetch.tensormap [%0];" ::"l"(&mapWlo) : "memory");
             int hs = 0, ws = 0;
             uint32_t hph = 0, wph = 0;
             long long h_issued = 0, w_issued = 0;
@@ -112,12 +128,13 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
                         if (half == 0) tma_load_4d(h_base + hs * PAIR_PLANE_SLOT, &mapO, ks * BK, txi * p.TW - 1, j0 - 1, img, hfull(hs));
                         else tma_load_4d(h_base + hs * PAIR_PLANE_SLOT, &mapE, ks * BK, txi * p.TW - 1, j0, img, hfull(hs));
                         h_issued++;
-                        if (++hs == PAIR_NH) { hs = 0; hph ^= 1u; }
-                        for (int q = 0; q < 6; q++) {
+                        if (++hs == NH) { hs = 0; hph ^= 1u; }
+                        for (int pq = 0; pq < 6 * PASSES && ok; pq++) {             /* X3: the filter tiles, their low parts, the filter tiles again */
+                            const int q = pq % 6;
                             const int i = half + 2 * (q / 3), kx = q % 3;           /* input row 2j-1+i: i = 0, 2 live in the odd plane, 1, 3 in the even */
                             if (!mbar_wait(wempty(ws), wph ^ 1u, abort_flag, p.status, 1)) { ok = false; break; }
                             mbar_expect_tx(wfull(ws), PAIR_W_BYTES);
-                            tma_load_2d(w_base + ws * PAIR_W_BYTES, &mapW, (i * 3 + kx) * p.CinPad + ks * BK, 0, wfull(ws));
+                            tma_load_2d(w_base + ws * PAIR_W_BYTES, (X3 && pq / 6 == 1) ? &mapWlo : &mapW, (i * 3 + kx) * p.CinPad + ks * BK, 0, wfull(ws));
                             w_issued++;
                             if (++ws == PAIR_NW) { ws = 0; wph ^= 1u; }
                         }
@@ -125,10 +142,10 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
                 }
             }
             if (!ok) {
-                long long pend = h_issued < PAIR_NH ? h_issued : PAIR_NH;
+                long long pend = h_issued < NH ? h_issued : NH;
                 int s = hs; uint32_t ph = hph;
                 for (long long i = 0; i < pend; i++) {
-                    if (--s < 0) { s = PAIR_NH - 1; ph ^= 1u; }
+                    if (--s < 0) { s = NH - 1; ph ^= 1u; }
                     const long long t0 = clock64();
                     while (!mbar_try(hfull(s), ph) && clock64() - t0 < WAIT_CYCLES) { }
                 }
@@ -145,7 +162,7 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
         if (lane == 0) {
             const uint32_t idesc = make_idesc(p.ncols);
             int hs = 0, ws = 0;
-            uint32_t hph = 0, wph = 0;
+            uint32_t hph = 0, wph = 0, xph = 0;
             int it = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x, it++) {
@@ -157,29 +174,37 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
                 for (int ks = 0; ks < p.kslabs && ok; ks++) {
                     for (int half = 0; half < 2 && ok; half++) {
                         if (!mbar_wait(hfull(hs), hph, abort_flag, p.status, 6)) { ok = false; break; }
-                        const uint32_t plane = h_base + hs * PAIR_PLANE_SLOT;
-                        for (int q = 0; q < 6; q++) {
+                        uint32_t plane = h_base + hs * PAIR_PLANE_SLOT;
+                        for (int pq = 0; pq < 6 * PASSES && ok; pq++) {
+                            if (X3 && pq == 12) {
+                                /* passes 0 and 1 (plane as loaded) are issued; pass 2 reads its low part, which the splitter warps wrote */
+                                if (!mbar_wait(xlo_full, xph, abort_flag, p.status, 12)) { ok = false; break; }
+                                tc_fence_after();
+                                plane = xlo_base;
+                            }
                             if (!mbar_wait(wfull(ws), wph, abort_flag, p.status, 3)) { ok = false; break; }
                             tc_fence_after();
                             /* input row 2j-1+i with i = half + 2*(q/3): the second three products read one block row further down */
+                            const int q = pq % 6;
                             const int down = q / 3, kx = q - down * 3;
                             const uint64_t adesc = make_smem_desc(w_base + ws * PAIR_W_BYTES);
                             const uint64_t bdesc = make_smem_desc(plane + (uint32_t)((down * p.P + kx) * BK * 4));
 #pragma unroll
                             for (int j = 0; j < BK / 8; j++)
-                                umma_tf32(d_tmem, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, (ks | half | q | j) ? 1u : 0u);
+                                umma_tf32(d_tmem, adesc + (uint64_t)(j * 2), bdesc + (uint64_t)(j * 2), idesc, (ks | half | pq | j) ? 1u : 0u);
                             umma_commit(wempty(ws));
                             if (++ws == PAIR_NW) { ws = 0; wph ^= 1u; }
                         }
+                        if (X3) { if (ok) umma_commit(xlo_free); xph ^= 1u; }
                         if (ok) umma_commit(hempty(hs));
-                        if (++hs == PAIR_NH) { hs = 0; hph ^= 1u; }
+                        if (++hs == NH) { hs = 0; hph ^= 1u; }
                     }
                 }
                 if (ok) umma_commit(tfull_bar(acc));
             }
             if (!ok) umma_drain(drain_bar);
         }
-    } else {
+    } else if (warp < 6) {
         const int quarter = warp & 3;
         const int lower = quarter >> 1;                          /* 0: output rows 2j, 1: rows 2j+1 */
         const int pr = quarter & 1;                              /* channels pr*32 .. pr*32+31 */
@@ -315,6 +340,36 @@ k_umma_conv_pair(const __grid_constant__ CUtensorMap mapO, const __grid_constant
             __syncwarp();
             if (lane == 0) mbar_arrive(tempty_bar(acc));
         }
+    } else if (X3) {
+        /* splitter warps: the low part of every plane into the low-part buffer, while passes 0 and 1 of that plane run */
+        const int sw = warp - 6;
+        int hs = 0;
+        uint32_t hph = 0, xph = 0;
+        bool ok = true;
+        const int chunks = (int)(plane_bytes / 16);
+        for (int t = blockIdx.x; t < total_tiles && ok; t += gridDim.x) {
+            for (int kh = 0; kh < 2 * p.kslabs; kh++) {
+                /* the plane was written by TMA: wait on its barrier (visibility); the buffer is free once pass 2 of the plane before
+                   has read it (first use: the wait on the preceding phase returns at once) */
+                if (!mbar_wait_warp(hfull(hs), hph, abort_flag, p.status, 10)) { ok = false; break; }
+                if (!mbar_wait_warp(xlo_free, xph ^ 1u, abort_flag, p.status, 11)) { ok = false; break; }
+                const uint4 *blk = reinterpret_cast<const uint4 *>(gen + hs * PAIR_PLANE_SLOT);
+                uint4 *lo = reinterpret_cast<uint4 *>(gen + NH * PAIR_PLANE_SLOT);
+                for (int i = sw * 32 + lane; i < chunks; i += PAIR_SPLIT_WARPS * 32) {
+                    uint4 v = blk[i];
+                    v.x = __float_as_uint(__uint_as_float(v.x) - __uint_as_float(v.x & 0xffffe000u));
+                    v.y = __float_as_uint(__uint_as_float(v.y) - __uint_as_float(v.y & 0xffffe000u));
+                    v.z = __float_as_uint(__uint_as_float(v.z) - __uint_as_float(v.z & 0xffffe000u));
+                    v.w = __float_as_uint(__uint_as_float(v.w) - __uint_as_float(v.w & 0xffffe000u));
+                    lo[i] = v;
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(xlo_full);
+                xph ^= 1u;
+                if (++hs == NH) { hs = 0; hph ^= 1u; }
+            }
+        }
     }
     tc_fence_before();
     __syncthreads();
@@ -342,18 +397,22 @@ double drk_umma_pair_fill(int W, int H)
     return drk_umma_pair_geometry(W, H, &P, &TW, &TJ);
 }
 
-int drk_umma_pair_launch(cudaStream_t st, const CUtensorMap *mapO, const CUtensorMap *mapE, const CUtensorMap *mapW, const UmmaParams *p, int grid)
+/* mapWlo: the filters' low parts (three-pass mode, x3 != 0); otherwise unused (pass mapW) */
+int drk_umma_pair_launch(cudaStream_t st, const CUtensorMap *mapO, const CUtensorMap *mapE, const CUtensorMap *mapW, const CUtensorMap *mapWlo,
+                         const UmmaParams *p, int grid, int x3)
 {
     static bool attr_done[64];                      /* the opt-in shared-memory size is a per-device function attribute */
     int dev = 0;
     cudaGetDevice(&dev);
     if (dev < 0 || dev >= 64) dev = 0;
     if (!attr_done[dev]) {
-        cudaError_t e = cudaFuncSetAttribute(k_umma_conv_pair, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
+        cudaError_t e = cudaFuncSetAttribute(k_umma_conv_pair<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(k_umma_conv_pair<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, PAIR_SMEM);
         if (e != cudaSuccess) return (int)e;
         attr_done[dev] = true;
     }
-    drk_launch_dep(k_umma_conv_pair, dim3(grid), dim3(PAIR_THREADS), PAIR_SMEM, st, *mapO, *mapE, *mapW, *p);
+    if (x3) drk_launch_dep(k_umma_conv_pair<true>, dim3(grid), dim3(PAIR_THREADS(1)), PAIR_SMEM, st, *mapO, *mapE, *mapW, *mapWlo, *p);
+    else drk_launch_dep(k_umma_conv_pair<false>, dim3(grid), dim3(PAIR_THREADS(0)), PAIR_SMEM, st, *mapO, *mapE, *mapW, *mapW, *p);
     DRK_COUNT_LAUNCH();
     return DRK_LAUNCH_RESULT();
 }

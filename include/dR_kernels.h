@@ -163,13 +163,14 @@ dRk_TensorConvPlan *dRk_tensor_conv_plan(const float *in, const float *wT, const
 int dRk_tensor_conv_set_input_map(dRk_TensorConvPlan *plan, int ldi, const int *ch, const float *scale, const float *shift);
 /* FP32-accurate 3x3 stride-1 convolution on the tensor cores ("3xTF32"): every product x*w is evaluated as
  * hi(x)*hi(w) + hi(x)*lo(w) + lo(x)*hi(w) with hi() = the 19 bits a TF32 MMA reads, in three passes into one FP32 accumulator
- * (transposed kernel, FLOAT32 tensor maps, the low part of the activations computed in shared memory).  Error bound as the
+ * (transposed kernel, or the row-pair kernel for at most 64 output channels; FLOAT32 tensor maps, the low part of the activations
+ * computed in shared memory).  Error bound as the
  * exact-FP32 kernels (1e-4 * max|ref| per layer) at a third of the TF32 kernels' rate.  Same reference kernel as dRk_tensor_conv
  * (conv2dwinograd2, Kernels/dR_winograd2.cl:23-254).  wT2 = filters + their low parts, dRk_tensor_conv_x3_pack_weights;
  * the returned plan runs and is freed with dRk_tensor_conv_run / dRk_tensor_conv_free. */
 int dRk_tensor_conv_x3_supported(int W, int H, int Cin, int Cout);
-size_t dRk_tensor_conv_x3_packed_floats(int Cin, int Cout);
-int dRk_tensor_conv_x3_pack_weights(const float *w, float *dst, int Cin, int Cout);
+size_t dRk_tensor_conv_x3_packed_floats(int W, int H, int Cin, int Cout);
+int dRk_tensor_conv_x3_pack_weights(const float *w, float *dst, int W, int H, int Cin, int Cout);
 dRk_TensorConvPlan *dRk_tensor_conv_x3_plan(const float *in, const float *wT2, const float *bias, float *out, int n, int W, int H,
                                             int Cin, int Cout, int act, int ldo, int coff, int fuse_pool2, int *status);
 /* Planner introspection, no device needed: the kernel (1 flat 1x1, 2 plain, 3 halo, 4 transposed, 5 row pair, 6 few-channel

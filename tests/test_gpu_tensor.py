@@ -1,5 +1,7 @@
 """GPU parity tests of the tensor-core (tcgen05, TF32) convolution path against the CPU oracle.
 Bound: max|err| <= 3e-3 * max|ref| per layer output, and equal softmax top-1 on whole networks."""
+import ctypes
+
 import numpy as np
 import pytest
 
@@ -350,6 +352,8 @@ X3_SHAPES = [
     ("x3_conv3_2", 40, 256, 256, 56, 56, False),           # the benchmark's geometries at full depth
     ("x3_conv5_pool", 64, 512, 512, 14, 14, True),
     ("x3_conv1_2", 4, 64, 64, 224, 224, True),
+    ("x3_w15", 2, 24, 40, 34, 15, False),                   # too narrow for the row-pair blocks: transposed kernel; Cin not a multiple of 32
+    ("x3_pair_odd_h", 2, 32, 48, 61, 28, False),
 ]
 
 
@@ -372,6 +376,10 @@ def test_fp32_accurate_tensor_conv_matches_oracle_at_the_fp32_bound(name, n, cin
         got = dr.apply(g)[0]
         launches = dr.lib.dR_getLaunchCount(g.ptr)
         assert dr.lib.dR_getDeviceStatus(g.ptr) == 0
+        geom = (ctypes.c_int * 4)()
+        kernel = dr.lib.dR_getConvTensorKernel(c.ptr, geom)
+        # at most 64 output channels on an image that suits its blocks: the row-pair kernel in three-pass mode (5); else the transposed kernel (4)
+        assert kernel == (5 if name in ("x3_pool_p30", "x3_conv1_2", "x3_pair_odd_h") else 4), (name, kernel, list(geom))
     ho, wo = (h // 2, w // 2) if pool else (h, w)
     got = got.reshape(n, cout, ho, wo)
     assert launches == 3                                # feed layout, convolution (+ pool in its epilogue), output layout
